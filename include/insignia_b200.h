@@ -1,0 +1,301 @@
+/*
+ * insignia_b200 -- C ABI of the sm_100a decode kernels and of the decode engine.
+ *
+ * This is the boundary a maintainer of the reference (novysvet/insignia) binds
+ * to replace its token loop.  Every entry point takes plain pointers, sizes and
+ * a CUDA stream; none allocates device memory or synchronises unless its comment
+ * says so.  Return value: 0 on success, a negative INSG_E_* code otherwise
+ * (insg_last_error() gives text).  All pointers are DEVICE pointers unless
+ * marked "host".  Each comment cites the reference interface the entry point
+ * replaces, as path:line in the reference project.
+ */
+#ifndef INSIGNIA_B200_H
+#define INSIGNIA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define INSG_API __attribute__((visibility("default")))
+#else
+#define INSG_API
+#endif
+
+typedef struct CUstream_st *insg_stream_t; /* == cudaStream_t */
+
+enum {
+    INSG_OK = 0,
+    INSG_E_SHAPE = -1,   /* unsupported or inconsistent sizes            */
+    INSG_E_CUDA = -2,    /* a CUDA runtime call or launch failed         */
+    INSG_E_ARG = -3,     /* null pointer / bad enum / misaligned pointer */
+    INSG_E_RUNTIME = -4, /* host-side std::runtime_error (engine calls)  */
+    INSG_E_LIMIT = -5    /* size beyond a documented fixed maximum       */
+};
+
+INSG_API const char *insg_last_error(void);  /* host string, thread-local */
+INSG_API int insg_version(void);
+/* Kernel tuning knobs ("gemv_deq" 0|1, "gemv_unr" 2|4, "gemv_ctas_per_sm"); process-wide, for benchmarking. */
+INSG_API int insg_tune_set(const char *key /* host */, int value);
+
+/* ------------------------------------------------------------------ MXFP4 */
+
+/* y[rows] = W x, W in the MLX checkpoint layout: U32[rows][cols/8] (nibble j of
+ * word i = element 8i+j) + U8[rows][cols/32] E8M0 scales; x, y fp32.
+ * cols % 32 == 0.  Replaces mxfp4_gemv_mlx (include/insignia_layout.cuh:48,
+ * src/mxfp4.cu:41-77); the warps_per_row knob of the reference has no meaning
+ * here and is dropped. */
+INSG_API int insg_mxfp4_gemv_mlx(const uint32_t *weight, const uint8_t *scales, const float *x, float *y, int rows,
+                                 int cols, insg_stream_t stream);
+
+/* out[cols] = dequantised row `row` (the embedding lookup).  Replaces
+ * mxfp4_get_row_mlx (include/insignia_layout.cuh:49, src/mxfp4.cu:132-133). */
+INSG_API int insg_mxfp4_get_row_mlx(const uint32_t *weight, const uint8_t *scales, float *out, int row, int cols,
+                                    insg_stream_t stream);
+
+/* Same lookup with the row index read from device memory (*device_row), so the call can sit
+ * inside a captured CUDA graph; rows outside [0, rows) produce zeros.  Replaces
+ * Qwen35Weights::embed (src/qwen35.cu:9) on the engine's path. */
+INSG_API int insg_mxfp4_embed(const uint32_t *weight, const uint8_t *scales, float *out, const int *device_row,
+                              int rows, int cols, int pdl, insg_stream_t stream);
+
+/* Writes the two device scalars the engine's kernels read (token id, position); either pointer may be NULL. */
+INSG_API int insg_set_scalars(int *device_token, int token, int *device_position, int position, insg_stream_t stream);
+
+/* out[rows][cols] fp32 = full dequantisation, bit-exact with the reference's
+ * decode of a code and a scale byte (src/mxfp4.cu:50-53: lut[code] * (scale<<23)).
+ * Exists so dequantisation can be checked bit for bit. */
+INSG_API int insg_mxfp4_dequant_mlx(const uint32_t *weight, const uint8_t *scales, float *out, int rows, int cols,
+                                    insg_stream_t stream);
+
+/* Tile-interleaved weight layout used by the fused GEMV kernels.  Same
+ * information and the same byte count as the MLX layout (17 bytes per 32
+ * weights): rows are grouped in tiles of 16, K in blocks of 128, and each
+ * (tile, block) record is 1024 bytes of nibbles + 64 scale bytes laid out in the
+ * order the tensor-core fragments consume them.  rows % 16 == 0, cols % 128 == 0.
+ * No reference counterpart: the reference streams the MLX layout directly
+ * (src/decode.cu:13). */
+INSG_API size_t insg_mxfp4_packed_bytes(int rows, int cols);
+INSG_API int insg_mxfp4_repack(const uint32_t *weight, const uint8_t *scales, void *packed, int rows, int cols,
+                               insg_stream_t stream);
+
+/* y[m][rows] = W x[m] for m < M (1 <= M <= 8), W in the packed layout; x is
+ * fp32 [M][cols], y fp32 [M][rows].  Plain (no fused prologue/epilogue) form of
+ * the kernel the engine runs; replaces Qwen35Decode::linear (src/decode.cu:13). */
+INSG_API int insg_mxfp4_gemv_packed(const void *packed, const float *x, float *y, int rows, int cols, int M,
+                                    insg_stream_t stream);
+
+/* ---------------------------------------------------------- fused GEMV op */
+
+/* What is done to the activation vector before the contraction. */
+enum {
+    INSG_PRO_PLAIN = 0,        /* x = in                                                        */
+    INSG_PRO_RMSNORM = 1,      /* x = in * rsqrt(mean(in^2)+1e-6) * w_bf16          (src/qwen_kernels.cu:5) */
+    INSG_PRO_GATED_RMSNORM = 2,/* per 128-wide head: rmsnorm(in) * w_bf16[128] * silu(aux)  (src/qwen_kernels.cu:5, G) */
+    INSG_PRO_SIGMOID_GATE = 3, /* x = in * sigmoid(aux[i])                           (src/qwen_kernels.cu:11) */
+    INSG_PRO_SIGMOID_GATE_HEAD0 = 4, /* x = in * sigmoid(aux[(i>>8)*512+256]) : gate element 0 of the head
+                                  broadcast over its 256 lanes; aux is the interleaved q_proj output
+                                  (src/qwen_kernels.cu:31,36) */
+    INSG_PRO_SIGMOID_GATE_QPROJ = 5 /* x = in * sigmoid(aux[(i>>8)*512+256+(i&255)]) : element-wise gate read
+                                  from the interleaved q_proj output */
+};
+
+/* What is done with each output row. */
+enum {
+    INSG_EPI_STORE = 0,     /* out[row] = y                                                     */
+    INSG_EPI_RESIDUAL = 1,  /* out[row] += y                                   (src/ops.cu:8)   */
+    INSG_EPI_CONV_SILU = 2, /* causal conv4 + SiLU on channel `row` with history  (src/qwen_kernels.cu:7) */
+    INSG_EPI_BETA = 3,      /* out[row] = sigmoid(y)                           (src/qwen_kernels.cu:9) */
+    INSG_EPI_DECAY = 4,     /* out[row] = -exp(A_log[row]) * softplus(y + dt_bias[row]) (src/qwen_kernels.cu:9) */
+    INSG_EPI_SWIGLU = 5,    /* two matrices: out[row] = silu(y_gate) * y_up    (src/ops.cu:7)   */
+    INSG_EPI_LOGITS = 6     /* out[row] = y and a running arg-max of the rows  (src/qwen_kernels.cu:20) */
+};
+
+/* One matrix (or gate/up pair) inside a fused launch. */
+typedef struct insg_gemv_segment {
+    const void *packed;      /* packed weights                                         */
+    const void *packed2;     /* second matrix for INSG_EPI_SWIGLU, else NULL           */
+    float *out;              /* fp32 [rows]                                            */
+    int rows;                /* multiple of 16                                         */
+    int epilogue;            /* INSG_EPI_*                                             */
+    float *conv_state;       /* CONV_SILU: fp32 [rows][3] history, updated             */
+    const uint16_t *conv_w;  /* CONV_SILU: bf16 [rows][4]                              */
+    const float *A_log;      /* DECAY: fp32 [rows]                                     */
+    const uint16_t *dt_bias; /* DECAY: bf16 [rows]                                     */
+} insg_gemv_segment;
+
+/* A fused launch: prologue on the shared input vector, up to 4 matrices that
+ * all multiply it, an epilogue per matrix.  cols % 128 == 0, cols <= 12288. */
+typedef struct insg_gemv_op {
+    const float *in;          /* fp32 [cols]                                           */
+    const float *aux;         /* prologue operand (gate / z), or NULL                  */
+    const uint16_t *norm_w;   /* bf16 norm weight for the RMSNorm prologues, or NULL   */
+    float *x_out;             /* optional: the prologue's result fp32 [cols], or NULL  */
+    int cols;
+    int prologue;             /* INSG_PRO_*                                            */
+    int n_segments;           /* 1..4                                                  */
+    insg_gemv_segment seg[4];
+    /* INSG_EPI_LOGITS only: partial arg-max scratch (>= insg_gemv_argmax_scratch_bytes(), its
+     * first 64 bytes zero before the first call and left zero by every call).  The winning row
+     * is written to *token_out and, when non-NULL, to *token_feedback and to
+     * token_log[*position_inout]; then *position_inout is incremented (when non-NULL). */
+    void *argmax_scratch;
+    int *token_out;
+    int *token_feedback;
+    int *token_log;
+    int *position_inout;
+    int pdl;                  /* 1: launch with programmatic dependent launch          */
+} insg_gemv_op;
+
+INSG_API size_t insg_gemv_argmax_scratch_bytes(void);
+INSG_API int insg_gemv_fused(const insg_gemv_op *op /* host */, insg_stream_t stream);
+
+/* ------------------------------------------------------------ DeltaNet */
+
+/* One gated-delta-rule step for 32 value heads (16 q/k heads, head>>1), dk=dv=128.
+ * state fp32 [32][128(k)][128(v)] updated in place; q16,k16 fp32 [16][128];
+ * v32 fp32 [32][128]; g32, beta32 fp32 [32]; out32 fp32 [32][128].
+ * Replaces deltanet_decode (include/insignia_deltanet.cuh:5, src/deltanet.cu:4-14). */
+INSG_API int insg_deltanet_decode(float *state, const float *q16, const float *k16, const float *v32,
+                                  const float *g32, const float *beta32, float *out32, int pdl,
+                                  insg_stream_t stream);
+
+/* ------------------------------------------------------------ attention */
+
+/* KV cache element type. */
+enum { INSG_KV_F32 = 0, INSG_KV_BF16 = 1 };
+
+/* Bytes of scratch insg_gqa_decode needs for `tokens` cached tokens. */
+INSG_API size_t insg_gqa_scratch_bytes(int tokens);
+
+/* Split-K flash-decode for 16 query heads over 4 kv heads, head_dim 256, scale
+ * 1/16: out[16][256] = softmax(q K^T / 16) V over `tokens` cache rows; cache
+ * layout [token][4][256] of fp32 or bf16.  q fp32 [16][256] already normalised
+ * and rotated.  `scratch` holds the per-split partials (see
+ * insg_gqa_scratch_bytes); its first 64 bytes must be zero before the first call
+ * and are left zero by every call.  Replaces gqa_decode
+ * (include/insignia_attention.cuh:4, src/attention.cu:4-5), without its ~12K-token
+ * shared-memory limit. */
+INSG_API int insg_gqa_decode(const float *q, const void *k_cache, const void *v_cache, float *out, int tokens,
+                             int kv_dtype, void *scratch, size_t scratch_bytes, insg_stream_t stream);
+
+/* Fused attention step of the engine: per-head RMSNorm of q and k (bf16 weights,
+ * eps 1e-6), partial RoPE on dims 0..63 at *position (theta 1e7, rotate-half,
+ * skipped at position 0), store of k,v at cache row *position, then the same
+ * split-K attention over *position+1 rows.  qraw is the interleaved q_proj
+ * output [16][q256|gate256]; k_raw, v fp32 [4][256].  Replaces
+ * split_q_gate + qwen35_qk_norm_rope_gate + store_kv + gqa_decode
+ * (src/qwen_kernels.cu:15,31; src/ops.cu:9; src/attention.cu:4). */
+typedef struct insg_attn_op {
+    const float *qraw;
+    const float *k_raw;
+    const float *v;
+    const uint16_t *q_norm_w; /* bf16 [256] */
+    const uint16_t *k_norm_w; /* bf16 [256] */
+    void *k_cache;
+    void *v_cache;
+    float *out;               /* fp32 [16][256]                                       */
+    const int *position;      /* device int: cache row / rotary position of this token */
+    int position_offset;      /* added to *position (the MTP head passes -1)          */
+    int max_context;
+    int kv_dtype;
+    int fast_trig;            /* 1: __powf/__sinf/__cosf as the reference (src/ops.cu:9), 0: accurate */
+    void *scratch;
+    size_t scratch_bytes;
+    int pdl;
+} insg_attn_op;
+INSG_API int insg_attention_step(const insg_attn_op *op /* host */, insg_stream_t stream);
+
+/* ----------------------------------------------- stand-alone small kernels */
+/* One entry point per reference free function, same argument meaning. */
+
+/* src/qwen_kernels.cu:6 (rmsnorm_bf16 / gated_rmsnorm_bf16); gate may be NULL */
+INSG_API int insg_rmsnorm_bf16(const float *x, const uint16_t *w, const float *gate, float *y, int rows, int cols,
+                               int zero_centered, insg_stream_t stream);
+/* src/ops.cu:6 (rmsnorm_zero_centered, fp32 weight, 1+w) */
+INSG_API int insg_rmsnorm_zero_centered(const float *x, const float *w, float *y, int rows, int cols, float eps,
+                                        insg_stream_t stream);
+/* src/qwen_kernels.cu:8 */
+INSG_API int insg_causal_conv4_silu(float *x, float *state, const uint16_t *w, int channels, insg_stream_t stream);
+/* src/qwen_kernels.cu:10 */
+INSG_API int insg_deltanet_parameters(float *a, float *b, const float *A_log, const uint16_t *dt_bias, int heads,
+                                      insg_stream_t stream);
+/* src/ops.cu:10 (the reference's unused `gate` argument is dropped) */
+INSG_API int insg_qk_norm_rope(float *q, float *k, const uint16_t *q_w, const uint16_t *k_w, int position,
+                               int fast_trig, insg_stream_t stream);
+/* src/ops.cu:7,8 */
+INSG_API int insg_silu_mul(const float *gate, const float *up, float *y, int n, insg_stream_t stream);
+INSG_API int insg_residual_add(float *x, const float *delta, int n, insg_stream_t stream);
+/* src/qwen_kernels.cu:11,16,32,37,27 */
+INSG_API int insg_sigmoid_mul(float *x, const float *gate, int n, insg_stream_t stream);
+INSG_API int insg_store_kv(const float *k, const float *v, void *k_cache, void *v_cache, int position,
+                           int kv_dtype, insg_stream_t stream);
+INSG_API int insg_split_q_gate(const float *interleaved, float *q, float *gate, insg_stream_t stream);
+INSG_API int insg_expand_gate_heads(const float *head_gate, float *gate256, insg_stream_t stream);
+INSG_API int insg_concat(const float *a, const float *b, float *out, int n, insg_stream_t stream);
+/* src/qwen_kernels.cu:21 ; ties resolve to the lowest index */
+INSG_API int insg_argmax_logits(const float *logits, int n, int *device_token, insg_stream_t stream);
+/* src/qwen_kernels.cu:26 : y[rows] = W_bf16[rows][cols] x (mtp.fc) */
+INSG_API int insg_bf16_gemv(const uint16_t *w, const float *x, float *y, int rows, int cols, int pdl,
+                            insg_stream_t stream);
+
+/* --------------------------------------------------------------- engine */
+/* Handle-based face of the C++ host classes (ModelFile, Qwen35Weights,
+ * DecodeWorkspace, Qwen35Decode: include/insignia_model.hpp, insignia_qwen35.hpp,
+ * insignia_decode.hpp of the reference) for callers that cannot include C++
+ * headers.  These DO allocate (at create) and DO synchronise where noted. */
+typedef struct insg_engine insg_engine;
+
+typedef struct insg_engine_options {
+    uint64_t device_budget_bytes; /* TieredStorage budget (src/storage.cu:6); 0 = 16 GiB        */
+    int max_context;              /* DecodeWorkspace ctx (src/decode.cu:10); 0 = 4096            */
+    int kv_dtype;                 /* INSG_KV_F32 (the reference's cache) or INSG_KV_BF16        */
+    int gate_elementwise;         /* 0: head-broadcast gate as the reference engine
+                                     (src/qwen_kernels.cu:36); 1: element-wise gate as its NumPy
+                                     tools (tools/reference_all_layers.py:13)                   */
+    int accurate_trig;            /* 0: fast intrinsics for RoPE as the reference; 1: sincosf   */
+    int use_graph;                /* 1: capture the token step in a CUDA graph                  */
+    int use_pdl;                  /* 1: programmatic dependent launch between kernels           */
+    int n_layers;                 /* 0 = 32                                                     */
+    int vocab;                    /* 0 = 248320 (rows of lm_head used for logits)               */
+    int device;                   /* CUDA device ordinal                                        */
+} insg_engine_options;
+
+INSG_API insg_engine *insg_engine_create(const char *index_path /* host, UTF-8 */, const insg_engine_options *opt);
+INSG_API void insg_engine_destroy(insg_engine *e);
+/* Qwen35Weights::embed into workspace.hidden (src/qwen35.cu:9, src/test_full_model.cu:6) */
+INSG_API int insg_engine_embed(insg_engine *e, int token);
+/* Qwen35Decode::layer (src/decode.cu:20) */
+INSG_API int insg_engine_layer(insg_engine *e, int layer);
+/* Qwen35Decode::forward_token (src/decode.cu:21): asynchronous */
+INSG_API int insg_engine_forward_token(insg_engine *e, int token);
+/* Qwen35Decode::logits_argmax (src/decode.cu:22): synchronises, returns the token id (>=0) */
+INSG_API int insg_engine_logits_argmax(insg_engine *e);
+/* Qwen35Decode::decode_token (src/decode.cu:23): synchronises, returns the token id (>=0) */
+INSG_API int insg_engine_decode_token(insg_engine *e, int token);
+/* Qwen35Decode::mtp_draft (src/decode.cu:24): synchronises, returns the draft token id */
+INSG_API int insg_engine_mtp_draft(insg_engine *e, int token);
+/* Greedy generation without a host round trip per token: feeds `first_token`, then each
+ * arg-max back in, `count` times; writes the `count` produced ids to out_tokens (host).
+ * Synchronises once at the end.  No reference counterpart (its loop is src/generate_ids.cu:4). */
+INSG_API int insg_engine_generate(insg_engine *e, int first_token, int count, int *out_tokens /* host */);
+INSG_API int insg_engine_position(insg_engine *e);
+INSG_API int insg_engine_set_position(insg_engine *e, int position);
+/* Re-zeroes the recurrent state and position (what constructing a fresh DecodeWorkspace does). */
+INSG_API int insg_engine_reset(insg_engine *e);
+/* Copies a workspace buffer to the host: "hidden", "logits", "delta_state", "conv_state", ... */
+INSG_API int insg_engine_read(insg_engine *e, const char *field, float *out /* host */, uint64_t count);
+/* Device pointer of a workspace buffer (for callers that post-process on the GPU). */
+INSG_API void *insg_engine_buffer(insg_engine *e, const char *field);
+INSG_API insg_stream_t insg_engine_stream(insg_engine *e);
+/* Kernel launches issued by the engine since creation (own kernels only). */
+INSG_API uint64_t insg_engine_launch_count(insg_engine *e);
+INSG_API uint64_t insg_engine_device_bytes(insg_engine *e);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INSIGNIA_B200_H */

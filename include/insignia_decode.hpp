@@ -1,0 +1,97 @@
+// Token loop of the Qwen3.5-style hybrid: per-sequence workspace + decode driver.
+//
+// Drop-in for the reference header of the same name (include/insignia_decode.hpp:5-24,
+// behaviour: src/decode.cu:9-69): same classes, public fields, methods and error
+// strings.  Underneath, each layer is five fused sm_100a kernels instead of
+// eighteen launches, chained with programmatic dependent launch and (for
+// forward_token / decode_token / generate) replayed from a CUDA graph.
+// Additive members are marked.
+#pragma once
+#include "insignia_qwen35.hpp"
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace insignia {
+
+// Additive knobs; the defaults reproduce the reference engine's behaviour.
+struct DecodeOptions {
+    bool kv_bf16 = false;          // false: fp32 KV cache as the reference (src/decode.cu:10); true: bf16 cache
+    bool gate_elementwise = false; // false: head-broadcast attention gate (src/qwen_kernels.cu:36);
+                                   // true: element-wise gate (tools/reference_all_layers.py:13)
+    bool accurate_trig = false;    // false: __powf/__sinf/__cosf for RoPE (src/ops.cu:9); true: powf/sincosf
+    bool use_graph = true;         // replay the token step from a CUDA graph
+    bool use_pdl = true;           // programmatic dependent launch between kernels
+    int n_layers = Qwen35Shape::layers;
+    int vocab = Qwen35Shape::vocab;
+};
+
+class INSIGNIA_API DecodeWorkspace final {
+public:
+    explicit DecodeWorkspace(int max_context = 4096, cudaStream_t stream = nullptr);
+    // Additive: options (KV cache element type).
+    DecodeWorkspace(int max_context, cudaStream_t stream, const DecodeOptions &options);
+    ~DecodeWorkspace();
+    DecodeWorkspace(const DecodeWorkspace &) = delete;
+
+    // Public device buffers, same names and extents as the reference (src/decode.cu:10).
+    // hidden[4096] is the residual stream; logits[248320]; delta_state[24][32][128][128];
+    // conv_state[24][8192][3]; kv_* [8][ctx][1024]; mtp_* [ctx][1024].  With a bf16 cache
+    // kv_*/mtp_* point at bf16 storage of the same element count.
+    float *hidden{}, *norm{}, *qkv{}, *attn_gate{}, *key{}, *value{}, *z{}, *a{}, *b{}, *core{}, *gate{}, *up{},
+        *down{}, *logits{}, *delta_state{}, *conv_state{}, *kv_keys{}, *kv_values{}, *mtp_keys{}, *mtp_values{};
+    int max_context{}, position{};
+    cudaStream_t stream{};
+
+    // Additive.
+    DecodeOptions options{};
+    int *d_token{};      // device: token fed to the embedding
+    int *d_position{};   // device: rotary position / cache row of the current token
+    int *d_next{};       // device: arg-max of the last logits
+    void *attn_scratch{};
+    void *argmax_scratch{};
+    void reset(); // zero recurrent state and position, as a fresh workspace
+
+private:
+    void allocate();
+};
+
+class INSIGNIA_API Qwen35Decode final {
+public:
+    Qwen35Decode(Qwen35Weights &weights, DecodeWorkspace &workspace);
+    ~Qwen35Decode();
+    void delta_layer(int layer);
+    void attention_layer(int layer);
+    void layer(int layer);
+    int decode_token(int token);
+    void forward_token(int token);
+    int logits_argmax();
+    int mtp_draft(int input_token);
+
+    // Additive: greedy generation with the arg-max fed back on the device; one sync at the end.
+    std::vector<int> generate(int first_token, int count);
+    uint64_t launch_count() const noexcept { return launches_; }
+    cudaStream_t execution_stream();
+    struct Plan; // resolved weight pointers + captured graph (opaque)
+
+private:
+    Plan &plan();
+    void sync_scalars(int token);
+    void enqueue_embed();
+    void enqueue_delta(int layer);
+    void enqueue_attention(int layer);
+    void enqueue_head();
+    void enqueue_token_step();
+    void replay_token_step();
+    Qwen35Weights &w_;
+    DecodeWorkspace &x_;
+    std::unique_ptr<Plan> plan_;
+    uint64_t launches_{};
+    bool fused_token_valid_{};
+};
+
+} // namespace insignia

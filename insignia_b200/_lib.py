@@ -1,0 +1,114 @@
+"""ctypes loader for ``libinsignia_b200.so`` (the C ABI in include/insignia_b200.h).
+
+There is no CPU fallback: if the library is missing or fails to load, importing
+this module's :func:`lib` raises, and every op built on it fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libinsignia_b200.so")
+_lib = None
+
+vp, i32, u64, sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t
+
+
+class GemvSegment(C.Structure):
+    _fields_ = [("packed", vp), ("packed2", vp), ("out", vp), ("rows", i32), ("epilogue", i32), ("conv_state", vp),
+                ("conv_w", vp), ("A_log", vp), ("dt_bias", vp)]
+
+
+class GemvOp(C.Structure):
+    _fields_ = [("in_", vp), ("aux", vp), ("norm_w", vp), ("x_out", vp), ("cols", i32), ("prologue", i32),
+                ("n_segments", i32), ("seg", GemvSegment * 4), ("argmax_scratch", vp), ("token_out", vp),
+                ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("pdl", i32)]
+
+
+class AttnOp(C.Structure):
+    _fields_ = [("qraw", vp), ("k_raw", vp), ("v", vp), ("q_norm_w", vp), ("k_norm_w", vp), ("k_cache", vp),
+                ("v_cache", vp), ("out", vp), ("position", vp), ("position_offset", i32), ("max_context", i32),
+                ("kv_dtype", i32), ("fast_trig", i32), ("scratch", vp), ("scratch_bytes", sz), ("pdl", i32)]
+
+
+class EngineOptions(C.Structure):
+    _fields_ = [("device_budget_bytes", u64), ("max_context", i32), ("kv_dtype", i32), ("gate_elementwise", i32),
+                ("accurate_trig", i32), ("use_graph", i32), ("use_pdl", i32), ("n_layers", i32), ("vocab", i32),
+                ("device", i32)]
+
+
+# name -> (restype, argtypes); every symbol include/insignia_b200.h declares
+SIGNATURES = {
+    "insg_last_error": (C.c_char_p, []),
+    "insg_version": (i32, []),
+    "insg_tune_set": (i32, [C.c_char_p, i32]),
+    "insg_mxfp4_gemv_mlx": (i32, [vp, vp, vp, vp, i32, i32, vp]),
+    "insg_mxfp4_get_row_mlx": (i32, [vp, vp, vp, i32, i32, vp]),
+    "insg_mxfp4_embed": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "insg_set_scalars": (i32, [vp, i32, vp, i32, vp]),
+    "insg_mxfp4_dequant_mlx": (i32, [vp, vp, vp, i32, i32, vp]),
+    "insg_mxfp4_packed_bytes": (sz, [i32, i32]),
+    "insg_mxfp4_repack": (i32, [vp, vp, vp, i32, i32, vp]),
+    "insg_mxfp4_gemv_packed": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "insg_gemv_argmax_scratch_bytes": (sz, []),
+    "insg_gemv_fused": (i32, [C.POINTER(GemvOp), vp]),
+    "insg_deltanet_decode": (i32, [vp] * 7 + [i32, vp]),
+    "insg_gqa_scratch_bytes": (sz, [i32]),
+    "insg_gqa_decode": (i32, [vp, vp, vp, vp, i32, i32, vp, sz, vp]),
+    "insg_attention_step": (i32, [C.POINTER(AttnOp), vp]),
+    "insg_rmsnorm_bf16": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "insg_rmsnorm_zero_centered": (i32, [vp, vp, vp, i32, i32, C.c_float, vp]),
+    "insg_causal_conv4_silu": (i32, [vp, vp, vp, i32, vp]),
+    "insg_deltanet_parameters": (i32, [vp, vp, vp, vp, i32, vp]),
+    "insg_qk_norm_rope": (i32, [vp, vp, vp, vp, i32, i32, vp]),
+    "insg_silu_mul": (i32, [vp, vp, vp, i32, vp]),
+    "insg_residual_add": (i32, [vp, vp, i32, vp]),
+    "insg_sigmoid_mul": (i32, [vp, vp, i32, vp]),
+    "insg_store_kv": (i32, [vp, vp, vp, vp, i32, i32, vp]),
+    "insg_split_q_gate": (i32, [vp, vp, vp, vp]),
+    "insg_expand_gate_heads": (i32, [vp, vp, vp]),
+    "insg_concat": (i32, [vp, vp, vp, i32, vp]),
+    "insg_argmax_logits": (i32, [vp, i32, vp, vp]),
+    "insg_bf16_gemv": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "insg_engine_create": (vp, [C.c_char_p, C.POINTER(EngineOptions)]),
+    "insg_engine_destroy": (None, [vp]),
+    "insg_engine_embed": (i32, [vp, i32]),
+    "insg_engine_layer": (i32, [vp, i32]),
+    "insg_engine_forward_token": (i32, [vp, i32]),
+    "insg_engine_logits_argmax": (i32, [vp]),
+    "insg_engine_decode_token": (i32, [vp, i32]),
+    "insg_engine_mtp_draft": (i32, [vp, i32]),
+    "insg_engine_generate": (i32, [vp, i32, i32, C.POINTER(i32)]),
+    "insg_engine_position": (i32, [vp]),
+    "insg_engine_set_position": (i32, [vp, i32]),
+    "insg_engine_reset": (i32, [vp]),
+    "insg_engine_read": (i32, [vp, C.c_char_p, vp, u64]),
+    "insg_engine_buffer": (vp, [vp, C.c_char_p]),
+    "insg_engine_stream": (vp, [vp]),
+    "insg_engine_launch_count": (u64, [vp]),
+    "insg_engine_device_bytes": (u64, [vp]),
+}
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m insignia_b200.build` (there is no CPU fallback)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+class InsigniaError(RuntimeError):
+    pass
+
+
+def check(rc: int) -> int:
+    if rc < 0:
+        raise InsigniaError(lib().insg_last_error().decode() or f"error {rc}")
+    return rc

@@ -1,0 +1,332 @@
+// Split-K flash-decode GQA for sm_100a: 16 query heads over 4 kv heads, head_dim 256.
+//
+// Math (reference: src/attention.cu:4): score_t = (q_h . K[t][h>>2]) / 16, softmax over
+// the cached tokens, out_h = sum_t p_t V[t][h>>2]; cache layout [token][4][256].
+//
+// The reference runs one CTA per query head, keeps every score in shared memory
+// (which fails past ~12K tokens) and re-reads each kv head's cache four times.
+// Here a CTA owns (kv head, token range): it streams its slab of K and V exactly
+// once for the four query heads that share the kv head, keeps an online softmax
+// per warp, and leaves (max, denominator, weighted V) partials in scratch; the
+// last CTA to finish for a kv head folds the partials in split order, so results
+// do not depend on scheduling.  The fused entry also does the per-head RMSNorm,
+// partial RoPE and the cache write of the current token (src/ops.cu:9,
+// src/qwen_kernels.cu:15,31) so one launch replaces five.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace insg {
+
+constexpr int kAtThreads = 256;
+constexpr int kAtWarps = 8;
+constexpr int kSplits = 37;                  // 4 kv heads x 37 = 148 CTAs
+constexpr int kMinChunk = 64;                // tokens per split at least
+constexpr int kPartFloats = 8 + 4 * 256;     // m[4], l[4], acc[4][256]
+
+struct AttnParams {
+    const float *q;        // plain: [16][256] normalised; fused: interleaved q_proj output [16][512]
+    const float *k_raw;    // fused only
+    const float *v_new;    // fused only
+    const uint16_t *q_w, *k_w;
+    void *kc, *vc;
+    float *out;
+    const int *position;   // fused: device scalar
+    int position_offset;
+    int tokens;            // plain
+    int max_context;
+    int fast_trig;
+    unsigned *counters;    // [4] at the head of scratch
+    float *partials;       // [4][kSplits][kPartFloats]
+};
+
+template <bool BF16> struct KvRow;
+template <> struct KvRow<false> {
+    static __device__ __forceinline__ void load(const void *base, size_t row_elems, int lane, float (&o)[8])
+    {
+        const float4 *p = reinterpret_cast<const float4 *>(static_cast<const float *>(base) + row_elems) + lane * 2;
+        const float4 a = p[0], b = p[1];
+        o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+    }
+    static __device__ __forceinline__ float round(float v) { return v; }
+    static __device__ __forceinline__ void store(void *base, size_t idx, float v) { static_cast<float *>(base)[idx] = v; }
+};
+template <> struct KvRow<true> {
+    static __device__ __forceinline__ void load(const void *base, size_t row_elems, int lane, float (&o)[8])
+    {
+        const uint4 r = *(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + row_elems) + lane);
+        o[0] = __uint_as_float(r.x << 16); o[1] = __uint_as_float(r.x & 0xffff0000u);
+        o[2] = __uint_as_float(r.y << 16); o[3] = __uint_as_float(r.y & 0xffff0000u);
+        o[4] = __uint_as_float(r.z << 16); o[5] = __uint_as_float(r.z & 0xffff0000u);
+        o[6] = __uint_as_float(r.w << 16); o[7] = __uint_as_float(r.w & 0xffff0000u);
+    }
+    static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    static __device__ __forceinline__ void store(void *base, size_t idx, float v)
+    {
+        static_cast<__nv_bfloat16 *>(base)[idx] = __float2bfloat16_rn(v);
+    }
+};
+
+// RMSNorm over 256 (one warp, 8 values per lane, dims lane*8..+7) then rotate-half
+// RoPE on dims 0..63 (lanes 0..7; the partner dim i+-32 lives 4 lanes away).
+__device__ __forceinline__ void norm_rope_256(float (&v)[8], const uint16_t *w, int lane, int pos, bool fast)
+{
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) ss = fmaf(v[j], v[j], ss);
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / 256.f + 1e-6f);
+    const uint4 wv = reinterpret_cast<const uint4 *>(w)[lane];
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const float wf = bf16_bits_to_float((j & 1) ? (ww[j >> 1] >> 16) : (ww[j >> 1] & 0xffff));
+        v[j] *= inv * wf;
+    }
+    if (pos != 0) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], 4);
+            if (lane < 8) {
+                const int i = lane * 8 + j, half = i & 31;
+                float c, s;
+                if (fast) {
+                    const float a = float(pos) * __powf(10000000.0f, -float(2 * half) / 64.0f);
+                    c = __cosf(a);
+                    s = __sinf(a);
+                } else {
+                    const float a = float(pos) * powf(10000000.0f, -float(2 * half) / 64.0f);
+                    sincosf(a, &s, &c);
+                }
+                v[j] = v[j] * c + (i < 32 ? -other : other) * s;
+            }
+        }
+    }
+}
+
+template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) attn_splitk_kernel(const __grid_constant__ AttnParams p)
+{
+    using Row = KvRow<BF16>;
+    __shared__ __align__(16) float s_q[4][256];
+    __shared__ __align__(16) float s_knew[256], s_vnew[256];
+    __shared__ float s_m[kAtWarps][4], s_l[kAtWarps][4];
+    __shared__ __align__(16) float s_acc[kAtWarps][4][256];
+    __shared__ int s_last;
+
+    const int kvh = blockIdx.x / kSplits, split = blockIdx.x % kSplits;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    int tokens = p.tokens, pos = -1;
+    if constexpr (FUSED) {
+        pos = *p.position + p.position_offset;
+        tokens = pos + 1;
+    }
+    if (tokens > p.max_context) tokens = p.max_context; // host checks; never index past the cache
+    const int chunk = max(kMinChunk, (tokens + kSplits - 1) / kSplits);
+    const int nsplit = (tokens + chunk - 1) / chunk;
+    const int t0 = split * chunk, t1 = min(tokens, t0 + chunk);
+    const bool has_work = t0 < tokens;
+
+    if (has_work) {
+        // ---- query (and current key) preparation --------------------------------
+        if constexpr (FUSED) {
+            if (warp < 4) {
+                float v[8];
+                const float *src = p.q + size_t(kvh * 4 + warp) * 512 + lane * 8;
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = src[j];
+                norm_rope_256(v, p.q_w, lane, pos, p.fast_trig != 0);
+#pragma unroll
+                for (int j = 0; j < 8; j++) s_q[warp][lane * 8 + j] = v[j];
+            } else if (warp == 4 && pos >= t0 && pos < t1) {
+                float v[8];
+                const float *src = p.k_raw + kvh * 256 + lane * 8;
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = src[j];
+                norm_rope_256(v, p.k_w, lane, pos, p.fast_trig != 0);
+                const size_t row = (size_t(pos) * 4 + kvh) * 256 + lane * 8;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    Row::store(p.kc, row + j, v[j]);
+                    s_knew[lane * 8 + j] = Row::round(v[j]);
+                }
+            } else if (warp == 5 && pos >= t0 && pos < t1) {
+                const size_t row = (size_t(pos) * 4 + kvh) * 256 + lane * 8;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float v = p.v_new[kvh * 256 + lane * 8 + j];
+                    Row::store(p.vc, row + j, v);
+                    s_vnew[lane * 8 + j] = Row::round(v);
+                }
+            }
+        } else {
+            for (int i = tid; i < 1024; i += kAtThreads) s_q[i >> 8][i & 255] = p.q[size_t(kvh) * 1024 + i];
+        }
+    }
+    __syncthreads();
+
+    if (has_work) {
+        float q[4][8];
+#pragma unroll
+        for (int h = 0; h < 4; h++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) q[h][j] = s_q[h][lane * 8 + j] * 0.0625f;
+
+        float m[4], l[4], acc[4][8];
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            m[h] = -3.0e38f;
+            l[h] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[h][j] = 0.f;
+        }
+        for (int t = t0 + warp; t < t1; t += kAtWarps) {
+            float kk[8], vv[8];
+            if (FUSED && t == pos) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) { kk[j] = s_knew[lane * 8 + j]; vv[j] = s_vnew[lane * 8 + j]; }
+            } else {
+                const size_t row = (size_t(t) * 4 + kvh) * 256;
+                Row::load(p.kc, row, lane, kk);
+                Row::load(p.vc, row, lane, vv);
+            }
+            float s[4];
+#pragma unroll
+            for (int h = 0; h < 4; h++) {
+                float z = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) z = fmaf(q[h][j], kk[j], z);
+                s[h] = z;
+            }
+#pragma unroll
+            for (int mk = 16; mk; mk >>= 1) {
+#pragma unroll
+                for (int h = 0; h < 4; h++) s[h] += __shfl_xor_sync(0xffffffffu, s[h], mk);
+            }
+#pragma unroll
+            for (int h = 0; h < 4; h++) {
+                const float mn = fmaxf(m[h], s[h]);
+                const float corr = __expf(m[h] - mn), pr = __expf(s[h] - mn);
+                m[h] = mn;
+                l[h] = fmaf(l[h], corr, pr);
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[h][j] = fmaf(acc[h][j], corr, pr * vv[j]);
+            }
+        }
+        // ---- fold the 8 warps --------------------------------------------------------
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            if (lane == 0) { s_m[warp][h] = m[h]; s_l[warp][h] = l[h]; }
+#pragma unroll
+            for (int j = 0; j < 8; j++) s_acc[warp][h][lane * 8 + j] = acc[h][j];
+        }
+    }
+    __syncthreads();
+    float *part = p.partials + size_t(kvh * kSplits + split) * kPartFloats;
+    if (has_work) {
+        const int d = tid;
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            float mg = s_m[0][h];
+#pragma unroll
+            for (int w = 1; w < kAtWarps; w++) mg = fmaxf(mg, s_m[w][h]);
+            float lg = 0.f, a = 0.f;
+#pragma unroll
+            for (int w = 0; w < kAtWarps; w++) {
+                const float e = __expf(s_m[w][h] - mg); // warps without tokens carry m=-3e38, l=0, acc=0
+                lg = fmaf(s_l[w][h], e, lg);
+                a = fmaf(s_acc[w][h][d], e, a);
+            }
+            part[8 + h * 256 + d] = a;
+            if (d == 0) { part[h] = mg; part[4 + h] = lg; }
+        }
+    }
+    // ---- last CTA of this kv head folds the splits -----------------------------------
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned ticket = atomicAdd(p.counters + kvh, 1u);
+        s_last = (ticket == kSplits - 1);
+    }
+    __syncthreads();
+    if (s_last) {
+        __threadfence();
+        const volatile float *pp = p.partials + size_t(kvh * kSplits) * kPartFloats;
+        const int d = tid;
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            float mg = -3.0e38f;
+            for (int s = 0; s < nsplit; s++) mg = fmaxf(mg, pp[size_t(s) * kPartFloats + h]);
+            float lg = 0.f, a = 0.f;
+            for (int s = 0; s < nsplit; s++) {
+                const float e = __expf(pp[size_t(s) * kPartFloats + h] - mg);
+                lg = fmaf(pp[size_t(s) * kPartFloats + 4 + h], e, lg);
+                a = fmaf(pp[size_t(s) * kPartFloats + 8 + h * 256 + d], e, a);
+            }
+            p.out[size_t(kvh * 4 + h) * 256 + d] = a / lg;
+        }
+        if (tid == 0) p.counters[kvh] = 0u;
+    }
+}
+
+template <bool BF16, bool FUSED> int launch_attn(const AttnParams &p, cudaStream_t st, bool pdl)
+{
+    return launch(attn_splitk_kernel<BF16, FUSED>, dim3(4 * kSplits), dim3(kAtThreads), 0, st, pdl, p);
+}
+
+size_t attn_scratch_bytes() { return 64 + size_t(4) * kSplits * kPartFloats * sizeof(float); }
+
+int attn_plain_launch(const float *q, const void *kc, const void *vc, float *out, int tokens, int kv_dtype, void *scratch,
+                      cudaStream_t st)
+{
+    AttnParams p = {};
+    p.q = q; p.kc = const_cast<void *>(kc); p.vc = const_cast<void *>(vc); p.out = out;
+    p.tokens = tokens; p.max_context = tokens;
+    p.counters = static_cast<unsigned *>(scratch);
+    p.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + 64);
+    return kv_dtype == INSG_KV_BF16 ? launch_attn<true, false>(p, st, false) : launch_attn<false, false>(p, st, false);
+}
+
+} // namespace insg
+
+using namespace insg;
+
+extern "C" {
+
+size_t insg_gqa_scratch_bytes(int tokens)
+{
+    (void)tokens; // the split count is fixed, so the scratch does not grow with the context
+    return attn_scratch_bytes();
+}
+
+int insg_gqa_decode(const float *q, const void *k_cache, const void *v_cache, float *out, int tokens, int kv_dtype,
+                    void *scratch, size_t scratch_bytes, insg_stream_t stream)
+{
+    if (tokens <= 0) return INSG_OK; // src/attention.cu:5 returns silently
+    if (!q || !k_cache || !v_cache || !out || !scratch) return fail(INSG_E_ARG, "gqa_decode: null pointer");
+    if (kv_dtype != INSG_KV_F32 && kv_dtype != INSG_KV_BF16) return fail(INSG_E_ARG, "gqa_decode: bad kv dtype");
+    if (scratch_bytes < attn_scratch_bytes()) return fail(INSG_E_SHAPE, "gqa_decode: scratch too small");
+    return attn_plain_launch(q, k_cache, v_cache, out, tokens, kv_dtype, scratch, stream);
+}
+
+int insg_attention_step(const insg_attn_op *op, insg_stream_t stream)
+{
+    if (!op || !op->qraw || !op->k_raw || !op->v || !op->q_norm_w || !op->k_norm_w || !op->k_cache || !op->v_cache ||
+        !op->out || !op->position || !op->scratch)
+        return fail(INSG_E_ARG, "attention_step: null pointer");
+    if (op->scratch_bytes < attn_scratch_bytes()) return fail(INSG_E_SHAPE, "attention_step: scratch too small");
+    if (op->max_context <= 0) return fail(INSG_E_SHAPE, "attention_step: max_context");
+    AttnParams p = {};
+    p.q = op->qraw; p.k_raw = op->k_raw; p.v_new = op->v; p.q_w = op->q_norm_w; p.k_w = op->k_norm_w;
+    p.kc = op->k_cache; p.vc = op->v_cache; p.out = op->out;
+    p.position = op->position; p.position_offset = op->position_offset;
+    p.max_context = op->max_context; p.fast_trig = op->fast_trig;
+    p.counters = static_cast<unsigned *>(op->scratch);
+    p.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(op->scratch) + 64);
+    const bool pdl = op->pdl != 0;
+    return op->kv_dtype == INSG_KV_BF16 ? launch_attn<true, true>(p, stream, pdl) : launch_attn<false, true>(p, stream, pdl);
+}
+
+} // extern "C"

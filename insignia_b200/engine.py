@@ -1,0 +1,99 @@
+"""Python mirror of the reference's decode classes over the C ABI's engine handle.
+
+``Engine`` bundles what the reference's drivers build by hand (src/test_generate.cu:3):
+``ModelFile`` -> ``Qwen35Weights`` -> ``DecodeWorkspace`` -> ``Qwen35Decode``, with the
+same method names (``embed``, ``layer``, ``forward_token``, ``logits_argmax``,
+``decode_token``, ``mtp_draft``) and the same errors, surfaced as ``InsigniaError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import EngineOptions, InsigniaError, check
+
+FIELD_SIZES = {"hidden": 4096, "norm": 4096, "qkv": 8192, "core": 4096, "z": 4096, "a": 32, "b": 32, "gate": 12288,
+               "key": 1024, "value": 1024, "down": 4096, "logits": 248320, "delta_state": 24 * 32 * 128 * 128,
+               "conv_state": 24 * 8192 * 3}
+
+
+class Engine:
+    def __init__(self, index_path: str, max_context: int = 4096, budget_bytes: int = 16 << 30, kv_bf16: bool = False,
+                 gate_elementwise: bool = False, accurate_trig: bool = False, use_graph: bool = True,
+                 use_pdl: bool = True, n_layers: int = 32, vocab: int = 248320, device: int = 0):
+        o = EngineOptions(budget_bytes, max_context, int(kv_bf16), int(gate_elementwise), int(accurate_trig),
+                          int(use_graph), int(use_pdl), n_layers, vocab, device)
+        self.vocab = vocab
+        self._h = _lib.lib().insg_engine_create(index_path.encode(), C.byref(o))
+        if not self._h:
+            raise InsigniaError(_lib.lib().insg_last_error().decode())
+
+    def close(self):
+        if getattr(self, "_h", None):
+            _lib.lib().insg_engine_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def embed(self, token: int):
+        check(_lib.lib().insg_engine_embed(self._h, token))
+
+    def layer(self, layer: int):
+        check(_lib.lib().insg_engine_layer(self._h, layer))
+
+    def forward_token(self, token: int):
+        check(_lib.lib().insg_engine_forward_token(self._h, token))
+
+    def logits_argmax(self) -> int:
+        return check(_lib.lib().insg_engine_logits_argmax(self._h))
+
+    def decode_token(self, token: int) -> int:
+        return check(_lib.lib().insg_engine_decode_token(self._h, token))
+
+    def mtp_draft(self, token: int) -> int:
+        return check(_lib.lib().insg_engine_mtp_draft(self._h, token))
+
+    def generate(self, first_token: int, count: int) -> list[int]:
+        buf = (C.c_int * count)()
+        check(_lib.lib().insg_engine_generate(self._h, first_token, count, buf))
+        return list(buf)
+
+    @property
+    def position(self) -> int:
+        return _lib.lib().insg_engine_position(self._h)
+
+    @position.setter
+    def position(self, p: int):
+        check(_lib.lib().insg_engine_set_position(self._h, p))
+
+    def reset(self):
+        check(_lib.lib().insg_engine_reset(self._h))
+
+    def read(self, field: str, count: int | None = None) -> np.ndarray:
+        n = count if count is not None else (self.vocab if field == "logits" else FIELD_SIZES[field])
+        out = np.empty(n, np.float32)
+        check(_lib.lib().insg_engine_read(self._h, field.encode(), out.ctypes.data, n))
+        return out
+
+    def buffer(self, field: str) -> int:
+        return _lib.lib().insg_engine_buffer(self._h, field.encode())
+
+    @property
+    def stream(self) -> int:
+        return _lib.lib().insg_engine_stream(self._h) or 0
+
+    @property
+    def launch_count(self) -> int:
+        return _lib.lib().insg_engine_launch_count(self._h)
+
+    @property
+    def device_bytes(self) -> int:
+        return _lib.lib().insg_engine_device_bytes(self._h)

@@ -1,0 +1,598 @@
+// insignia::DecodeWorkspace / insignia::Qwen35Decode on the fused sm_100a kernels
+// (interface: include/insignia_decode.hpp; reference behaviour: src/decode.cu:9-69).
+//
+// Kernel sequence per token (reference: 18 launches per layer, ~580 per token):
+//   embed                                                       1
+//   DeltaNet layer : in_proj(qkv|z|a|b) + conv/SiLU/gates, delta step, out_proj+residual,
+//                    gate/up + SwiGLU, down + residual           5
+//   attention layer: q|k|v proj, norm/RoPE/KV store/split-K attention, o_proj(gated)+residual,
+//                    gate/up + SwiGLU, down + residual           5
+//   final norm + lm_head + arg-max                               1
+// = 162 launches, replayed from one CUDA graph with programmatic dependent launch edges.
+#include "insignia_decode.hpp"
+
+#include "insignia_b200.h"
+
+#include <stdexcept>
+
+namespace insignia {
+namespace {
+
+constexpr int kHidden = Qwen35Shape::hidden, kInter = Qwen35Shape::intermediate;
+const char *const kLM = "language_model";
+
+void cuda_check(cudaError_t e, const char *what)
+{
+    if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+void insg_check(int rc)
+{
+    if (rc != INSG_OK) throw std::runtime_error(insg_last_error());
+}
+template <class T> void dev_alloc(T **p, size_t count)
+{
+    cuda_check(cudaMalloc(reinterpret_cast<void **>(p), count * sizeof(T)), "cudaMalloc workspace");
+}
+
+} // namespace
+
+// --------------------------------------------------------------- workspace
+DecodeWorkspace::DecodeWorkspace(int ctx, cudaStream_t s) : max_context(ctx), stream(s) { allocate(); }
+
+DecodeWorkspace::DecodeWorkspace(int ctx, cudaStream_t s, const DecodeOptions &o) : max_context(ctx), stream(s), options(o)
+{
+    allocate();
+}
+
+void DecodeWorkspace::allocate()
+{
+    if (max_context <= 0) throw std::runtime_error("max_context must be positive");
+    const size_t kv_scale = options.kv_bf16 ? 2 : 1; // element counts below are in floats
+    dev_alloc(&hidden, 4096);
+    dev_alloc(&norm, 4096);
+    dev_alloc(&qkv, 8192);
+    dev_alloc(&attn_gate, 4096);
+    dev_alloc(&key, 1024);
+    dev_alloc(&value, 1024);
+    dev_alloc(&z, 4096);
+    dev_alloc(&a, 32);
+    dev_alloc(&b, 32);
+    dev_alloc(&core, 4096);
+    dev_alloc(&gate, 12288);
+    dev_alloc(&up, 12288);
+    dev_alloc(&down, 4096);
+    dev_alloc(&logits, size_t(Qwen35Shape::vocab));
+    dev_alloc(&delta_state, size_t(24) * 32 * 128 * 128);
+    dev_alloc(&conv_state, size_t(24) * 8192 * 3);
+    const size_t kv_floats = (size_t(8) * max_context * 1024 + kv_scale - 1) / kv_scale;
+    const size_t mtp_floats = (size_t(max_context) * 1024 + kv_scale - 1) / kv_scale;
+    dev_alloc(&kv_keys, kv_floats);
+    dev_alloc(&kv_values, kv_floats);
+    dev_alloc(&mtp_keys, mtp_floats);
+    dev_alloc(&mtp_values, mtp_floats);
+    dev_alloc(&d_token, 4 + size_t(max_context) + 1); // token, position, next, pad, then the token log
+    d_position = d_token + 1;
+    d_next = d_token + 2;
+    cuda_check(cudaMalloc(&attn_scratch, insg_gqa_scratch_bytes(max_context)), "cudaMalloc attention scratch");
+    cuda_check(cudaMalloc(&argmax_scratch, insg_gemv_argmax_scratch_bytes()), "cudaMalloc arg-max scratch");
+    cuda_check(cudaMemsetAsync(attn_scratch, 0, 64, stream), "memset");
+    cuda_check(cudaMemsetAsync(argmax_scratch, 0, 64, stream), "memset");
+    cuda_check(cudaMemsetAsync(d_token, 0, (4 + size_t(max_context) + 1) * sizeof(int), stream), "memset");
+    // The reference leaves the KV caches uninitialised (src/decode.cu:10); rows are always written before they are read.
+    reset();
+}
+
+void DecodeWorkspace::reset()
+{
+    cuda_check(cudaMemsetAsync(delta_state, 0, size_t(24) * 32 * 128 * 128 * 4, stream), "memset delta state");
+    cuda_check(cudaMemsetAsync(conv_state, 0, size_t(24) * 8192 * 3 * 4, stream), "memset conv state");
+    position = 0;
+}
+
+DecodeWorkspace::~DecodeWorkspace()
+{
+    for (void *p : {(void *)hidden, (void *)norm, (void *)qkv, (void *)attn_gate, (void *)key, (void *)value, (void *)z, (void *)a,
+                    (void *)b, (void *)core, (void *)gate, (void *)up, (void *)down, (void *)logits, (void *)delta_state,
+                    (void *)conv_state, (void *)kv_keys, (void *)kv_values, (void *)mtp_keys, (void *)mtp_values, (void *)d_token,
+                    attn_scratch, argmax_scratch})
+        cudaFree(p);
+}
+
+// --------------------------------------------------------------------- plan
+struct Qwen35Decode::Plan {
+    struct Block { // weights of one decoder block
+        bool ready = false, attention = false;
+        const uint16_t *in_norm{}, *post_norm{};
+        PackedMatrix qkv, z, a, b, out;               // DeltaNet
+        const uint16_t *conv_w{}, *dt_bias{}, *dn_norm{};
+        const float *A_log{};
+        PackedMatrix q, k, v, o;                      // attention
+        const uint16_t *q_norm{}, *k_norm{};
+        PackedMatrix gate, up, down;                  // MLP
+    };
+    std::vector<Block> layers;
+    Block mtp;
+    bool head_ready = false, embed_ready = false, mtp_ready = false;
+    const uint16_t *final_norm{};
+    PackedMatrix lm_head;
+    QuantMatrix embed;
+    const uint16_t *mtp_fc{}, *mtp_norm_e{}, *mtp_norm_h{}, *mtp_norm{};
+    std::vector<std::string> pinned;      // tensors held for the lifetime of the plan
+    std::vector<std::string> pinned_mats; // matrices held (embed_tokens)
+    cudaStream_t stream{};
+    bool own_stream = false;
+    cudaGraph_t graph{};
+    cudaGraphExec_t exec{};
+    uint64_t graph_nodes = 0;
+    bool capturing = false;
+};
+
+Qwen35Decode::Qwen35Decode(Qwen35Weights &weights, DecodeWorkspace &workspace) : w_(weights), x_(workspace) {}
+
+Qwen35Decode::~Qwen35Decode()
+{
+    if (!plan_) return;
+    Plan &p = *plan_;
+    cudaStreamSynchronize(p.stream);
+    if (p.exec) cudaGraphExecDestroy(p.exec);
+    if (p.graph) cudaGraphDestroy(p.graph);
+    for (const std::string &n : p.pinned) w_.storage().release(n);
+    for (const std::string &n : p.pinned_mats) w_.release(n);
+    if (p.own_stream) cudaStreamDestroy(p.stream);
+}
+
+Qwen35Decode::Plan &Qwen35Decode::plan()
+{
+    if (!plan_) {
+        plan_ = std::make_unique<Plan>();
+        plan_->layers.resize(Qwen35Shape::layers);
+        if (x_.stream) {
+            plan_->stream = x_.stream;
+        } else {
+            // The legacy default stream cannot be captured into a graph.  A blocking stream keeps the
+            // ordering a default-stream caller expects (it synchronises with the legacy stream both ways).
+            cuda_check(cudaStreamCreateWithFlags(&plan_->stream, cudaStreamDefault), "cudaStreamCreate");
+            plan_->own_stream = true;
+        }
+    }
+    return *plan_;
+}
+
+namespace {
+struct Loader {
+    Qwen35Weights &w;
+    std::vector<std::string> &pinned;
+    const void *small(const std::string &name, DType want, uint64_t min_bytes)
+    {
+        DeviceView v = w.storage().acquire(name);
+        pinned.push_back(name);
+        if (v.dtype != want || v.bytes < min_bytes) throw std::runtime_error("unexpected dtype or size: " + name);
+        return v.data;
+    }
+    const uint16_t *bf16(const std::string &name, uint64_t n) { return static_cast<const uint16_t *>(small(name, DType::bf16, n * 2)); }
+    PackedMatrix mat(const std::string &base, int rows, int cols)
+    {
+        PackedMatrix m = w.packed(base);
+        if (m.rows != rows || m.cols != cols) throw std::runtime_error("unexpected matrix shape: " + base);
+        return m;
+    }
+};
+} // namespace
+
+// --------------------------------------------------------------- enqueue helpers
+namespace {
+struct Ctx {
+    DecodeWorkspace &x;
+    cudaStream_t st;
+    bool pdl;
+    uint64_t &launches;
+};
+
+void run_gemv(Ctx &c, insg_gemv_op &op)
+{
+    op.pdl = c.pdl ? 1 : 0;
+    insg_check(insg_gemv_fused(&op, c.st));
+    c.launches++;
+}
+
+insg_gemv_segment seg(const PackedMatrix &m, float *out, int epilogue)
+{
+    insg_gemv_segment s = {};
+    s.packed = m.data;
+    s.out = out;
+    s.rows = m.rows;
+    s.epilogue = epilogue;
+    return s;
+}
+} // namespace
+
+// The three kernels shared by both block types: post-norm + gate/up + SwiGLU, down + residual.
+static void enqueue_mlp_block(Ctx &c, const Qwen35Decode::Plan::Block &b)
+{
+    insg_gemv_op op = {};
+    op.in = c.x.hidden;
+    op.norm_w = b.post_norm;
+    op.x_out = c.x.norm;
+    op.cols = kHidden;
+    op.prologue = INSG_PRO_RMSNORM;
+    op.n_segments = 1;
+    op.seg[0] = seg(b.gate, c.x.gate, INSG_EPI_SWIGLU);
+    op.seg[0].packed2 = b.up.data;
+    run_gemv(c, op);
+
+    insg_gemv_op dn = {};
+    dn.in = c.x.gate;
+    dn.cols = kInter;
+    dn.prologue = INSG_PRO_PLAIN;
+    dn.n_segments = 1;
+    dn.seg[0] = seg(b.down, c.x.hidden, INSG_EPI_RESIDUAL);
+    run_gemv(c, dn);
+}
+
+static void enqueue_delta_block(Ctx &c, const Qwen35Decode::Plan::Block &b, int di)
+{
+    DecodeWorkspace &x = c.x;
+    insg_gemv_op in = {};
+    in.in = x.hidden;
+    in.norm_w = b.in_norm;
+    in.x_out = x.norm;
+    in.cols = kHidden;
+    in.prologue = INSG_PRO_RMSNORM;
+    in.n_segments = 4;
+    in.seg[0] = seg(b.qkv, x.qkv, INSG_EPI_CONV_SILU);
+    in.seg[0].conv_state = x.conv_state + size_t(di) * 8192 * 3;
+    in.seg[0].conv_w = b.conv_w;
+    in.seg[1] = seg(b.z, x.z, INSG_EPI_STORE);
+    in.seg[2] = seg(b.a, x.a, INSG_EPI_DECAY);
+    in.seg[2].A_log = b.A_log;
+    in.seg[2].dt_bias = b.dt_bias;
+    in.seg[3] = seg(b.b, x.b, INSG_EPI_BETA);
+    run_gemv(c, in);
+
+    insg_check(insg_deltanet_decode(x.delta_state + size_t(di) * 32 * 128 * 128, x.qkv, x.qkv + 2048, x.qkv + 4096, x.a, x.b, x.core,
+                                    c.pdl ? 1 : 0, c.st));
+    c.launches++;
+
+    insg_gemv_op out = {};
+    out.in = x.core;
+    out.aux = x.z;
+    out.norm_w = b.dn_norm;
+    out.cols = 4096;
+    out.prologue = INSG_PRO_GATED_RMSNORM;
+    out.n_segments = 1;
+    out.seg[0] = seg(b.out, x.hidden, INSG_EPI_RESIDUAL);
+    run_gemv(c, out);
+
+    enqueue_mlp_block(c, b);
+}
+
+static void enqueue_attention_block(Ctx &c, const Qwen35Decode::Plan::Block &b, void *kc, void *vc, int position_offset)
+{
+    DecodeWorkspace &x = c.x;
+    insg_gemv_op in = {};
+    in.in = x.hidden;
+    in.norm_w = b.in_norm;
+    in.x_out = x.norm;
+    in.cols = kHidden;
+    in.prologue = INSG_PRO_RMSNORM;
+    in.n_segments = 3;
+    in.seg[0] = seg(b.q, x.gate, INSG_EPI_STORE); // interleaved [16][q256|gate256], as the reference (src/decode.cu:19)
+    in.seg[1] = seg(b.k, x.key, INSG_EPI_STORE);
+    in.seg[2] = seg(b.v, x.value, INSG_EPI_STORE);
+    run_gemv(c, in);
+
+    insg_attn_op at = {};
+    at.qraw = x.gate;
+    at.k_raw = x.key;
+    at.v = x.value;
+    at.q_norm_w = b.q_norm;
+    at.k_norm_w = b.k_norm;
+    at.k_cache = kc;
+    at.v_cache = vc;
+    at.out = x.core;
+    at.position = x.d_position;
+    at.position_offset = position_offset;
+    at.max_context = x.max_context;
+    at.kv_dtype = x.options.kv_bf16 ? INSG_KV_BF16 : INSG_KV_F32;
+    at.fast_trig = x.options.accurate_trig ? 0 : 1;
+    at.scratch = x.attn_scratch;
+    at.scratch_bytes = insg_gqa_scratch_bytes(x.max_context);
+    at.pdl = c.pdl ? 1 : 0;
+    insg_check(insg_attention_step(&at, c.st));
+    c.launches++;
+
+    insg_gemv_op o = {};
+    o.in = x.core;
+    o.aux = x.gate;
+    o.cols = 4096;
+    o.prologue = x.options.gate_elementwise ? INSG_PRO_SIGMOID_GATE_QPROJ : INSG_PRO_SIGMOID_GATE_HEAD0;
+    o.n_segments = 1;
+    o.seg[0] = seg(b.o, x.hidden, INSG_EPI_RESIDUAL);
+    run_gemv(c, o);
+
+    enqueue_mlp_block(c, b);
+}
+
+static void load_mlp(Loader &L, const std::string &p, Qwen35Decode::Plan::Block &b)
+{
+    b.post_norm = L.bf16(p + ".post_attention_layernorm.weight", kHidden);
+    b.gate = L.mat(p + ".mlp.gate_proj", kInter, kHidden);
+    b.up = L.mat(p + ".mlp.up_proj", kInter, kHidden);
+    b.down = L.mat(p + ".mlp.down_proj", kHidden, kInter);
+}
+
+static void load_attention(Loader &L, const std::string &p, Qwen35Decode::Plan::Block &b)
+{
+    const std::string a = p + ".self_attn";
+    b.attention = true;
+    b.in_norm = L.bf16(p + ".input_layernorm.weight", kHidden);
+    b.q = L.mat(a + ".q_proj", 8192, kHidden);
+    b.k = L.mat(a + ".k_proj", 1024, kHidden);
+    b.v = L.mat(a + ".v_proj", 1024, kHidden);
+    b.o = L.mat(a + ".o_proj", kHidden, 4096);
+    b.q_norm = L.bf16(a + ".q_norm.weight", 256);
+    b.k_norm = L.bf16(a + ".k_norm.weight", 256);
+    load_mlp(L, p, b);
+    b.ready = true;
+}
+
+static void load_delta(Loader &L, const std::string &p, Qwen35Decode::Plan::Block &b)
+{
+    const std::string a = p + ".linear_attn";
+    b.attention = false;
+    b.in_norm = L.bf16(p + ".input_layernorm.weight", kHidden);
+    b.qkv = L.mat(a + ".in_proj_qkv", 8192, kHidden);
+    b.z = L.mat(a + ".in_proj_z", 4096, kHidden);
+    b.a = L.mat(a + ".in_proj_a", 32, kHidden);
+    b.b = L.mat(a + ".in_proj_b", 32, kHidden);
+    b.conv_w = L.bf16(a + ".conv1d.weight", 8192 * 4);
+    b.A_log = static_cast<const float *>(L.small(a + ".A_log", DType::f32, 32 * 4));
+    b.dt_bias = L.bf16(a + ".dt_bias", 32);
+    b.dn_norm = L.bf16(a + ".norm.weight", 128);
+    b.out = L.mat(a + ".out_proj", kHidden, 4096);
+    load_mlp(L, p, b);
+    b.ready = true;
+}
+
+// ------------------------------------------------------------------ public API
+void Qwen35Decode::sync_scalars(int token)
+{
+    Plan &p = plan();
+    insg_check(insg_set_scalars(token >= 0 ? x_.d_token : nullptr, token, x_.d_position, x_.position, p.stream));
+    launches_++;
+}
+
+void Qwen35Decode::enqueue_embed()
+{
+    Plan &p = plan();
+    if (!p.embed_ready) {
+        const std::string base = std::string(kLM) + ".model.embed_tokens";
+        p.embed = w_.matrix(base);
+        p.pinned_mats.push_back(base);
+        if (p.embed.cols != kHidden) throw std::runtime_error("unexpected matrix shape: " + base);
+        p.embed_ready = true;
+    }
+    insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
+                                x_.hidden, x_.d_token, p.embed.rows, kHidden, x_.options.use_pdl ? 1 : 0, p.stream));
+    launches_++;
+}
+
+void Qwen35Decode::enqueue_delta(int l)
+{
+    Plan &p = plan();
+    Plan::Block &b = p.layers[l];
+    if (!b.ready) {
+        Loader L{w_, p.pinned};
+        load_delta(L, std::string(kLM) + ".model.layers." + std::to_string(l), b);
+    }
+    Ctx c{x_, p.stream, x_.options.use_pdl, launches_};
+    enqueue_delta_block(c, b, l - l / 4);
+}
+
+void Qwen35Decode::enqueue_attention(int l)
+{
+    Plan &p = plan();
+    Plan::Block &b = p.layers[l];
+    if (!b.ready) {
+        Loader L{w_, p.pinned};
+        load_attention(L, std::string(kLM) + ".model.layers." + std::to_string(l), b);
+    }
+    const size_t esz = x_.options.kv_bf16 ? 2 : 4;
+    const size_t off = size_t(l / 4) * x_.max_context * 1024 * esz;
+    Ctx c{x_, p.stream, x_.options.use_pdl, launches_};
+    enqueue_attention_block(c, b, reinterpret_cast<uint8_t *>(x_.kv_keys) + off, reinterpret_cast<uint8_t *>(x_.kv_values) + off, 0);
+}
+
+void Qwen35Decode::enqueue_head()
+{
+    Plan &p = plan();
+    if (!p.head_ready) {
+        Loader L{w_, p.pinned};
+        p.final_norm = L.bf16(std::string(kLM) + ".model.norm.weight", kHidden);
+        p.lm_head = w_.packed(std::string(kLM) + ".lm_head");
+        if (p.lm_head.cols != kHidden || p.lm_head.rows < x_.options.vocab) throw std::runtime_error("unexpected matrix shape: language_model.lm_head");
+        p.head_ready = true;
+    }
+    Ctx c{x_, p.stream, x_.options.use_pdl, launches_};
+    insg_gemv_op op = {};
+    op.in = x_.hidden;
+    op.norm_w = p.final_norm;
+    op.x_out = x_.norm;
+    op.cols = kHidden;
+    op.prologue = INSG_PRO_RMSNORM;
+    op.n_segments = 1;
+    op.seg[0] = seg(p.lm_head, x_.logits, INSG_EPI_LOGITS);
+    op.seg[0].rows = x_.options.vocab;
+    op.argmax_scratch = x_.argmax_scratch;
+    op.token_out = x_.d_next;
+    op.token_feedback = x_.d_token;
+    op.token_log = x_.d_token + 4;
+    op.position_inout = x_.d_position;
+    run_gemv(c, op);
+}
+
+cudaStream_t Qwen35Decode::execution_stream() { return plan().stream; }
+
+void Qwen35Decode::delta_layer(int l)
+{
+    if (l < 0 || l >= 32 || Qwen35Shape::full_attention(l)) throw std::runtime_error("not a DeltaNet layer");
+    sync_scalars(-1);
+    enqueue_delta(l);
+    fused_token_valid_ = false;
+}
+
+void Qwen35Decode::attention_layer(int l)
+{
+    if (l < 0 || l >= 32 || !Qwen35Shape::full_attention(l)) throw std::runtime_error("not a full attention layer");
+    if (x_.position >= x_.max_context) throw std::runtime_error("KV cache full");
+    sync_scalars(-1);
+    enqueue_attention(l);
+    fused_token_valid_ = false;
+}
+
+void Qwen35Decode::layer(int l)
+{
+    if (Qwen35Shape::full_attention(l)) attention_layer(l);
+    else delta_layer(l);
+}
+
+// embed, all layers, head: what one graph replay does
+void Qwen35Decode::enqueue_token_step()
+{
+    enqueue_embed();
+    for (int l = 0; l < x_.options.n_layers; l++) {
+        if (Qwen35Shape::full_attention(l)) enqueue_attention(l);
+        else enqueue_delta(l);
+    }
+    enqueue_head();
+}
+
+void Qwen35Decode::replay_token_step()
+{
+    Plan &p = plan();
+    if (!x_.options.use_graph) {
+        enqueue_token_step();
+        return;
+    }
+    if (!p.exec) {
+        // First call: run eagerly once (loads and repacks every weight, which allocates and synchronises and
+        // therefore cannot happen during capture) -- that eager pass IS this token's step.  The graph is
+        // captured on the second call, from then on every step is a replay.
+        if (!p.capturing) {
+            enqueue_token_step();
+            p.capturing = true; // weights are resident now
+            return;
+        }
+        const uint64_t before = launches_;
+        cuda_check(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal), "begin graph capture");
+        try {
+            enqueue_token_step();
+        } catch (...) {
+            cudaGraph_t g = nullptr;
+            cudaStreamEndCapture(p.stream, &g);
+            if (g) cudaGraphDestroy(g);
+            throw;
+        }
+        cuda_check(cudaStreamEndCapture(p.stream, &p.graph), "end graph capture");
+        p.graph_nodes = launches_ - before;
+        launches_ = before;
+        cuda_check(cudaGraphInstantiate(&p.exec, p.graph, 0), "instantiate graph");
+    }
+    cuda_check(cudaGraphLaunch(p.exec, p.stream), "launch graph");
+    launches_ += p.graph_nodes;
+}
+
+void Qwen35Decode::forward_token(int token)
+{
+    if (token < 0 || token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
+    if (x_.options.n_layers > 3 && x_.position >= x_.max_context) throw std::runtime_error("KV cache full");
+    sync_scalars(token);
+    replay_token_step();
+    x_.position++;
+    fused_token_valid_ = true;
+}
+
+int Qwen35Decode::logits_argmax()
+{
+    Plan &p = plan();
+    if (!fused_token_valid_) { // logits were not produced by the fused head: reduce them now
+        insg_check(insg_argmax_logits(x_.logits, x_.options.vocab, x_.d_next, p.stream));
+        launches_++;
+    }
+    int result = -1;
+    cuda_check(cudaMemcpyAsync(&result, x_.d_next, sizeof(int), cudaMemcpyDeviceToHost, p.stream), "read token");
+    cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
+    return result;
+}
+
+int Qwen35Decode::decode_token(int token)
+{
+    forward_token(token);
+    return logits_argmax();
+}
+
+std::vector<int> Qwen35Decode::generate(int first_token, int count)
+{
+    std::vector<int> out(size_t(count > 0 ? count : 0));
+    if (count <= 0) return out;
+    if (first_token < 0 || first_token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
+    if (x_.position + count > x_.max_context) throw std::runtime_error("KV cache full");
+    Plan &p = plan();
+    const int start = x_.position;
+    sync_scalars(first_token);
+    for (int i = 0; i < count; i++) {
+        replay_token_step(); // the head feeds its arg-max back into d_token and advances d_position
+        x_.position++;
+    }
+    fused_token_valid_ = true;
+    cuda_check(cudaMemcpyAsync(out.data(), x_.d_token + 4 + start, size_t(count) * sizeof(int), cudaMemcpyDeviceToHost, p.stream),
+               "read tokens");
+    cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
+    return out;
+}
+
+int Qwen35Decode::mtp_draft(int token)
+{
+    if (token < 0 || token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
+    if (x_.position < 1) throw std::runtime_error("mtp_draft needs a forwarded token");
+    Plan &p = plan();
+    const std::string m = std::string(kLM) + ".mtp";
+    if (!p.mtp_ready) {
+        Loader L{w_, p.pinned};
+        p.mtp_fc = L.bf16(m + ".fc.weight", size_t(kHidden) * 2 * kHidden);
+        p.mtp_norm_e = L.bf16(m + ".pre_fc_norm_embedding.weight", kHidden);
+        p.mtp_norm_h = L.bf16(m + ".pre_fc_norm_hidden.weight", kHidden);
+        p.mtp_norm = L.bf16(m + ".norm.weight", kHidden);
+        load_attention(L, m + ".layers.0", p.mtp);
+        p.mtp_ready = true;
+    }
+    if (!p.head_ready || !p.embed_ready) throw std::runtime_error("mtp_draft needs a forwarded token");
+    const bool pdl = x_.options.use_pdl;
+    sync_scalars(token);
+    // embedding of the input token and the last hidden state, each normalised, side by side in qkv[8192]
+    insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
+                                x_.down, x_.d_token, p.embed.rows, kHidden, 0, p.stream));
+    insg_check(insg_rmsnorm_bf16(x_.down, p.mtp_norm_e, nullptr, x_.qkv, 1, kHidden, 0, p.stream));
+    insg_check(insg_rmsnorm_bf16(x_.hidden, p.mtp_norm_h, nullptr, x_.qkv + kHidden, 1, kHidden, 0, p.stream));
+    insg_check(insg_bf16_gemv(p.mtp_fc, x_.qkv, x_.hidden, kHidden, 2 * kHidden, 0, p.stream)); // overwrites the residual, as the reference
+    launches_ += 4;
+    Ctx c{x_, p.stream, pdl, launches_};
+    enqueue_attention_block(c, p.mtp, x_.mtp_keys, x_.mtp_values, -1); // rotary position / cache row position-1, position rows attended
+
+    insg_gemv_op op = {};
+    op.in = x_.hidden;
+    op.norm_w = p.mtp_norm;
+    op.x_out = x_.norm;
+    op.cols = kHidden;
+    op.prologue = INSG_PRO_RMSNORM;
+    op.n_segments = 1;
+    op.seg[0] = seg(p.lm_head, x_.logits, INSG_EPI_LOGITS);
+    op.seg[0].rows = x_.options.vocab;
+    op.argmax_scratch = x_.argmax_scratch;
+    op.token_out = x_.d_next;
+    run_gemv(c, op);
+    fused_token_valid_ = true;
+    return logits_argmax();
+}
+
+} // namespace insignia

@@ -1,0 +1,188 @@
+// Handle-based C face of the C++ host classes (declarations: include/insignia_b200.h, "engine" section).
+#include "insignia_b200.h"
+#include "insignia_decode.hpp"
+
+#include <cstring>
+#include <stdexcept>
+#include <vector>
+#include <memory>
+#include <string>
+
+namespace insg {
+int fail(int code, const std::string &msg);
+}
+
+struct insg_engine {
+    insignia::ModelFile model;
+    std::unique_ptr<insignia::Qwen35Weights> weights;
+    std::unique_ptr<insignia::DecodeWorkspace> ws;
+    std::unique_ptr<insignia::Qwen35Decode> dec;
+    int device = 0;
+};
+
+namespace {
+template <class F> int guarded(insg_engine *e, F &&f)
+{
+    if (!e) return insg::fail(INSG_E_ARG, "null engine");
+    try {
+        cudaSetDevice(e->device);
+        return f();
+    } catch (const std::exception &ex) {
+        return insg::fail(INSG_E_RUNTIME, ex.what());
+    }
+}
+
+float *field_ptr(insignia::DecodeWorkspace &x, const std::string &f)
+{
+    if (f == "hidden") return x.hidden;
+    if (f == "norm") return x.norm;
+    if (f == "qkv") return x.qkv;
+    if (f == "attn_gate") return x.attn_gate;
+    if (f == "key") return x.key;
+    if (f == "value") return x.value;
+    if (f == "z") return x.z;
+    if (f == "a") return x.a;
+    if (f == "b") return x.b;
+    if (f == "core") return x.core;
+    if (f == "gate") return x.gate;
+    if (f == "up") return x.up;
+    if (f == "down") return x.down;
+    if (f == "logits") return x.logits;
+    if (f == "delta_state") return x.delta_state;
+    if (f == "conv_state") return x.conv_state;
+    if (f == "kv_keys") return x.kv_keys;
+    if (f == "kv_values") return x.kv_values;
+    if (f == "mtp_keys") return x.mtp_keys;
+    if (f == "mtp_values") return x.mtp_values;
+    return nullptr;
+}
+} // namespace
+
+extern "C" {
+
+insg_engine *insg_engine_create(const char *index_path, const insg_engine_options *opt)
+{
+    if (!index_path) {
+        insg::fail(INSG_E_ARG, "null index path");
+        return nullptr;
+    }
+    insg_engine_options o = {};
+    if (opt) o = *opt;
+    try {
+        auto e = std::make_unique<insg_engine>();
+        e->device = o.device;
+        e->model = insignia::ModelFile(index_path); // host-only: file errors surface before any CUDA call
+        if (cudaSetDevice(o.device) != cudaSuccess) throw std::runtime_error("cudaSetDevice failed");
+        e->weights = std::make_unique<insignia::Qwen35Weights>(e->model, o.device_budget_bytes ? o.device_budget_bytes : (16ull << 30));
+        insignia::DecodeOptions d;
+        d.kv_bf16 = o.kv_dtype == INSG_KV_BF16;
+        d.gate_elementwise = o.gate_elementwise != 0;
+        d.accurate_trig = o.accurate_trig != 0;
+        d.use_graph = o.use_graph != 0;
+        d.use_pdl = o.use_pdl != 0;
+        if (o.n_layers > 0) d.n_layers = o.n_layers;
+        if (o.vocab > 0) d.vocab = o.vocab;
+        if (d.n_layers > insignia::Qwen35Shape::layers || d.vocab > insignia::Qwen35Shape::vocab || (d.vocab & 15))
+            throw std::runtime_error("n_layers <= 32 and vocab <= 248320, a multiple of 16");
+        e->ws = std::make_unique<insignia::DecodeWorkspace>(o.max_context > 0 ? o.max_context : 4096, nullptr, d);
+        e->dec = std::make_unique<insignia::Qwen35Decode>(*e->weights, *e->ws);
+        return e.release();
+    } catch (const std::exception &ex) {
+        insg::fail(INSG_E_RUNTIME, ex.what());
+        return nullptr;
+    }
+}
+
+void insg_engine_destroy(insg_engine *e)
+{
+    if (!e) return;
+    cudaSetDevice(e->device);
+    e->dec.reset();
+    e->ws.reset();
+    e->weights.reset();
+    delete e;
+}
+
+int insg_engine_embed(insg_engine *e, int token)
+{
+    return guarded(e, [&] {
+        e->weights->embed(token, e->ws->hidden);
+        return INSG_OK;
+    });
+}
+int insg_engine_layer(insg_engine *e, int layer)
+{
+    return guarded(e, [&] {
+        e->dec->layer(layer);
+        return INSG_OK;
+    });
+}
+int insg_engine_forward_token(insg_engine *e, int token)
+{
+    return guarded(e, [&] {
+        e->dec->forward_token(token);
+        return INSG_OK;
+    });
+}
+int insg_engine_logits_argmax(insg_engine *e)
+{
+    return guarded(e, [&] { return e->dec->logits_argmax(); });
+}
+int insg_engine_decode_token(insg_engine *e, int token)
+{
+    return guarded(e, [&] { return e->dec->decode_token(token); });
+}
+int insg_engine_mtp_draft(insg_engine *e, int token)
+{
+    return guarded(e, [&] { return e->dec->mtp_draft(token); });
+}
+int insg_engine_generate(insg_engine *e, int first_token, int count, int *out_tokens)
+{
+    return guarded(e, [&] {
+        if (!out_tokens && count > 0) return insg::fail(INSG_E_ARG, "null output");
+        const std::vector<int> t = e->dec->generate(first_token, count);
+        if (!t.empty()) std::memcpy(out_tokens, t.data(), t.size() * sizeof(int));
+        return int(INSG_OK);
+    });
+}
+int insg_engine_position(insg_engine *e) { return e ? e->ws->position : INSG_E_ARG; }
+int insg_engine_set_position(insg_engine *e, int position)
+{
+    if (!e || position < 0) return insg::fail(INSG_E_ARG, "bad position");
+    e->ws->position = position;
+    return INSG_OK;
+}
+int insg_engine_reset(insg_engine *e)
+{
+    return guarded(e, [&] {
+        cudaStreamSynchronize(e->dec->execution_stream());
+        e->ws->reset();
+        cudaStreamSynchronize(e->ws->stream);
+        return INSG_OK;
+    });
+}
+int insg_engine_read(insg_engine *e, const char *field, float *out, uint64_t count)
+{
+    return guarded(e, [&] {
+        float *src = field ? field_ptr(*e->ws, field) : nullptr;
+        if (!src || !out) return insg::fail(INSG_E_ARG, "unknown workspace field");
+        cudaStream_t st = e->dec->execution_stream();
+        if (cudaMemcpyAsync(out, src, count * sizeof(float), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+            cudaStreamSynchronize(st) != cudaSuccess)
+            return insg::fail(INSG_E_CUDA, cudaGetErrorString(cudaGetLastError()));
+        return int(INSG_OK);
+    });
+}
+void *insg_engine_buffer(insg_engine *e, const char *field)
+{
+    if (!e || !field) return nullptr;
+    return field_ptr(*e->ws, field);
+}
+insg_stream_t insg_engine_stream(insg_engine *e) { return e ? e->dec->execution_stream() : nullptr; }
+uint64_t insg_engine_launch_count(insg_engine *e) { return e ? e->dec->launch_count() : 0; }
+uint64_t insg_engine_device_bytes(insg_engine *e)
+{
+    return e ? e->weights->storage().device_bytes() + e->weights->packed_bytes() : 0;
+}
+
+} // extern "C"

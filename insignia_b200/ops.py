@@ -1,0 +1,208 @@
+"""Thin Python callers of the C ABI on torch CUDA tensors (torch only supplies device memory and streams).
+
+Every function forwards to one ``insg_*`` entry point of include/insignia_b200.h on the
+current torch stream.  Inputs must be contiguous CUDA tensors of the stated dtype;
+nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import AttnOp, GemvOp, check
+
+PRO = {"plain": 0, "rmsnorm": 1, "gated_rmsnorm": 2, "sigmoid_gate": 3, "sigmoid_gate_head0": 4, "sigmoid_gate_qproj": 5}
+EPI = {"store": 0, "residual": 1, "conv_silu": 2, "beta": 3, "decay": 4, "swiglu": 5, "logits": 6}
+KV_F32, KV_BF16 = 0, 1
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    if t is None:
+        return None
+    if not t.is_cuda or not t.is_contiguous():
+        raise ValueError("expected a contiguous CUDA tensor")
+    return t.data_ptr()
+
+
+def tune(key: str, value: int) -> None:
+    check(_lib.lib().insg_tune_set(key.encode(), value))
+
+
+def gemv_mlx(weight, scales, x):
+    rows, cols = weight.shape[0], weight.shape[1] * 8
+    y = torch.empty(rows, dtype=torch.float32, device=x.device)
+    check(_lib.lib().insg_mxfp4_gemv_mlx(_p(weight), _p(scales), _p(x), _p(y), rows, cols, _stream()))
+    return y
+
+
+def get_row_mlx(weight, scales, row):
+    cols = weight.shape[1] * 8
+    out = torch.empty(cols, dtype=torch.float32, device=weight.device)
+    check(_lib.lib().insg_mxfp4_get_row_mlx(_p(weight), _p(scales), _p(out), row, cols, _stream()))
+    return out
+
+
+def dequant_mlx(weight, scales):
+    rows, cols = weight.shape[0], weight.shape[1] * 8
+    out = torch.empty((rows, cols), dtype=torch.float32, device=weight.device)
+    check(_lib.lib().insg_mxfp4_dequant_mlx(_p(weight), _p(scales), _p(out), rows, cols, _stream()))
+    return out
+
+
+def repack(weight, scales):
+    rows, cols = weight.shape[0], weight.shape[1] * 8
+    n = _lib.lib().insg_mxfp4_packed_bytes(rows, cols)
+    if n == 0:
+        raise ValueError("rows % 16 and cols % 128 must be 0")
+    packed = torch.empty(n, dtype=torch.uint8, device=weight.device)
+    check(_lib.lib().insg_mxfp4_repack(_p(weight), _p(scales), _p(packed), rows, cols, _stream()))
+    packed.rows, packed.cols = rows, cols
+    return packed
+
+
+def gemv_packed(packed, x, rows=None, cols=None):
+    rows = rows or packed.rows
+    cols = cols or packed.cols
+    x2 = x.reshape(-1, cols)
+    y = torch.empty((x2.shape[0], rows), dtype=torch.float32, device=x.device)
+    check(_lib.lib().insg_mxfp4_gemv_packed(_p(packed), _p(x2), _p(y), rows, cols, x2.shape[0], _stream()))
+    return y.reshape(*x.shape[:-1], rows)
+
+
+def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False):
+    """``segments``: list of dicts with packed, out, rows, epilogue (+ packed2 / conv_state, conv_w / A_log, dt_bias).
+    ``argmax``: dict(scratch, token_out[, token_feedback, token_log, position]) for the logits epilogue."""
+    op = GemvOp()
+    op.in_, op.aux, op.norm_w, op.x_out = _p(inp), _p(aux), _p(norm_w), _p(x_out)
+    op.cols, op.prologue, op.n_segments = inp.shape[-1], PRO[prologue], len(segments)
+    for i, s in enumerate(segments):
+        g = op.seg[i]
+        g.packed, g.packed2, g.out = _p(s["packed"]), _p(s.get("packed2")), _p(s["out"])
+        g.rows, g.epilogue = s["rows"], EPI[s["epilogue"]]
+        g.conv_state, g.conv_w = _p(s.get("conv_state")), _p(s.get("conv_w"))
+        g.A_log, g.dt_bias = _p(s.get("A_log")), _p(s.get("dt_bias"))
+    if argmax:
+        op.argmax_scratch, op.token_out = _p(argmax["scratch"]), _p(argmax["token_out"])
+        op.token_feedback, op.token_log = _p(argmax.get("token_feedback")), _p(argmax.get("token_log"))
+        op.position_inout = _p(argmax.get("position"))
+    op.pdl = int(pdl)
+    check(_lib.lib().insg_gemv_fused(C.byref(op), _stream()))
+
+
+def argmax_scratch(device):
+    return torch.zeros(_lib.lib().insg_gemv_argmax_scratch_bytes(), dtype=torch.uint8, device=device)
+
+
+def deltanet_decode(state, q16, k16, v32, g32, beta32, pdl=False):
+    out = torch.empty(32 * 128, dtype=torch.float32, device=state.device)
+    check(_lib.lib().insg_deltanet_decode(_p(state), _p(q16), _p(k16), _p(v32), _p(g32), _p(beta32), _p(out), int(pdl),
+                                          _stream()))
+    return out
+
+
+def gqa_scratch(device, tokens=0):
+    return torch.zeros(_lib.lib().insg_gqa_scratch_bytes(tokens), dtype=torch.uint8, device=device)
+
+
+def gqa_decode(q, k_cache, v_cache, tokens, scratch=None):
+    kv = KV_BF16 if k_cache.dtype == torch.bfloat16 else KV_F32
+    scratch = scratch if scratch is not None else gqa_scratch(q.device, tokens)
+    out = torch.empty(16 * 256, dtype=torch.float32, device=q.device)
+    check(_lib.lib().insg_gqa_decode(_p(q), _p(k_cache), _p(v_cache), _p(out), tokens, kv, _p(scratch), scratch.numel(),
+                                     _stream()))
+    return out
+
+
+def attention_step(qraw, k_raw, v, q_w, k_w, k_cache, v_cache, position, max_context, scratch, position_offset=0,
+                   fast_trig=True, pdl=False):
+    op = AttnOp()
+    op.qraw, op.k_raw, op.v, op.q_norm_w, op.k_norm_w = _p(qraw), _p(k_raw), _p(v), _p(q_w), _p(k_w)
+    op.k_cache, op.v_cache = _p(k_cache), _p(v_cache)
+    out = torch.empty(16 * 256, dtype=torch.float32, device=qraw.device)
+    op.out, op.position, op.position_offset, op.max_context = _p(out), _p(position), position_offset, max_context
+    op.kv_dtype = KV_BF16 if k_cache.dtype == torch.bfloat16 else KV_F32
+    op.fast_trig, op.scratch, op.scratch_bytes, op.pdl = int(fast_trig), _p(scratch), scratch.numel(), int(pdl)
+    check(_lib.lib().insg_attention_step(C.byref(op), _stream()))
+    return out
+
+
+def rmsnorm_bf16(x, w, zero_centered=False, gate=None):
+    x2 = x.reshape(-1, x.shape[-1])
+    y = torch.empty_like(x2)
+    check(_lib.lib().insg_rmsnorm_bf16(_p(x2), _p(w), _p(gate), _p(y), x2.shape[0], x2.shape[1], int(zero_centered),
+                                       _stream()))
+    return y.reshape(x.shape)
+
+
+def rmsnorm_zero_centered(x, w, eps=1e-6):
+    y = torch.empty_like(x)
+    check(_lib.lib().insg_rmsnorm_zero_centered(_p(x), _p(w), _p(y), x.shape[0], x.shape[1], eps, _stream()))
+    return y
+
+
+def causal_conv4_silu(x, state, w):
+    check(_lib.lib().insg_causal_conv4_silu(_p(x), _p(state), _p(w), x.numel(), _stream()))
+
+
+def deltanet_parameters(a, b, A_log, dt_bias):
+    check(_lib.lib().insg_deltanet_parameters(_p(a), _p(b), _p(A_log), _p(dt_bias), a.numel(), _stream()))
+
+
+def qk_norm_rope(q, k, q_w, k_w, position, fast_trig=True):
+    check(_lib.lib().insg_qk_norm_rope(_p(q), _p(k), _p(q_w), _p(k_w), position, int(fast_trig), _stream()))
+
+
+def silu_mul(gate, up):
+    y = torch.empty_like(gate)
+    check(_lib.lib().insg_silu_mul(_p(gate), _p(up), _p(y), gate.numel(), _stream()))
+    return y
+
+
+def residual_add(x, delta):
+    check(_lib.lib().insg_residual_add(_p(x), _p(delta), x.numel(), _stream()))
+
+
+def sigmoid_mul(x, gate):
+    check(_lib.lib().insg_sigmoid_mul(_p(x), _p(gate), x.numel(), _stream()))
+
+
+def store_kv(k, v, k_cache, v_cache, position):
+    kv = KV_BF16 if k_cache.dtype == torch.bfloat16 else KV_F32
+    check(_lib.lib().insg_store_kv(_p(k), _p(v), _p(k_cache), _p(v_cache), position, kv, _stream()))
+
+
+def split_q_gate(interleaved):
+    q = torch.empty(4096, dtype=torch.float32, device=interleaved.device)
+    g = torch.empty_like(q)
+    check(_lib.lib().insg_split_q_gate(_p(interleaved), _p(q), _p(g), _stream()))
+    return q, g
+
+
+def expand_gate_heads(gate):
+    out = torch.empty_like(gate)
+    check(_lib.lib().insg_expand_gate_heads(_p(gate), _p(out), _stream()))
+    return out
+
+
+def concat(a, b):
+    out = torch.empty(a.numel() * 2, dtype=torch.float32, device=a.device)
+    check(_lib.lib().insg_concat(_p(a), _p(b), _p(out), a.numel(), _stream()))
+    return out
+
+
+def argmax_logits(logits):
+    out = torch.zeros(1, dtype=torch.int32, device=logits.device)
+    check(_lib.lib().insg_argmax_logits(_p(logits), logits.numel(), _p(out), _stream()))
+    return out
+
+
+def bf16_gemv(w, x, pdl=False):
+    y = torch.empty(w.shape[0], dtype=torch.float32, device=x.device)
+    check(_lib.lib().insg_bf16_gemv(_p(w), _p(x), _p(y), w.shape[0], w.shape[1], int(pdl), _stream()))
+    return y

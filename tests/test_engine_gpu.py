@@ -1,0 +1,147 @@
+"""The decode engine (C++ host classes through the C ABI) on a 4-layer synthetic checkpoint:
+against golden vectors from the reference's NumPy tools, the CPU oracle, and the compiled reference engine."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
+from oracle import oracle as orc  # noqa: E402
+from tests import refengine  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def cos(a, b):
+    return float(a @ b / np.linalg.norm(a) / np.linalg.norm(b))
+
+
+def close(a, b, rel=2e-2):
+    """north-star layer bar: cosine >= 0.9999 and max-abs-rel <= 2e-2 (relative to the largest reference element)."""
+    return cos(a, b) >= 0.9999 and np.max(np.abs(a - b)) <= rel * np.abs(b).max()
+
+
+def small_engine(idx, **kw):
+    from insignia_b200.engine import Engine
+
+    kw.setdefault("n_layers", 4)
+    kw.setdefault("vocab", 64)
+    kw.setdefault("max_context", 64)
+    return Engine(idx, **kw)
+
+
+def test_layers_match_numpy_tool_golden(cuda, golden_ckpt):
+    gold = np.load(os.path.join(GOLD, "layers_tok42.npy"))
+    with small_engine(golden_ckpt[1], gate_elementwise=True, use_graph=False) as e:
+        e.embed(42)
+        for l in range(4):
+            e.layer(l)
+            h = e.read("hidden")
+            assert close(h, gold[l]), l
+            assert np.max(np.abs(h - gold[l])) <= 1e-4 * np.abs(gold[l]).max(), l
+
+
+@pytest.mark.parametrize("graph,pdl", [(False, False), (False, True), (True, True)])
+def test_multi_token_decode_vs_oracle(cuda, golden_ckpt, graph, pdl):
+    from insignia_b200.checkpoint_io import SafetensorsReader
+
+    m = orc.OracleModel(SafetensorsReader(golden_ckpt[0]), max_context=64, gate="broadcast", n_layers=4)
+    tokens = [42, 7, 63, 0, 21, 5, 33, 60, 1, 2]
+    with small_engine(golden_ckpt[1], use_graph=graph, use_pdl=pdl) as e:
+        for i, t in enumerate(tokens):
+            got = e.decode_token(t)
+            want = m.decode_token(t)
+            h, lg = e.read("hidden"), e.read("logits")
+            assert close(h, m.hidden, 1e-3), i
+            assert np.max(np.abs(lg - m.logits[:64])) <= 1e-3 * np.abs(m.logits).max(), i
+            assert got == want == int(np.argmax(lg)), i
+            assert e.position == m.position == i + 1
+        ds = e.read("delta_state", 3 * 32 * 128 * 128)
+        assert np.max(np.abs(ds - m.delta_state[:3].reshape(-1))) <= 1e-3 * np.abs(m.delta_state[:3]).max()
+        cs = e.read("conv_state", 3 * 8192 * 3)
+        assert np.max(np.abs(cs - m.conv_state[:3].reshape(-1))) <= 1e-3 * np.abs(m.conv_state[:3]).max()
+        assert e.launch_count > 0
+
+
+def test_generate_equals_decode_token_loop(cuda, golden_ckpt):
+    with small_engine(golden_ckpt[1]) as a, small_engine(golden_ckpt[1]) as b:
+        for t in (3, 9):
+            a.forward_token(t), b.forward_token(t)
+        first = a.logits_argmax()
+        assert first == b.logits_argmax()
+        gen = a.generate(first, 20)
+        loop, t = [], first
+        for _ in range(20):
+            t = b.decode_token(t)
+            loop.append(t)
+        assert gen == loop
+        assert a.position == b.position == 22
+        assert np.array_equal(a.read("hidden"), b.read("hidden"))  # same kernels, same order: bit-identical
+
+
+def test_kv_bf16_and_accurate_trig_modes(cuda, golden_ckpt):
+    from insignia_b200.checkpoint_io import SafetensorsReader
+
+    m = orc.OracleModel(SafetensorsReader(golden_ckpt[0]), max_context=64, gate="elementwise", n_layers=4)
+    with small_engine(golden_ckpt[1], gate_elementwise=True, accurate_trig=True) as e32, \
+            small_engine(golden_ckpt[1], gate_elementwise=True, accurate_trig=True, kv_bf16=True) as e16:
+        for i, t in enumerate([42, 7, 63, 0, 21, 5]):
+            m.forward_token(t)
+            e32.forward_token(t), e16.forward_token(t)
+            assert close(e32.read("hidden"), m.hidden, 1e-4), i
+            assert close(e16.read("hidden"), m.hidden, 2e-2), i
+
+
+def test_engine_errors_follow_reference(cuda, golden_ckpt):
+    from insignia_b200.engine import InsigniaError
+
+    with small_engine(golden_ckpt[1], max_context=2) as e:
+        with pytest.raises(InsigniaError, match="not a DeltaNet layer"):
+            e._h and __import__("insignia_b200._lib", fromlist=["x"]).check(
+                __import__("insignia_b200._lib", fromlist=["x"]).lib().insg_engine_layer(e._h, 32))
+        with pytest.raises(InsigniaError, match="token out of range"):
+            e.forward_token(248320)
+        with pytest.raises(InsigniaError, match="token out of range"):
+            e.embed(-1)
+        e.forward_token(1), e.forward_token(2)
+        with pytest.raises(InsigniaError, match="KV cache full"):
+            e.forward_token(3)
+        e.reset()
+        assert e.position == 0
+        e.forward_token(1)
+    with pytest.raises(InsigniaError, match="cannot open Insignia index"):
+        small_engine("/nonexistent.idx")
+
+
+def test_storage_budget_eviction_error(cuda, golden_ckpt):
+    """A budget below one tensor throws like the reference (src/storage.cu:8)."""
+    from insignia_b200.engine import InsigniaError
+
+    with small_engine(golden_ckpt[1], budget_bytes=1 << 20, use_graph=False) as e:
+        with pytest.raises(InsigniaError, match="tensor exceeds device budget"):
+            e.embed(1)
+            e.layer(0)
+
+
+@pytest.mark.skipif(not refengine.available(), reason="compiled reference (oracle/_ref) not built")
+def test_layers_vs_compiled_reference_engine(cuda, golden_ckpt):
+    """The reference's own engine (unmodified sources) driven like src/dump_layers.cu:5 / src/test_full_model.cu:6:
+    embed, layers 0..3, position++, for several tokens; same calls on this engine."""
+    ref = refengine.RefEngine(golden_ckpt[1], max_context=64)
+    try:
+        with small_engine(golden_ckpt[1], use_graph=False) as e:
+            for i, t in enumerate([42, 7, 63, 0, 21, 5, 33, 11]):
+                ref.embed(t), e.embed(t)
+                for l in range(4):
+                    ref.layer(l), e.layer(l)
+                    a, b = e.read("hidden"), ref.read("hidden", 4096)
+                    assert close(a, b, 1e-3), (i, l)
+                    assert np.max(np.abs(a - b)) <= 2e-4 * np.abs(b).max(), (i, l)
+                ref.position = ref.position + 1
+                e.position = e.position + 1
+            ds, dr = e.read("delta_state", 3 * 32 * 128 * 128), ref.read("delta_state", 3 * 32 * 128 * 128)
+            assert np.max(np.abs(ds - dr)) <= 2e-4 * np.abs(dr).max()
+    finally:
+        ref.close()
