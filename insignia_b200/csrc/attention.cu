@@ -44,7 +44,7 @@ template <> struct KvRow<false> {
     static __device__ __forceinline__ void load(const void *base, size_t row_elems, int lane, float (&o)[8])
     {
         const float4 *p = reinterpret_cast<const float4 *>(static_cast<const float *>(base) + row_elems) + lane * 2;
-        const float4 a = p[0], b = p[1];
+        const float4 a = __ldcg(p), b = __ldcg(p + 1);
         o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
     }
     static __device__ __forceinline__ float round(float v) { return v; }
@@ -53,7 +53,7 @@ template <> struct KvRow<false> {
 template <> struct KvRow<true> {
     static __device__ __forceinline__ void load(const void *base, size_t row_elems, int lane, float (&o)[8])
     {
-        const uint4 r = *(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + row_elems) + lane);
+        const uint4 r = __ldcg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + row_elems) + lane);
         o[0] = __uint_as_float(r.x << 16); o[1] = __uint_as_float(r.x & 0xffff0000u);
         o[2] = __uint_as_float(r.y << 16); o[3] = __uint_as_float(r.y & 0xffff0000u);
         o[4] = __uint_as_float(r.z << 16); o[5] = __uint_as_float(r.z & 0xffff0000u);
@@ -120,7 +120,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
 
     int tokens = p.tokens, pos = -1;
     if constexpr (FUSED) {
-        pos = *p.position + p.position_offset;
+        pos = __ldcg(p.position) + p.position_offset;
         tokens = pos + 1;
     }
     if (tokens > p.max_context) tokens = p.max_context; // host checks; never index past the cache
@@ -136,7 +136,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
                 float v[8];
                 const float *src = p.q + size_t(kvh * 4 + warp) * 512 + lane * 8;
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = src[j];
+                for (int j = 0; j < 8; j++) v[j] = __ldcg(src + j);
                 norm_rope_256(v, p.q_w, lane, pos, p.fast_trig != 0);
 #pragma unroll
                 for (int j = 0; j < 8; j++) s_q[warp][lane * 8 + j] = v[j];
@@ -144,7 +144,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
                 float v[8];
                 const float *src = p.k_raw + kvh * 256 + lane * 8;
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = src[j];
+                for (int j = 0; j < 8; j++) v[j] = __ldcg(src + j);
                 norm_rope_256(v, p.k_w, lane, pos, p.fast_trig != 0);
                 const size_t row = (size_t(pos) * 4 + kvh) * 256 + lane * 8;
 #pragma unroll
@@ -156,13 +156,13 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
                 const size_t row = (size_t(pos) * 4 + kvh) * 256 + lane * 8;
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
-                    const float v = p.v_new[kvh * 256 + lane * 8 + j];
+                    const float v = __ldcg(p.v_new + kvh * 256 + lane * 8 + j);
                     Row::store(p.vc, row + j, v);
                     s_vnew[lane * 8 + j] = Row::round(v);
                 }
             }
         } else {
-            for (int i = tid; i < 1024; i += kAtThreads) s_q[i >> 8][i & 255] = p.q[size_t(kvh) * 1024 + i];
+            for (int i = tid; i < 1024; i += kAtThreads) s_q[i >> 8][i & 255] = __ldcg(p.q + size_t(kvh) * 1024 + i);
         }
     }
     __syncthreads();

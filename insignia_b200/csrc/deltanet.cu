@@ -42,15 +42,15 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
     float *S = state + size_t(head) * 128 * 128;
     float4 cell[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) cell[j] = *reinterpret_cast<const float4 *>(S + size_t(kr + 32 * j) * 128 + v0);
+    for (int j = 0; j < 4; j++) cell[j] = __ldcg(reinterpret_cast<const float4 *>(S + size_t(kr + 32 * j) * 128 + v0));
 
     pdl_wait();
 
     // L2 norms of q and k over 128 (eps added to the sum, as the reference)
     float qv = 0.f, kv = 0.f;
     if (tid < 128) {
-        qv = q16[kh * 128 + tid];
-        kv = k16[kh * 128 + tid];
+        qv = __ldcg(q16 + kh * 128 + tid);
+        kv = __ldcg(k16 + kh * 128 + tid);
     }
     float qn = warp_sum(qv * qv), kn = warp_sum(kv * kv);
     if (lane == 0) { s_red[warp] = qn; s_red[8 + warp] = kn; }
@@ -61,8 +61,8 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
     if (tid < 128) { s_q[tid] = qv * qs; s_k[tid] = kv * ks; }
     __syncthreads();
 
-    const float decay = expf(g32[head]);
-    const float beta = beta32[head];
+    const float decay = expf(__ldcg(g32 + head));
+    const float beta = __ldcg(beta32 + head);
 
     // mem_v = sum_i (S*d) * k
     float4 pm = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
         float mem = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; w++) mem += s_part[w][tid];
-        s_delta[tid] = (v32[head * 128 + slice * 32 + tid] - mem) * beta;
+        s_delta[tid] = (__ldcg(v32 + head * 128 + slice * 32 + tid) - mem) * beta;
     }
     __syncthreads();
     const float4 dl = *reinterpret_cast<const float4 *>(&s_delta[vq * 4]);

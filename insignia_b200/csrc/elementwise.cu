@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(256) bf16_gemv_kernel(const uint16_t *__restri
 #pragma unroll 4
     for (int i = lane; i < nvec; i += 32) {
         const uint4 q = ldg_stream(wr + i);
-        const float4 x0 = reinterpret_cast<const float4 *>(x)[i * 2], x1 = reinterpret_cast<const float4 *>(x)[i * 2 + 1];
+        const float4 x0 = __ldcg(reinterpret_cast<const float4 *>(x) + i * 2), x1 = __ldcg(reinterpret_cast<const float4 *>(x) + i * 2 + 1);
         z = fmaf(__uint_as_float(q.x << 16), x0.x, z); z = fmaf(__uint_as_float(q.x & 0xffff0000u), x0.y, z);
         z = fmaf(__uint_as_float(q.y << 16), x0.z, z); z = fmaf(__uint_as_float(q.y & 0xffff0000u), x0.w, z);
         z = fmaf(__uint_as_float(q.z << 16), x1.x, z); z = fmaf(__uint_as_float(q.z & 0xffff0000u), x1.y, z);

@@ -29,8 +29,6 @@
 namespace insg {
 
 constexpr int kRec = 1088;            // bytes per (16-row tile, 128-k block): 1024 nibble bytes + 64 scale bytes
-constexpr int kThreads = 256;         // 8 warps split K
-constexpr int kWarps = 8;
 constexpr float kLoScale = 1.0f / 2048.0f;
 
 struct SegDev {
@@ -52,6 +50,7 @@ struct GemvParams {
     float2 *argmax_partial; // [grid] (value, index as int bits)
     unsigned *ticket;
     int *token_out, *token_feedback, *token_log, *position_inout;
+    int ksplit, gpc; // warps per tile group, groups per CTA
 };
 
 // ---- E2M1 x8 (one u32) -> four fp16x2 registers -----------------------------
@@ -119,7 +118,7 @@ __device__ __forceinline__ void cursor_set(const GemvParams &p, Cursor &c, int n
     c.base = (c.mat ? s.packed2 : s.packed) + size_t(c.tile - s.tile_begin) * nkb * kRec;
 }
 
-__device__ __forceinline__ Cursor cursor_next(const GemvParams &p, const Cursor &c, int nchunk, int nkb)
+__device__ __forceinline__ Cursor cursor_next(const GemvParams &p, const Cursor &c, int nchunk, int nkb, int stride)
 {
     Cursor n = c;
     if (c.chunk + 1 < nchunk) {
@@ -131,7 +130,7 @@ __device__ __forceinline__ Cursor cursor_next(const GemvParams &p, const Cursor 
         n.mat = 1;
     } else {
         n.mat = 0;
-        n.tile = c.tile + gridDim.x;
+        n.tile = c.tile + stride;
     }
     cursor_set(p, n, nkb);
     return n;
@@ -193,28 +192,52 @@ __device__ __forceinline__ void compute_chunk(const Chunk<UNR> &b, const Cursor 
     }
 }
 
+// Block-wide reductions for a run-time warp count (<= 16); `scratch` needs 16 floats.
+__device__ __forceinline__ float block_sum_dyn(float v, float *scratch, int nwarps)
+{
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nwarps; i++) t += scratch[i];
+    return t;
+}
+__device__ __forceinline__ float block_max_dyn(float v, float *scratch, int nwarps)
+{
+    v = warp_max(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = scratch[0];
+    for (int i = 1; i < nwarps; i++) t = fmaxf(t, scratch[i]);
+    return t;
+}
+
 // ---- activation prologue: fp32 vector -> two fp16 pieces in shared memory ----
-// Returns 1/alpha (the factor that undoes the power-of-two pre-scale).
+// Returns 1/alpha (the factor that undoes the power-of-two pre-scale).  Activations are
+// read with ld.global.cg: under programmatic dependent launch this CTA may have been
+// resident (and its L1 filled) before the producing kernel wrote them.
 template <int DEQ>
 __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, float *scratch)
 {
-    const int cols = p.cols, tid = threadIdx.x, lane = tid & 31;
+    const int cols = p.cols, tid = threadIdx.x, lane = tid & 31, nthreads = blockDim.x, nwarps = nthreads >> 5;
     const float *in = p.in + size_t(m) * cols;
     const int nvec = cols >> 2;
     float inv_rms = 1.f;
     if (p.prologue == INSG_PRO_RMSNORM) {
         float ss = 0.f;
-        for (int i = tid; i < nvec; i += kThreads) {
-            const float4 v = reinterpret_cast<const float4 *>(in)[i];
+        for (int i = tid; i < nvec; i += nthreads) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(in) + i);
             ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
         }
-        ss = block_sum<kWarps>(ss, scratch);
+        ss = block_sum_dyn(ss, scratch, nwarps);
         inv_rms = rsqrtf(ss / float(cols) + 1e-6f);
     }
     // The transformed vector is evaluated twice (once for its maximum, once for the split)
-    // instead of being staged in fp32: the inputs sit in L1/L2 and K = 12288 would not fit.
+    // instead of being staged in fp32: the inputs sit in L2 and K = 12288 would not fit.
     auto value4 = [&](int i) -> float4 {
-        float4 v = reinterpret_cast<const float4 *>(in)[i];
+        float4 v = __ldcg(reinterpret_cast<const float4 *>(in) + i);
         const int k = i << 2;
         switch (p.prologue) {
         case INSG_PRO_RMSNORM: {
@@ -231,7 +254,7 @@ __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, f
             ss = warp_sum(ss);
             const float inv = rsqrtf(ss / 128.f + 1e-6f);
             const uint2 wv = reinterpret_cast<const uint2 *>(p.norm_w)[lane];
-            const float4 z = reinterpret_cast<const float4 *>(p.aux + size_t(m) * cols)[i];
+            const float4 z = __ldcg(reinterpret_cast<const float4 *>(p.aux + size_t(m) * cols) + i);
             v.x = v.x * inv * bf16_bits_to_float(wv.x & 0xffff) * fast_silu(z.x);
             v.y = v.y * inv * bf16_bits_to_float(wv.x >> 16) * fast_silu(z.y);
             v.z = v.z * inv * bf16_bits_to_float(wv.y & 0xffff) * fast_silu(z.z);
@@ -239,18 +262,18 @@ __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, f
             break;
         }
         case INSG_PRO_SIGMOID_GATE: {
-            const float4 g = reinterpret_cast<const float4 *>(p.aux + size_t(m) * cols)[i];
+            const float4 g = __ldcg(reinterpret_cast<const float4 *>(p.aux + size_t(m) * cols) + i);
             v.x *= fast_sigmoid(g.x); v.y *= fast_sigmoid(g.y); v.z *= fast_sigmoid(g.z); v.w *= fast_sigmoid(g.w);
             break;
         }
         case INSG_PRO_SIGMOID_GATE_HEAD0: {
-            const float g = fast_sigmoid(p.aux[size_t(m) * 2 * cols + (k >> 8) * 512 + 256]);
+            const float g = fast_sigmoid(__ldcg(p.aux + size_t(m) * 2 * cols + (k >> 8) * 512 + 256));
             v.x *= g; v.y *= g; v.z *= g; v.w *= g;
             break;
         }
         case INSG_PRO_SIGMOID_GATE_QPROJ: {
             const float4 g =
-                *reinterpret_cast<const float4 *>(p.aux + size_t(m) * 2 * cols + (k >> 8) * 512 + 256 + (k & 255));
+                __ldcg(reinterpret_cast<const float4 *>(p.aux + size_t(m) * 2 * cols + (k >> 8) * 512 + 256 + (k & 255)));
             v.x *= fast_sigmoid(g.x); v.y *= fast_sigmoid(g.y); v.z *= fast_sigmoid(g.z); v.w *= fast_sigmoid(g.w);
             break;
         }
@@ -259,19 +282,19 @@ __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, f
         return v;
     };
     float amax = 0.f;
-    for (int i = tid; i < nvec; i += kThreads) {
+    for (int i = tid; i < nvec; i += nthreads) {
         const float4 v = value4(i);
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
         if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out + size_t(m) * cols)[i] = v;
     }
-    const float tmax = block_max<kWarps>(amax, scratch);
+    const float tmax = block_max_dyn(amax, scratch, nwarps);
     // alpha = 2^(12 - floor(log2(max))) keeps the largest element in [2^12, 2^13)
     int eb = int((__float_as_uint(tmax) >> 23) & 0xffu);
     eb = min(max(eb, 20), 240);
     const float alpha = __uint_as_float(uint32_t(266 - eb) << 23);
     const float inv_alpha = __uint_as_float(uint32_t(eb - 12) << 23);
     __half *hi = xs + size_t(m * 2) * xstride, *lo = hi + xstride;
-    for (int i = tid; i < nvec; i += kThreads) {
+    for (int i = tid; i < nvec; i += nthreads) {
         const float4 v = value4(i);
         const float e[4] = {v.x * alpha, v.y * alpha, v.z * alpha, v.w * alpha};
 #pragma unroll
@@ -286,27 +309,40 @@ __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, f
     return inv_alpha;
 }
 
+__device__ __forceinline__ void group_barrier(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Work decomposition: a GROUP of `ksplit` warps owns a 16-row tile and splits its K range;
+// a CTA holds `gpc` groups; group G of the grid walks tiles G, G+groups, ...  Warps never
+// meet at a CTA-wide barrier after the prologue, so while one warp waits on its weight
+// loads the others compute.  Each warp runs a two-deep software pipeline (loads of chunk
+// n+1 in flight while chunk n is multiplied) that continues across tile boundaries.
 template <int DEQ, int UNR, int M>
-__global__ void __launch_bounds__(kThreads) gemv_fused_kernel(const __grid_constant__ GemvParams p)
+__global__ void __launch_bounds__(512, 1) gemv_fused_kernel(const __grid_constant__ GemvParams p)
 {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int nkb = p.cols >> 7;
     const int xstride = p.cols + 8;
+    const int ksplit = p.ksplit, gpc = p.gpc;
     __half *xs = reinterpret_cast<__half *>(smem_raw);
-    float *red = reinterpret_cast<float *>(smem_raw + size_t(M) * 2 * xstride * sizeof(__half)); // [2][8][M][16]
-    float *scratch = red + 2 * kWarps * M * 16;                                                  // 64 + 256 floats
+    float *red = reinterpret_cast<float *>(smem_raw + size_t(M) * 2 * xstride * sizeof(__half)); // [gpc][2][ksplit][M][16]
+    float *scratch = red + size_t(gpc) * 2 * ksplit * M * 16;                                    // 64 floats
     __shared__ int s_last;
 
     pdl_launch_dependents();
 
-    const int kb0 = (warp * nkb) / kWarps, kb1 = ((warp + 1) * nkb) / kWarps;
-    const int span = (nkb + kWarps - 1) / kWarps;
+    const int grp_local = warp / ksplit, wk = warp - grp_local * ksplit;
+    const int kb0 = (wk * nkb) / ksplit, kb1 = ((wk + 1) * nkb) / ksplit;
+    const int span = (nkb + ksplit - 1) / ksplit;
     const int nchunk = max(1, (span + UNR - 1) / UNR);
+    const int stride = int(gridDim.x) * gpc;
 
     Cursor cur;
-    cur.tile = blockIdx.x;
+    cur.tile = grp_local < gpc ? int(blockIdx.x) * gpc + grp_local : p.total_tiles; // spare warps idle
     cur.mat = 0;
     cur.chunk = 0;
     cursor_set(p, cur, nkb);
@@ -325,84 +361,94 @@ __global__ void __launch_bounds__(kThreads) gemv_fused_kernel(const __grid_const
     float acc[M][4];
 #pragma unroll
     for (int m = 0; m < M; m++) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
-    float gate_val = 0.f; // gate_proj result held by the row's thread while up_proj streams
+    float gate_val = 0.f; // gate_proj result held by the row's lane while up_proj streams
     float best = -3.402823466e38f;
     int best_idx = 0x7fffffff;
     int parity = 0;
+    float *gred = red + size_t(grp_local) * 2 * ksplit * M * 16;
 
     auto finish = [&](const Cursor &c) {
-        // fold hi/lo pieces, sum the quad (4 scale groups), then the 8 warps through shared memory
-        float *r = red + parity * (kWarps * M * 16);
+        float y[M];
 #pragma unroll
         for (int m = 0; m < M; m++) {
+            // fold hi/lo pieces, sum the quad (4 scale groups); lanes 0..15 then hold rows 0..15 of the tile
             float v0 = fmaf(acc[m][1], kLoScale, acc[m][0]);
             float v1 = fmaf(acc[m][3], kLoScale, acc[m][2]);
             v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
             v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
             v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
-            if (t == 0) {
-                r[(warp * M + m) * 16 + g] = v0;
-                r[(warp * M + m) * 16 + g + 8] = v1;
-            }
+            const float r0 = __shfl_sync(0xffffffffu, v0, (lane & 7) * 4);
+            const float r1 = __shfl_sync(0xffffffffu, v1, (lane & 7) * 4);
+            y[m] = (lane & 8) ? r1 : r0;
             acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
         }
-        __syncthreads();
-        if (tid < 16 * M) {
-            const int m = tid >> 4, rr = tid & 15;
-            float y = 0.f;
+        if (ksplit > 1) {
+            float *r = gred + size_t(parity) * ksplit * M * 16;
+            if (lane < 16) {
 #pragma unroll
-            for (int w = 0; w < kWarps; w++) y += r[(w * M + m) * 16 + rr];
-            float ia = inv_alpha[0];
+                for (int m = 0; m < M; m++) r[(wk * M + m) * 16 + lane] = y[m];
+            }
+            group_barrier(1 + grp_local, 32 * ksplit);
+            if (wk == 0 && lane < 16) {
 #pragma unroll
-            for (int mm = 1; mm < M; mm++)
-                if (m == mm) ia = inv_alpha[mm];
-            y *= ia * (DEQ == 1 ? 16384.0f : 1.0f);
+                for (int m = 0; m < M; m++) {
+                    float z = 0.f;
+                    for (int w = 0; w < ksplit; w++) z += r[(w * M + m) * 16 + lane];
+                    y[m] = z;
+                }
+            }
+            parity ^= 1;
+        }
+        if (wk == 0 && lane < 16) {
             const SegDev &s = p.seg[c.seg];
-            const int row = (c.tile - s.tile_begin) * 16 + rr;
-            float *out = s.out + size_t(m) * s.rows;
-            switch (s.epilogue) {
-            case INSG_EPI_STORE: out[row] = y; break;
-            case INSG_EPI_RESIDUAL: out[row] += y; break;
-            case INSG_EPI_CONV_SILU: {
-                float *st = s.conv_state + size_t(row) * 3;
-                const uint2 wv = reinterpret_cast<const uint2 *>(s.conv_w)[row];
-                const float w0 = bf16_bits_to_float(wv.x & 0xffff), w1 = bf16_bits_to_float(wv.x >> 16);
-                const float w2 = bf16_bits_to_float(wv.y & 0xffff), w3 = bf16_bits_to_float(wv.y >> 16);
-                const float s0 = st[0], s1 = st[1], s2 = st[2];
-                const float z = fmaf(s0, w0, fmaf(s1, w1, fmaf(s2, w2, y * w3)));
-                st[0] = s1; st[1] = s2; st[2] = y;
-                out[row] = fast_silu(z);
-                break;
-            }
-            case INSG_EPI_BETA: out[row] = fast_sigmoid(y); break;
-            case INSG_EPI_DECAY: {
-                const float z = y + bf16_bits_to_float(s.dt_bias[row]);
-                const float soft = z > 20.f ? z : log1pf(__expf(z));
-                out[row] = -__expf(s.A_log[row]) * soft;
-                break;
-            }
-            case INSG_EPI_SWIGLU:
-                if (c.mat == 0) gate_val = y;
-                else out[row] = fast_silu(gate_val) * y;
-                break;
-            case INSG_EPI_LOGITS:
-                out[row] = y;
-                if (y > best || (y == best && row < best_idx)) { best = y; best_idx = row; }
-                break;
-            default: break;
+            const int row = (c.tile - s.tile_begin) * 16 + lane;
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float v = y[m] * inv_alpha[m] * (DEQ == 1 ? 16384.0f : 1.0f);
+                float *out = s.out + size_t(m) * s.rows;
+                switch (s.epilogue) {
+                case INSG_EPI_STORE: out[row] = v; break;
+                case INSG_EPI_RESIDUAL: out[row] = __ldcg(out + row) + v; break;
+                case INSG_EPI_CONV_SILU: {
+                    float *st = s.conv_state + size_t(row) * 3;
+                    const uint2 wv = reinterpret_cast<const uint2 *>(s.conv_w)[row];
+                    const float w0 = bf16_bits_to_float(wv.x & 0xffff), w1 = bf16_bits_to_float(wv.x >> 16);
+                    const float w2 = bf16_bits_to_float(wv.y & 0xffff), w3 = bf16_bits_to_float(wv.y >> 16);
+                    const float s0 = __ldcg(st), s1 = __ldcg(st + 1), s2 = __ldcg(st + 2);
+                    const float z = fmaf(s0, w0, fmaf(s1, w1, fmaf(s2, w2, v * w3)));
+                    st[0] = s1; st[1] = s2; st[2] = v;
+                    out[row] = fast_silu(z);
+                    break;
+                }
+                case INSG_EPI_BETA: out[row] = fast_sigmoid(v); break;
+                case INSG_EPI_DECAY: {
+                    const float z = v + bf16_bits_to_float(s.dt_bias[row]);
+                    const float soft = z > 20.f ? z : log1pf(__expf(z));
+                    out[row] = -__expf(s.A_log[row]) * soft;
+                    break;
+                }
+                case INSG_EPI_SWIGLU:
+                    if (c.mat == 0) gate_val = v;
+                    else out[row] = fast_silu(gate_val) * v;
+                    break;
+                case INSG_EPI_LOGITS:
+                    out[row] = v;
+                    if (v > best || (v == best && row < best_idx)) { best = v; best_idx = row; }
+                    break;
+                default: break;
+                }
             }
         }
-        parity ^= 1;
     };
 
     while (cur.valid) {
-        Cursor n1 = cursor_next(p, cur, nchunk, nkb);
+        Cursor n1 = cursor_next(p, cur, nchunk, nkb, stride);
         if (n1.valid) load_chunk<UNR>(B, n1, kb0, kb1, lane);
         compute_chunk<DEQ, UNR, M>(A, cur, kb0, kb1, xs, xstride, bactive, t, piece, acc);
         if (cur.chunk == nchunk - 1) finish(cur);
         if (!n1.valid) break;
-        Cursor n2 = cursor_next(p, n1, nchunk, nkb);
+        Cursor n2 = cursor_next(p, n1, nchunk, nkb, stride);
         if (n2.valid) load_chunk<UNR>(A, n2, kb0, kb1, lane);
         compute_chunk<DEQ, UNR, M>(B, n1, kb0, kb1, xs, xstride, bactive, t, piece, acc);
         if (n1.chunk == nchunk - 1) finish(n1);
@@ -411,26 +457,32 @@ __global__ void __launch_bounds__(kThreads) gemv_fused_kernel(const __grid_const
 
     // ---- arg-max over the rows this launch produced (lm_head) ----------------
     if (p.argmax_partial) {
-        if (warp == 0) {
+        float *sv = scratch + 16;                                  // [16]
+        int *si = reinterpret_cast<int *>(scratch + 32);          // [16]
 #pragma unroll
-            for (int mk = 8; mk; mk >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, best, mk);
-                const int oi = __shfl_xor_sync(0xffffffffu, best_idx, mk);
-                if (ov > best || (ov == best && oi < best_idx)) { best = ov; best_idx = oi; }
-            }
-            if (lane == 0) {
-                p.argmax_partial[blockIdx.x] = make_float2(best, __int_as_float(best_idx));
-                __threadfence();
-                const unsigned ticket = atomicAdd(p.ticket, 1u);
-                s_last = (ticket == gridDim.x - 1);
-            }
+        for (int mk = 8; mk; mk >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, mk);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_idx, mk);
+            if (ov > best || (ov == best && oi < best_idx)) { best = ov; best_idx = oi; }
+        }
+        if (lane == 0) { sv[warp] = (wk == 0) ? best : -3.402823466e38f; si[warp] = (wk == 0) ? best_idx : 0x7fffffff; }
+        __syncthreads();
+        if (tid == 0) {
+            float bv = sv[0];
+            int bi = si[0];
+            for (int w = 1; w < nwarps; w++)
+                if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+            p.argmax_partial[blockIdx.x] = make_float2(bv, __int_as_float(bi));
+            __threadfence();
+            const unsigned ticket = atomicAdd(p.ticket, 1u);
+            s_last = (ticket == gridDim.x - 1);
         }
         __syncthreads();
         if (s_last) {
             __threadfence();
             float bv = -3.402823466e38f;
             int bi = 0x7fffffff;
-            for (int i = tid; i < int(gridDim.x); i += kThreads) {
+            for (int i = tid; i < int(gridDim.x); i += int(blockDim.x)) {
                 const volatile float *e = reinterpret_cast<const volatile float *>(p.argmax_partial + i);
                 const float ev = e[0];
                 const int idx = __float_as_int(e[1]);
@@ -442,13 +494,11 @@ __global__ void __launch_bounds__(kThreads) gemv_fused_kernel(const __grid_const
                 const int oi = __shfl_xor_sync(0xffffffffu, bi, mk);
                 if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
             }
-            float *sv = scratch;
-            int *si = reinterpret_cast<int *>(scratch + 8);
             __syncthreads();
             if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
             __syncthreads();
             if (tid == 0) {
-                for (int w = 1; w < kWarps; w++)
+                for (int w = 1; w < nwarps; w++)
                     if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
                 *p.token_out = bi;
                 if (p.token_feedback) *p.token_feedback = bi;
@@ -529,7 +579,7 @@ __global__ void embed_kernel(const uint32_t *__restrict__ w, const uint8_t *__re
     pdl_wait();
     const int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= cols) return;
-    const int row = *row_ptr;
+    const int row = __ldcg(row_ptr);
     if (row < 0 || row >= rows) {
         out[k] = 0.f;
         return;
@@ -564,29 +614,31 @@ __global__ void dequant_kernel(const uint32_t *__restrict__ w, const uint8_t *__
 // ---- host side ------------------------------------------------------------------
 namespace {
 struct Tuning {
-    int deq = 0;          // 0 cvt, 1 shift/mask
-    int unr = 2;          // kblocks per prefetch step
-    int ctas_per_sm = 3;  // resident CTAs per SM the grid is sized for
+    int deq = 0;            // 0: cvt.e2m1x2, 1: shift/mask
+    int unr = 4;            // kblocks per prefetch step
+    int warps_per_sm = 16;  // warp slots per SM the decomposition is sized for
+    int warps_per_cta = 16; // CTA size in warps (1 CTA per SM at 16)
 } g_tune;
 
-template <int DEQ, int UNR, int M> int launch_variant(const GemvParams &p, int grid, size_t smem, cudaStream_t st, bool pdl)
+template <int DEQ, int UNR, int M>
+int launch_variant(const GemvParams &p, int grid, int threads, size_t smem, cudaStream_t st, bool pdl)
 {
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(gemv_fused_kernel<DEQ, UNR, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        attr_err = cudaFuncSetAttribute(gemv_fused_kernel<DEQ, UNR, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(gemv)");
-    return launch(gemv_fused_kernel<DEQ, UNR, M>, dim3(grid), dim3(kThreads), smem, st, pdl, p);
+    return launch(gemv_fused_kernel<DEQ, UNR, M>, dim3(grid), dim3(threads), smem, st, pdl, p);
 }
 
-template <int M> int dispatch(const GemvParams &p, int grid, size_t smem, cudaStream_t st, bool pdl)
+template <int M> int dispatch(const GemvParams &p, int grid, int threads, size_t smem, cudaStream_t st, bool pdl)
 {
     const int deq = g_tune.deq, unr = g_tune.unr;
-    if (deq == 0 && unr == 2) return launch_variant<0, 2, M>(p, grid, smem, st, pdl);
-    if (deq == 0 && unr == 4) return launch_variant<0, 4, M>(p, grid, smem, st, pdl);
-    if (deq == 1 && unr == 2) return launch_variant<1, 2, M>(p, grid, smem, st, pdl);
-    if (deq == 1 && unr == 4) return launch_variant<1, 4, M>(p, grid, smem, st, pdl);
+    if (deq == 0 && unr == 2) return launch_variant<0, 2, M>(p, grid, threads, smem, st, pdl);
+    if (deq == 0 && unr == 4) return launch_variant<0, 4, M>(p, grid, threads, smem, st, pdl);
+    if (deq == 1 && unr == 2) return launch_variant<1, 2, M>(p, grid, threads, smem, st, pdl);
+    if (deq == 1 && unr == 4) return launch_variant<1, 4, M>(p, grid, threads, smem, st, pdl);
     return fail(INSG_E_ARG, "unsupported GEMV tuning");
 }
 } // namespace
@@ -596,14 +648,10 @@ int gemv_tune(const char *key, int value)
     const std::string k = key;
     if (k == "gemv_deq") g_tune.deq = value;
     else if (k == "gemv_unr") g_tune.unr = value;
-    else if (k == "gemv_ctas_per_sm") g_tune.ctas_per_sm = value;
+    else if (k == "gemv_warps_per_sm") g_tune.warps_per_sm = std::max(1, std::min(value, 64));
+    else if (k == "gemv_warps_per_cta") g_tune.warps_per_cta = std::max(1, std::min(value, 16));
     else return fail(INSG_E_ARG, "unknown tuning key");
     return INSG_OK;
-}
-
-size_t gemv_smem_bytes(int cols, int M)
-{
-    return size_t(M) * 2 * (cols + 8) * sizeof(__half) + size_t(2) * kWarps * M * 16 * 4 + (64 + 256 + 32) * 4;
 }
 
 int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
@@ -611,10 +659,11 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
     if (!op || !op->in) return fail(INSG_E_ARG, "gemv: null operand");
     if (op->cols <= 0 || (op->cols & 127) || op->cols > 16384) return fail(INSG_E_SHAPE, "gemv: cols must be a multiple of 128, <= 16384");
     if (op->n_segments < 1 || op->n_segments > 4) return fail(INSG_E_SHAPE, "gemv: 1..4 segments");
-    if (M < 1 || M > 4) return fail(INSG_E_SHAPE, "gemv: 1..4 tokens per launch");
+    if (M != 1 && M != 2 && M != 4) return fail(INSG_E_SHAPE, "gemv: 1, 2 or 4 tokens per launch");
     if ((op->prologue == INSG_PRO_RMSNORM || op->prologue == INSG_PRO_GATED_RMSNORM) && !op->norm_w)
         return fail(INSG_E_ARG, "gemv: norm weight missing");
     if (op->prologue >= INSG_PRO_GATED_RMSNORM && !op->aux) return fail(INSG_E_ARG, "gemv: prologue operand missing");
+    if (op->prologue == INSG_PRO_GATED_RMSNORM && (op->cols & 1023)) return fail(INSG_E_SHAPE, "gemv: gated norm needs cols % 1024 == 0");
     GemvParams p = {};
     p.in = op->in; p.aux = op->aux; p.norm_w = op->norm_w; p.x_out = op->x_out;
     p.cols = op->cols; p.prologue = op->prologue; p.nseg = op->n_segments;
@@ -635,10 +684,22 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
         logits |= s.epilogue == INSG_EPI_LOGITS;
     }
     p.total_tiles = tiles;
-    const int grid = std::min(tiles, sm_count() * std::max(1, g_tune.ctas_per_sm));
+    // split K over as many warps as it takes to occupy the machine once (1, 2, 3, 4 or 8 per tile)
+    const int nkb = op->cols >> 7;
+    const int sms = sm_count();
+    const int slots = sms * g_tune.warps_per_sm;
+    const int r = slots / tiles;
+    int ksplit = r >= 8 ? 8 : r >= 4 ? 4 : r >= 3 ? 3 : r >= 2 ? 2 : 1;
+    while (ksplit > 1 && ksplit > nkb) ksplit = ksplit == 3 ? 2 : ksplit / 2;
+    const int gpc = std::max(1, g_tune.warps_per_cta / ksplit);
+    const int ctas_per_sm = std::max(1, g_tune.warps_per_sm / (ksplit * gpc));
+    const int grid = std::max(1, std::min((tiles + gpc - 1) / gpc, sms * ctas_per_sm));
+    p.ksplit = ksplit;
+    p.gpc = gpc;
     if (logits) {
         if (op->n_segments != 1) return fail(INSG_E_SHAPE, "gemv: the logits epilogue takes one segment");
         if (!op->argmax_scratch || !op->token_out) return fail(INSG_E_ARG, "gemv: arg-max scratch/token missing");
+        if (grid > 4096) return fail(INSG_E_LIMIT, "gemv: arg-max scratch holds 4096 partials");
         p.ticket = static_cast<unsigned *>(op->argmax_scratch);
         p.argmax_partial = reinterpret_cast<float2 *>(static_cast<uint8_t *>(op->argmax_scratch) + 64);
         p.token_out = op->token_out;
@@ -646,12 +707,13 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
         p.token_log = op->token_log;
         p.position_inout = op->position_inout;
     }
-    const size_t smem = gemv_smem_bytes(op->cols, M);
+    const size_t smem = size_t(M) * 2 * (op->cols + 8) * sizeof(__half) + size_t(gpc) * 2 * ksplit * M * 16 * 4 + 64 * 4;
+    const int threads = 32 * ksplit * gpc;
     const bool pdl = op->pdl != 0;
     switch (M) {
-    case 1: return dispatch<1>(p, grid, smem, st, pdl);
-    case 2: return dispatch<2>(p, grid, smem, st, pdl);
-    default: return dispatch<4>(p, grid, smem, st, pdl);
+    case 1: return dispatch<1>(p, grid, threads, smem, st, pdl);
+    case 2: return dispatch<2>(p, grid, threads, smem, st, pdl);
+    default: return dispatch<4>(p, grid, threads, smem, st, pdl);
     }
 }
 

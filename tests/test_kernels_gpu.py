@@ -53,7 +53,9 @@ def test_dequant_bit_exact_all_codes_and_scales(cuda):
     scales = np.arange(256, dtype=np.uint8).reshape(rows, 1)
     got = host(ops.dequant_mlx(dev(word), dev(scales)))
     want = orc.dequant_mlx(word, scales)
-    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    nan = np.isnan(want)  # 0 * Inf under scale byte 255: a NaN on both sides, payload bits are not specified
+    assert np.array_equal(np.isnan(got), nan) and nan.sum() == 2 * 2
+    assert np.array_equal(got.view(np.uint32)[~nan], want.view(np.uint32)[~nan])
     row = host(ops.get_row_mlx(dev(word), dev(scales), 131))
     assert np.array_equal(row.view(np.uint32), want[131].view(np.uint32))
 
@@ -387,7 +389,8 @@ def test_attention_step_sequence_vs_oracle(cuda, kv_bf16):
         orc.lib().orc_store_kv(k, v, kc_ref, vc_ref, pos)
         want = orc.gqa_decode(q, kc_ref, vc_ref, pos + 1)
         assert np.max(np.abs(out - want)) <= 5e-5, pos
-    assert np.max(np.abs(host(kc.float())[:70 * 1024] - kc_ref[:70 * 1024])) <= 1e-5
+    # fp32 cache: rounding only; bf16 cache: at most one bf16 ulp where the fp32 values straddle a rounding boundary
+    assert np.max(np.abs(host(kc.float())[:70 * 1024] - kc_ref[:70 * 1024])) <= (2.0 ** -7 * np.abs(kc_ref).max() if kv_bf16 else 1e-5)
 
 
 # -------------------------------------------------------------------- small ops

@@ -65,20 +65,32 @@ def test_multi_token_decode_vs_oracle(cuda, golden_ckpt, graph, pdl):
         assert e.launch_count > 0
 
 
-def test_generate_equals_decode_token_loop(cuda, golden_ckpt):
-    with small_engine(golden_ckpt[1]) as a, small_engine(golden_ckpt[1]) as b:
+def _run_tokens(idx, graph, pdl, use_generate):
+    with small_engine(idx, use_graph=graph, use_pdl=pdl) as e:
         for t in (3, 9):
-            a.forward_token(t), b.forward_token(t)
-        first = a.logits_argmax()
-        assert first == b.logits_argmax()
-        gen = a.generate(first, 20)
-        loop, t = [], first
-        for _ in range(20):
-            t = b.decode_token(t)
-            loop.append(t)
-        assert gen == loop
-        assert a.position == b.position == 22
-        assert np.array_equal(a.read("hidden"), b.read("hidden"))  # same kernels, same order: bit-identical
+            e.forward_token(t)
+        first = e.logits_argmax()
+        if use_generate:
+            toks = e.generate(first, 20)
+        else:
+            toks, t = [], first
+            for _ in range(20):
+                t = e.decode_token(t)
+                toks.append(t)
+        assert e.position == 22
+        return toks, e.read("hidden"), e.read("delta_state", 3 * 32 * 128 * 128)
+
+
+def test_generate_equals_decode_token_loop_bitwise(cuda, golden_ckpt):
+    """Graph replay, programmatic dependent launch and device-side token feedback must not change a single bit:
+    the kernels and their order are the same in every mode."""
+    base = _run_tokens(golden_ckpt[1], False, False, False)
+    for graph, pdl, gen in [(False, False, False), (False, True, False), (True, False, False), (True, True, False),
+                            (True, True, True), (False, True, True), (True, True, True)]:
+        toks, hidden, state = _run_tokens(golden_ckpt[1], graph, pdl, gen)
+        assert toks == base[0], (graph, pdl, gen)
+        assert np.array_equal(hidden, base[1]), (graph, pdl, gen, float(np.abs(hidden - base[1]).max()))
+        assert np.array_equal(state, base[2]), (graph, pdl, gen)
 
 
 def test_kv_bf16_and_accurate_trig_modes(cuda, golden_ckpt):
@@ -99,8 +111,7 @@ def test_engine_errors_follow_reference(cuda, golden_ckpt):
 
     with small_engine(golden_ckpt[1], max_context=2) as e:
         with pytest.raises(InsigniaError, match="not a DeltaNet layer"):
-            e._h and __import__("insignia_b200._lib", fromlist=["x"]).check(
-                __import__("insignia_b200._lib", fromlist=["x"]).lib().insg_engine_layer(e._h, 32))
+            e.layer(32)
         with pytest.raises(InsigniaError, match="token out of range"):
             e.forward_token(248320)
         with pytest.raises(InsigniaError, match="token out of range"):
