@@ -282,6 +282,11 @@ INSG_API int insg_engine_mtp_draft(insg_engine *e, int token);
  * arg-max back in, `count` times; writes the `count` produced ids to out_tokens (host).
  * Synchronises once at the end.  No reference counterpart (its loop is src/generate_ids.cu:4). */
 INSG_API int insg_engine_generate(insg_engine *e, int first_token, int count, int *out_tokens /* host */);
+/* One token step run eagerly with a CUDA-event pair around every launch (no dependent-launch overlap):
+ * ms[4], bytes[4], launches[4] (host) receive, per kernel class (0 fused GEMV, 1 DeltaNet step,
+ * 2 attention, 3 embedding), the summed durations, the algorithmic bytes and the launch counts.
+ * Advances the position like insg_engine_forward_token.  Synchronises.  No reference counterpart. */
+INSG_API int insg_engine_profile_token(insg_engine *e, int token, float *ms, uint64_t *bytes, int *launches);
 INSG_API int insg_engine_position(insg_engine *e);
 INSG_API int insg_engine_set_position(insg_engine *e, int position);
 /* Re-zeroes the recurrent state and position (what constructing a fresh DecodeWorkspace does). */

@@ -18,6 +18,8 @@
 
 namespace insignia {
 
+struct StepProfile;
+
 // Additive knobs; the defaults reproduce the reference engine's behaviour.
 struct DecodeOptions {
     bool kv_bf16 = false;          // false: fp32 KV cache as the reference (src/decode.cu:10); true: bf16 cache
@@ -76,6 +78,9 @@ public:
     std::vector<int> generate(int first_token, int count);
     uint64_t launch_count() const noexcept { return launches_; }
     cudaStream_t execution_stream();
+    // Additive: one token step run eagerly with an event pair around every launch.  Index 0: fused GEMV,
+    // 1: DeltaNet step, 2: attention, 3: embedding.  ms = summed durations, bytes = algorithmic bytes moved.
+    void profile_token(int token, float ms[4], uint64_t bytes[4], int launches[4]);
     struct Plan; // resolved weight pointers + captured graph (opaque)
 
 private:
@@ -91,6 +96,7 @@ private:
     DecodeWorkspace &x_;
     std::unique_ptr<Plan> plan_;
     uint64_t launches_{};
+    StepProfile *prof_{};
     bool fused_token_valid_{};
 };
 

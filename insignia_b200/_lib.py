@@ -80,6 +80,7 @@ SIGNATURES = {
     "insg_engine_decode_token": (i32, [vp, i32]),
     "insg_engine_mtp_draft": (i32, [vp, i32]),
     "insg_engine_generate": (i32, [vp, i32, i32, C.POINTER(i32)]),
+    "insg_engine_profile_token": (i32, [vp, i32, vp, vp, vp]),
     "insg_engine_position": (i32, [vp]),
     "insg_engine_set_position": (i32, [vp, i32]),
     "insg_engine_reset": (i32, [vp]),

@@ -66,6 +66,13 @@ class Engine:
         check(_lib.lib().insg_engine_generate(self._h, first_token, count, buf))
         return list(buf)
 
+    def profile_token(self, token: int) -> dict:
+        """One eager token step with per-launch CUDA events; per kernel class: ms, algorithmic bytes, launches."""
+        ms, by, ln = (C.c_float * 4)(), (C.c_uint64 * 4)(), (C.c_int * 4)()
+        check(_lib.lib().insg_engine_profile_token(self._h, token, ms, by, ln))
+        names = ("gemv", "deltanet", "attention", "embed")
+        return {n: {"ms": ms[i], "bytes": by[i], "launches": ln[i]} for i, n in enumerate(names)}
+
     @property
     def position(self) -> int:
         return _lib.lib().insg_engine_position(self._h)

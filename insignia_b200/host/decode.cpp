@@ -180,17 +180,55 @@ struct Loader {
 } // namespace
 
 // --------------------------------------------------------------- enqueue helpers
+struct StepProfile {
+    struct Ev {
+        cudaEvent_t start, stop;
+        int cls;
+        uint64_t bytes;
+    };
+    std::vector<Ev> events;
+};
+
 namespace {
 struct Ctx {
     DecodeWorkspace &x;
     cudaStream_t st;
     bool pdl;
     uint64_t &launches;
+    StepProfile *prof;
 };
+
+// Brackets one launch with events when a profile is being taken (never during graph capture).
+struct Timed {
+    StepProfile *p;
+    cudaStream_t st;
+    Timed(Ctx &c, int cls, uint64_t bytes) : p(c.prof), st(c.st)
+    {
+        if (!p) return;
+        cudaEvent_t a, b;
+        cuda_check(cudaEventCreate(&a), "event");
+        cuda_check(cudaEventCreate(&b), "event");
+        p->events.push_back({a, b, cls, bytes});
+        cuda_check(cudaEventRecord(a, st), "event record");
+    }
+    ~Timed()
+    {
+        if (p) cudaEventRecord(p->events.back().stop, st);
+    }
+};
+
+uint64_t gemv_bytes(const insg_gemv_op &op)
+{
+    uint64_t b = 0;
+    for (int i = 0; i < op.n_segments; i++)
+        b += uint64_t(op.seg[i].rows) * op.cols * 17 / 32 * (op.seg[i].epilogue == INSG_EPI_SWIGLU ? 2 : 1);
+    return b;
+}
 
 void run_gemv(Ctx &c, insg_gemv_op &op)
 {
     op.pdl = c.pdl ? 1 : 0;
+    Timed t(c, 0, gemv_bytes(op));
     insg_check(insg_gemv_fused(&op, c.st));
     c.launches++;
 }
@@ -249,9 +287,12 @@ static void enqueue_delta_block(Ctx &c, const Qwen35Decode::Plan::Block &b, int 
     in.seg[3] = seg(b.b, x.b, INSG_EPI_BETA);
     run_gemv(c, in);
 
-    insg_check(insg_deltanet_decode(x.delta_state + size_t(di) * 32 * 128 * 128, x.qkv, x.qkv + 2048, x.qkv + 4096, x.a, x.b, x.core,
-                                    c.pdl ? 1 : 0, c.st));
-    c.launches++;
+    {
+        Timed t(c, 1, uint64_t(2) * 32 * 128 * 128 * 4); // state read + write
+        insg_check(insg_deltanet_decode(x.delta_state + size_t(di) * 32 * 128 * 128, x.qkv, x.qkv + 2048, x.qkv + 4096, x.a, x.b,
+                                        x.core, c.pdl ? 1 : 0, c.st));
+        c.launches++;
+    }
 
     insg_gemv_op out = {};
     out.in = x.core;
@@ -298,8 +339,11 @@ static void enqueue_attention_block(Ctx &c, const Qwen35Decode::Plan::Block &b, 
     at.scratch = x.attn_scratch;
     at.scratch_bytes = insg_gqa_scratch_bytes(x.max_context);
     at.pdl = c.pdl ? 1 : 0;
-    insg_check(insg_attention_step(&at, c.st));
-    c.launches++;
+    {
+        Timed t(c, 2, uint64_t(x.position + 1) * 1024 * 2 * (x.options.kv_bf16 ? 2 : 4)); // K and V rows read
+        insg_check(insg_attention_step(&at, c.st));
+        c.launches++;
+    }
 
     insg_gemv_op o = {};
     o.in = x.core;
@@ -372,8 +416,10 @@ void Qwen35Decode::enqueue_embed()
         if (p.embed.cols != kHidden) throw std::runtime_error("unexpected matrix shape: " + base);
         p.embed_ready = true;
     }
+    Ctx c{x_, p.stream, x_.options.use_pdl && !prof_, launches_, prof_};
+    Timed t(c, 3, uint64_t(kHidden) * 17 / 32);
     insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
-                                x_.hidden, x_.d_token, p.embed.rows, kHidden, x_.options.use_pdl ? 1 : 0, p.stream));
+                                x_.hidden, x_.d_token, p.embed.rows, kHidden, c.pdl ? 1 : 0, p.stream));
     launches_++;
 }
 
@@ -385,7 +431,7 @@ void Qwen35Decode::enqueue_delta(int l)
         Loader L{w_, p.pinned};
         load_delta(L, std::string(kLM) + ".model.layers." + std::to_string(l), b);
     }
-    Ctx c{x_, p.stream, x_.options.use_pdl, launches_};
+    Ctx c{x_, p.stream, x_.options.use_pdl && !prof_, launches_, prof_};
     enqueue_delta_block(c, b, l - l / 4);
 }
 
@@ -399,7 +445,7 @@ void Qwen35Decode::enqueue_attention(int l)
     }
     const size_t esz = x_.options.kv_bf16 ? 2 : 4;
     const size_t off = size_t(l / 4) * x_.max_context * 1024 * esz;
-    Ctx c{x_, p.stream, x_.options.use_pdl, launches_};
+    Ctx c{x_, p.stream, x_.options.use_pdl && !prof_, launches_, prof_};
     enqueue_attention_block(c, b, reinterpret_cast<uint8_t *>(x_.kv_keys) + off, reinterpret_cast<uint8_t *>(x_.kv_values) + off, 0);
 }
 
@@ -413,7 +459,7 @@ void Qwen35Decode::enqueue_head()
         if (p.lm_head.cols != kHidden || p.lm_head.rows < x_.options.vocab) throw std::runtime_error("unexpected matrix shape: language_model.lm_head");
         p.head_ready = true;
     }
-    Ctx c{x_, p.stream, x_.options.use_pdl, launches_};
+    Ctx c{x_, p.stream, x_.options.use_pdl && !prof_, launches_, prof_};
     insg_gemv_op op = {};
     op.in = x_.hidden;
     op.norm_w = p.final_norm;
@@ -551,6 +597,36 @@ std::vector<int> Qwen35Decode::generate(int first_token, int count)
     return out;
 }
 
+void Qwen35Decode::profile_token(int token, float ms[4], uint64_t bytes[4], int launches[4])
+{
+    if (token < 0 || token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
+    if (x_.position >= x_.max_context) throw std::runtime_error("KV cache full");
+    Plan &p = plan();
+    StepProfile prof;
+    sync_scalars(token);
+    prof_ = &prof;
+    try {
+        enqueue_token_step(); // eager, one event pair per launch, no dependent-launch overlap
+    } catch (...) {
+        prof_ = nullptr;
+        throw;
+    }
+    prof_ = nullptr;
+    x_.position++;
+    fused_token_valid_ = true;
+    cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
+    for (int i = 0; i < 4; i++) { ms[i] = 0.f; bytes[i] = 0; launches[i] = 0; }
+    for (auto &e : prof.events) {
+        float t = 0.f;
+        cudaEventElapsedTime(&t, e.start, e.stop);
+        ms[e.cls] += t;
+        bytes[e.cls] += e.bytes;
+        launches[e.cls]++;
+        cudaEventDestroy(e.start);
+        cudaEventDestroy(e.stop);
+    }
+}
+
 int Qwen35Decode::mtp_draft(int token)
 {
     if (token < 0 || token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
@@ -576,7 +652,7 @@ int Qwen35Decode::mtp_draft(int token)
     insg_check(insg_rmsnorm_bf16(x_.hidden, p.mtp_norm_h, nullptr, x_.qkv + kHidden, 1, kHidden, 0, p.stream));
     insg_check(insg_bf16_gemv(p.mtp_fc, x_.qkv, x_.hidden, kHidden, 2 * kHidden, 0, p.stream)); // overwrites the residual, as the reference
     launches_ += 4;
-    Ctx c{x_, p.stream, pdl, launches_};
+    Ctx c{x_, p.stream, pdl, launches_, nullptr};
     enqueue_attention_block(c, p.mtp, x_.mtp_keys, x_.mtp_values, -1); // rotary position / cache row position-1, position rows attended
 
     insg_gemv_op op = {};

@@ -145,6 +145,14 @@ int insg_engine_generate(insg_engine *e, int first_token, int count, int *out_to
         return int(INSG_OK);
     });
 }
+int insg_engine_profile_token(insg_engine *e, int token, float *ms, uint64_t *bytes, int *launches)
+{
+    return guarded(e, [&] {
+        if (!ms || !bytes || !launches) return insg::fail(INSG_E_ARG, "null output");
+        e->dec->profile_token(token, ms, bytes, launches);
+        return int(INSG_OK);
+    });
+}
 int insg_engine_position(insg_engine *e) { return e ? e->ws->position : INSG_E_ARG; }
 int insg_engine_set_position(insg_engine *e, int position)
 {

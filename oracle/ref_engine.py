@@ -1,9 +1,9 @@
-"""ctypes access to oracle/_ref/libinsignia_ref.so: the reference's own CUDA engine, compiled
+"""TEST INFRASTRUCTURE ONLY.  ctypes access to oracle/_ref/libinsignia_ref.so: the reference's own CUDA engine, compiled
 unmodified for sm_100a by oracle/Makefile.  Used by the GPU tests as a second checker."""
 import ctypes as C
 import os
 
-_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libinsignia_ref.so")
+_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref", "libinsignia_ref.so")
 _lib = None
 
 

@@ -7,7 +7,8 @@ import pytest
 
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
 from oracle import oracle as orc  # noqa: E402
-from tests import fixtures as fx, refengine  # noqa: E402
+from oracle import ref_engine as refengine  # noqa: E402
+from tests import fixtures as fx  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")

@@ -8,7 +8,7 @@ import pytest
 
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
 from oracle import oracle as orc  # noqa: E402
-from tests import refengine  # noqa: E402
+from oracle import ref_engine as refengine  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
