@@ -182,6 +182,20 @@ INSG_API size_t insg_gqa_scratch_bytes(int tokens);
 INSG_API int insg_gqa_decode(const float *q, const void *k_cache, const void *v_cache, float *out, int tokens,
                              int kv_dtype, void *scratch, size_t scratch_bytes, insg_stream_t stream);
 
+/* The same attention as insg_gqa_decode for callers that must not allocate device memory and have
+ * no scratch buffer to hand over: code running inside a stream capture or a real-time serving
+ * loop where cudaMalloc is forbidden or would synchronise, and plug-in hosts whose allocator the
+ * library may not touch.  The split partials go to a fixed array inside the library image
+ * (about 600 KB per GPU that loads the library, kept until the process exits), so there is no
+ * scratch argument.  Limits and rules: at most 262144 cached tokens (INSG_E_LIMIT beyond);
+ * every call on a device shares that one array, so two calls that overlap on the GPU (different
+ * streams, or different threads) race -- serialise them; the first call on each device looks the
+ * array's address up and should therefore be made before any stream capture begins.  Calls no
+ * cudaMalloc / cudaFree or other allocating routine.  No counterpart in the reference, whose
+ * gqa_decode keeps its scores in dynamic shared memory (src/attention.cu:4-5). */
+INSG_API int insg_gqa_decode_noalloc(const float *q, const void *k_cache, const void *v_cache, float *out, int tokens,
+                                     int kv_dtype, insg_stream_t stream);
+
 /* Fused attention step of the engine: per-head RMSNorm of q and k (bf16 weights,
  * eps 1e-6), partial RoPE on dims 0..63 at *position (theta 1e7, rotate-half,
  * skipped at position 0), store of k,v at cache row *position, then the same

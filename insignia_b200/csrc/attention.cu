@@ -15,6 +15,8 @@
 #include "common.cuh"
 #include "host_util.h"
 
+#include <mutex>
+
 namespace insg {
 
 constexpr int kAtThreads = 256;
@@ -289,11 +291,58 @@ int attn_plain_launch(const float *q, const void *kc, const void *vc, float *out
     return kv_dtype == INSG_KV_BF16 ? launch_attn<true, false>(p, st, false) : launch_attn<false, false>(p, st, false);
 }
 
+// ---- allocation-free variant -----------------------------------------------------
+// Scratch for insg_gqa_decode_noalloc: lives in the library image, one copy per GPU that loads it
+// (about 600 KB, held until the process exits).  In host code the symbol name is only a handle, so
+// the device address is looked up once per device with cudaGetSymbolAddress and handed to the kernel.
+constexpr int kNoAllocMaxTokens = 262144; // the model's longest context
+constexpr size_t kNoAllocScratchBytes = 64 + size_t(4) * kSplits * kPartFloats * sizeof(float);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+namespace {
+std::mutex g_noalloc_mutex;
+void *g_noalloc_ptr[64] = {nullptr};
+} // namespace
+
+// Device address of the static scratch on the current device (first call per device resolves it).
+static int noalloc_scratch(void **out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(INSG_E_LIMIT, "gqa_decode_noalloc: device ordinal beyond 63");
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static attention scratch)");
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return INSG_OK;
+}
+
 } // namespace insg
 
 using namespace insg;
 
 extern "C" {
+
+int insg_gqa_decode_noalloc(const float *q, const void *k_cache, const void *v_cache, float *out, int tokens, int kv_dtype,
+                            insg_stream_t stream)
+{
+    if (tokens <= 0) return INSG_OK;
+    if (tokens > kNoAllocMaxTokens) return fail(INSG_E_LIMIT, "gqa_decode_noalloc: more than 262144 cached tokens");
+    if (!q || !k_cache || !v_cache || !out) return fail(INSG_E_ARG, "gqa_decode_noalloc: null pointer");
+    if (kv_dtype != INSG_KV_F32 && kv_dtype != INSG_KV_BF16) return fail(INSG_E_ARG, "gqa_decode_noalloc: bad kv dtype");
+    void *scratch = nullptr;
+    const int rc = noalloc_scratch(&scratch);
+    if (rc != INSG_OK) return rc;
+    // the per-kv-head arrival counters must start at zero; an earlier call that was cut short could have left them set
+    cudaError_t e = cudaMemsetAsync(scratch, 0, 64, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(static attention scratch)");
+    return attn_plain_launch(q, k_cache, v_cache, out, tokens, kv_dtype, scratch, stream);
+}
 
 size_t insg_gqa_scratch_bytes(int tokens)
 {

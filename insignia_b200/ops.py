@@ -119,6 +119,15 @@ def gqa_decode(q, k_cache, v_cache, tokens, scratch=None):
     return out
 
 
+def gqa_decode_noalloc(q, k_cache, v_cache, tokens):
+    """Same result as :func:`gqa_decode` without a scratch buffer: the partials live in a fixed array inside the
+    library (one per GPU), so nothing is allocated; calls that overlap on the GPU must be serialised by the caller."""
+    kv = KV_BF16 if k_cache.dtype == torch.bfloat16 else KV_F32
+    out = torch.empty(16 * 256, dtype=torch.float32, device=q.device)
+    check(_lib.lib().insg_gqa_decode_noalloc(_p(q), _p(k_cache), _p(v_cache), _p(out), tokens, kv, _stream()))
+    return out
+
+
 def attention_step(qraw, k_raw, v, q_w, k_w, k_cache, v_cache, position, max_context, scratch, position_offset=0,
                    fast_trig=True, pdl=False):
     op = AttnOp()
