@@ -38,7 +38,7 @@ enum {
 
 INSG_API const char *insg_last_error(void);  /* host string, thread-local */
 INSG_API int insg_version(void);
-/* Kernel tuning knobs ("gemv_deq" 0|1, "gemv_unr" 2|4, "gemv_ctas_per_sm"); process-wide, for benchmarking. */
+/* Kernel tuning knob ("gemv_unr": 2 or 4 records per prefetch chunk); process-wide, for benchmarking. */
 INSG_API int insg_tune_set(const char *key /* host */, int value);
 
 /* ------------------------------------------------------------------ MXFP4 */
@@ -147,10 +147,14 @@ typedef struct insg_gemv_op {
     int *token_feedback;
     int *token_log;
     int *position_inout;
+    /* Scratch for tiles cut by a CTA boundary (>= insg_gemv_splitk_scratch_bytes(), zeroed once, left zeroed by
+     * every call).  NULL selects a fixed array inside the library: then calls that overlap on one GPU race. */
+    void *splitk_scratch;
     int pdl;                  /* 1: launch with programmatic dependent launch          */
 } insg_gemv_op;
 
 INSG_API size_t insg_gemv_argmax_scratch_bytes(void);
+INSG_API size_t insg_gemv_splitk_scratch_bytes(void);
 INSG_API int insg_gemv_fused(const insg_gemv_op *op /* host */, insg_stream_t stream);
 
 /* ------------------------------------------------------------ DeltaNet */

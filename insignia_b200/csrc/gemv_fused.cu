@@ -1,0 +1,696 @@
+// Fused MXFP4 weight-streaming GEMV for sm_100a (batch-1 decode, up to 4 tokens per launch).
+//
+// Contraction (reference: src/mxfp4.cu:41-66): y[r] = sum_k lut[code(r,k)] * 2^(s(r,k/32)-127) * x[k].
+//
+// The path is HBM-bound: 17 bytes arrive per 32 weights, so the kernel is built around the byte
+// stream, not around the arithmetic:
+//   * weights come from the tile-interleaved copy made by insg_mxfp4_repack: one (16 rows x 128 k)
+//     record is 1088 contiguous bytes, read by a warp with two coalesced 512-byte loads + 64 scale
+//     bytes (ld.global.nc, no L1 allocation); every warp keeps two chunks of UNR records in flight,
+//     both issued BEFORE the programmatic-dependent-launch wait so they overlap the previous kernel;
+//   * work is cut "stream-K": the launch's records form one linear sequence (segment, tile, matrix,
+//     k-block) that is divided evenly over the CTAs (one per SM) and then over the 16 warps of a CTA,
+//     so every warp streams the same number of bytes whatever the matrix shape.  A warp folds each
+//     (tile, matrix) run it finishes into a shared-memory slot; after one CTA barrier the slots are
+//     summed in warp order; a tile cut by a CTA boundary is finished by whichever of its two CTAs
+//     arrives last at a ticket in global scratch, adding the two halves in a fixed order.  Nothing
+//     spins and the result does not depend on scheduling;
+//   * E2M1 nibbles become fp16 pairs with cvt.rn.f16x2.e2m1x2 (exact); the multiply-adds run on
+//     mma.sync.m16n8k16 (fp16 in, fp32 accumulate) purely as a cheap FMA engine.  The fp32 activation
+//     is split into two fp16 pieces (hi + lo * 2^-11 after an exact power-of-two pre-scale) so the
+//     products keep ~22 bits of x; the 8 columns of the MMA's B operand hold (4 scale groups) x
+//     (hi, lo): thread t of a quad owns scale group t of the 128-wide k-block, so accumulator
+//     columns separate the groups and the E8M0 scale is applied once per (row, group) in fp32;
+//   * the elementwise kernels around the GEMV are fused in: RMSNorm / gated RMSNorm / sigmoid-gate
+//     prologues on the activation, residual / conv+SiLU / decay / beta / SwiGLU / logits+arg-max
+//     epilogues on the rows.
+#include "common.cuh"
+#include "host_util.h"
+
+#include <algorithm>
+#include <mutex>
+
+namespace insg {
+
+constexpr int kRec = 1088;  // bytes per (16-row tile, 128-k block) record
+constexpr int kWarps = 16;  // warps per CTA, one CTA per SM
+constexpr int kThreads = kWarps * 32;
+constexpr int kMaxVec = 6;  // float4 per thread the prologue holds in registers (cols <= 12288)
+constexpr float kLoScale = 1.0f / 2048.0f;
+
+struct SegDev {
+    const uint8_t *packed, *packed2;
+    float *out;
+    float *conv_state;
+    const uint16_t *conv_w;
+    const float *A_log;
+    const uint16_t *dt_bias;
+    int tm_begin; // first (tile, matrix) index of the segment
+    int nmat;     // 1, or 2 for the gate/up pair of SwiGLU
+    int epilogue, rows;
+};
+
+struct GemvParams {
+    const float *in, *aux;
+    const uint16_t *norm_w;
+    float *x_out;
+    int cols, nkb, prologue, nseg;
+    int total_units, total_tm, slots; // records in the launch, (tile, matrix) runs, shared slots per warp
+    SegDev seg[4];
+    float2 *argmax_partial; // [grid] (value, index as int bits)
+    unsigned *argmax_ticket;
+    int *token_out, *token_feedback, *token_log, *position_inout;
+    float *sk_part;       // [grid][2 sides][2 matrices][4 tokens][16 rows]
+    unsigned *sk_ticket;  // [grid]
+};
+
+__device__ __forceinline__ void dequant8(uint32_t q, uint32_t (&h)[4])
+{
+    // register b holds elements (2b, 2b+1) of the 8-nibble word at their true value
+    asm("{\n"
+        " .reg .b8 b0, b1, b2, b3;\n"
+        " mov.b32 {b0, b1, b2, b3}, %4;\n"
+        " cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        " cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        " cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        " cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}\n"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(q));
+}
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Position in the linear record sequence.
+struct UnitIt {
+    int u;   // record index in the launch
+    int tm;  // (tile, matrix) run
+    int kb;  // k-block inside the run
+    const uint8_t *ptr;
+};
+
+__device__ __forceinline__ int seg_of(const GemvParams &p, int tm)
+{
+    int s = 0;
+#pragma unroll
+    for (int i = 1; i < 4; i++)
+        if (i < p.nseg && tm >= p.seg[i].tm_begin) s = i;
+    return s;
+}
+
+__device__ __forceinline__ const uint8_t *run_base(const GemvParams &p, int tm)
+{
+    const SegDev &s = p.seg[seg_of(p, tm)];
+    const int local = tm - s.tm_begin;
+    if (s.nmat == 2) return ((local & 1) ? s.packed2 : s.packed) + size_t(local >> 1) * p.nkb * kRec;
+    return s.packed + size_t(local) * p.nkb * kRec;
+}
+
+__device__ __forceinline__ void it_set(const GemvParams &p, UnitIt &it, int u)
+{
+    it.u = u;
+    it.tm = u / p.nkb;
+    it.kb = u - it.tm * p.nkb;
+    it.ptr = u < p.total_units ? run_base(p, it.tm) + size_t(it.kb) * kRec : nullptr;
+}
+
+__device__ __forceinline__ void it_next(const GemvParams &p, UnitIt &it)
+{
+    it.u++;
+    it.kb++;
+    it.ptr += kRec;
+    if (it.kb == p.nkb) {
+        it.kb = 0;
+        it.tm++;
+        it.ptr = it.u < p.total_units ? run_base(p, it.tm) : nullptr;
+    }
+}
+
+template <int UNR> struct Chunk {
+    uint4 wa[UNR], wb[UNR];
+    uint32_t sc[UNR];
+};
+
+// Issues the loads of the next UNR records (those below `end`) and advances the iterator past them.
+template <int UNR> __device__ __forceinline__ void load_chunk(const GemvParams &p, Chunk<UNR> &b, UnitIt &it, int end, int lane)
+{
+#pragma unroll
+    for (int j = 0; j < UNR; j++) {
+        if (it.u < end) {
+            b.wa[j] = ldg_stream(it.ptr + lane * 16);
+            b.wb[j] = ldg_stream(it.ptr + 512 + lane * 16);
+            b.sc[j] = ldg_stream_u16(it.ptr + 1024 + lane * 2);
+            it_next(p, it);
+        } else {
+            b.wa[j] = make_uint4(0, 0, 0, 0);
+            b.wb[j] = make_uint4(0, 0, 0, 0);
+            b.sc[j] = 0;
+        }
+    }
+}
+
+__device__ __forceinline__ float block_sum16(float v, float *scratch)
+{
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < kWarps; i++) t += scratch[i];
+    return t;
+}
+__device__ __forceinline__ float block_max16(float v, float *scratch)
+{
+    v = warp_max(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = scratch[0];
+#pragma unroll
+    for (int i = 1; i < kWarps; i++) t = fmaxf(t, scratch[i]);
+    return t;
+}
+
+// ---- activation prologue: fp32 vector -> two fp16 pieces in shared memory ----
+// One pass: the vector is read once (ld.global.cg: under programmatic dependent launch this CTA may
+// have been resident, and its L1 filled, before the producer wrote it), kept in registers through
+// the reductions, and written as hi/lo halves.  Returns 1/alpha, which undoes the pre-scale.
+__device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, float *scratch)
+{
+    const int cols = p.cols, tid = threadIdx.x, lane = tid & 31;
+    const float *in = p.in + size_t(m) * cols;
+    const int nvec = cols >> 2;
+    float4 v[kMaxVec];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxVec; j++) {
+        const int i = tid + j * kThreads;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < nvec) v[j] = __ldcg(reinterpret_cast<const float4 *>(in) + i);
+        ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
+    }
+    float inv_rms = 1.f;
+    if (p.prologue == INSG_PRO_RMSNORM) inv_rms = rsqrtf(block_sum16(ss, scratch) / float(cols) + 1e-6f);
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxVec; j++) {
+        const int i = tid + j * kThreads;
+        if (i < nvec) { // warp-uniform: nvec is a multiple of 32
+            float4 x = v[j];
+            const int k = i << 2;
+            switch (p.prologue) {
+            case INSG_PRO_RMSNORM: {
+                const uint2 wv = reinterpret_cast<const uint2 *>(p.norm_w)[i];
+                x.x = x.x * inv_rms * bf16_bits_to_float(wv.x & 0xffff);
+                x.y = x.y * inv_rms * bf16_bits_to_float(wv.x >> 16);
+                x.z = x.z * inv_rms * bf16_bits_to_float(wv.y & 0xffff);
+                x.w = x.w * inv_rms * bf16_bits_to_float(wv.y >> 16);
+                break;
+            }
+            case INSG_PRO_GATED_RMSNORM: {
+                // a warp covers one 128-wide head per j (32 lanes x float4)
+                const float hs = warp_sum(fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w))));
+                const float inv = rsqrtf(hs / 128.f + 1e-6f);
+                const uint2 wv = reinterpret_cast<const uint2 *>(p.norm_w)[lane];
+                const float4 z = __ldcg(reinterpret_cast<const float4 *>(p.aux + size_t(m) * cols) + i);
+                x.x = x.x * inv * bf16_bits_to_float(wv.x & 0xffff) * fast_silu(z.x);
+                x.y = x.y * inv * bf16_bits_to_float(wv.x >> 16) * fast_silu(z.y);
+                x.z = x.z * inv * bf16_bits_to_float(wv.y & 0xffff) * fast_silu(z.z);
+                x.w = x.w * inv * bf16_bits_to_float(wv.y >> 16) * fast_silu(z.w);
+                break;
+            }
+            case INSG_PRO_SIGMOID_GATE: {
+                const float4 g = __ldcg(reinterpret_cast<const float4 *>(p.aux + size_t(m) * cols) + i);
+                x.x *= fast_sigmoid(g.x); x.y *= fast_sigmoid(g.y); x.z *= fast_sigmoid(g.z); x.w *= fast_sigmoid(g.w);
+                break;
+            }
+            case INSG_PRO_SIGMOID_GATE_HEAD0: {
+                const float g = fast_sigmoid(__ldcg(p.aux + size_t(m) * 2 * cols + (k >> 8) * 512 + 256));
+                x.x *= g; x.y *= g; x.z *= g; x.w *= g;
+                break;
+            }
+            case INSG_PRO_SIGMOID_GATE_QPROJ: {
+                const float4 g =
+                    __ldcg(reinterpret_cast<const float4 *>(p.aux + size_t(m) * 2 * cols + (k >> 8) * 512 + 256 + (k & 255)));
+                x.x *= fast_sigmoid(g.x); x.y *= fast_sigmoid(g.y); x.z *= fast_sigmoid(g.z); x.w *= fast_sigmoid(g.w);
+                break;
+            }
+            default: break;
+            }
+            v[j] = x;
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
+            if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out + size_t(m) * cols)[i] = x;
+        }
+    }
+    const float tmax = block_max16(amax, scratch);
+    // alpha = 2^(12 - floor(log2(max))) puts the largest element in [2^12, 2^13): fp16 holds it with room to spare
+    int eb = int((__float_as_uint(tmax) >> 23) & 0xffu);
+    eb = min(max(eb, 20), 240);
+    const float alpha = __uint_as_float(uint32_t(266 - eb) << 23);
+    __half *hi = xs + size_t(m * 2) * xstride, *lo = hi + xstride;
+#pragma unroll
+    for (int j = 0; j < kMaxVec; j++) {
+        const int i = tid + j * kThreads;
+        if (i < nvec) {
+            const float e[4] = {v[j].x * alpha, v[j].y * alpha, v[j].z * alpha, v[j].w * alpha};
+            __half h[4], l[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                h[q] = __float2half_rn(e[q]);
+                l[q] = __float2half_rn((e[q] - __half2float(h[q])) * 2048.0f);
+            }
+            *reinterpret_cast<uint2 *>(hi + (i << 2)) = *reinterpret_cast<const uint2 *>(h);
+            *reinterpret_cast<uint2 *>(lo + (i << 2)) = *reinterpret_cast<const uint2 *>(l);
+        }
+    }
+    return __uint_as_float(uint32_t(eb - 12) << 23);
+}
+
+// One output row of one token through the epilogue of its segment.
+__device__ __forceinline__ void row_epilogue(const SegDev &s, int row, int m, float y0, float y1, float &best, int &best_idx)
+{
+    float *out = s.out + size_t(m) * s.rows;
+    switch (s.epilogue) {
+    case INSG_EPI_STORE: out[row] = y0; break;
+    case INSG_EPI_RESIDUAL: out[row] = __ldcg(out + row) + y0; break;
+    case INSG_EPI_CONV_SILU: {
+        float *st = s.conv_state + size_t(row) * 3;
+        const uint2 wv = reinterpret_cast<const uint2 *>(s.conv_w)[row];
+        const float w0 = bf16_bits_to_float(wv.x & 0xffff), w1 = bf16_bits_to_float(wv.x >> 16);
+        const float w2 = bf16_bits_to_float(wv.y & 0xffff), w3 = bf16_bits_to_float(wv.y >> 16);
+        const float s0 = __ldcg(st), s1 = __ldcg(st + 1), s2 = __ldcg(st + 2);
+        const float z = fmaf(s0, w0, fmaf(s1, w1, fmaf(s2, w2, y0 * w3)));
+        st[0] = s1; st[1] = s2; st[2] = y0;
+        out[row] = fast_silu(z);
+        break;
+    }
+    case INSG_EPI_BETA: out[row] = fast_sigmoid(y0); break;
+    case INSG_EPI_DECAY: {
+        const float z = y0 + bf16_bits_to_float(s.dt_bias[row]);
+        const float soft = z > 20.f ? z : log1pf(__expf(z));
+        out[row] = -__expf(s.A_log[row]) * soft;
+        break;
+    }
+    case INSG_EPI_SWIGLU: out[row] = fast_silu(y0) * y1; break;
+    case INSG_EPI_LOGITS:
+        out[row] = y0;
+        if (y0 > best || (y0 == best && row < best_idx)) { best = y0; best_idx = row; }
+        break;
+    default: break;
+    }
+}
+
+template <int UNR, int M>
+__global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_constant__ GemvParams p)
+{
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int nkb = p.nkb;
+    const int xstride = p.cols + 8;
+    __half *xs = reinterpret_cast<__half *>(smem_raw);
+    float *rec = reinterpret_cast<float *>(smem_raw + size_t(M) * 2 * xstride * sizeof(__half)); // [16 warps][slots][M][16]
+    float *scratch = rec + size_t(kWarps) * p.slots * M * 16;                                    // 64 floats
+    __shared__ int s_last;
+
+    pdl_launch_dependents();
+
+    // this CTA's and this warp's share of the record sequence
+    const int G = int(gridDim.x), c = int(blockIdx.x);
+    const int a = int((long long)p.total_units * c / G), b = int((long long)p.total_units * (c + 1) / G);
+    const int ua = a + int((long long)(b - a) * warp / kWarps), ub = a + int((long long)(b - a) * (warp + 1) / kWarps);
+    const int tm_first = ua / nkb;
+
+    UnitIt lit;
+    it_set(p, lit, ua);
+    Chunk<UNR> A, B;
+    load_chunk<UNR>(p, A, lit, ub, lane);
+    load_chunk<UNR>(p, B, lit, ub, lane);
+
+    pdl_wait();
+
+    float inv_alpha[M];
+#pragma unroll
+    for (int m = 0; m < M; m++) inv_alpha[m] = prologue(p, m, xs, xstride, scratch);
+    __syncthreads();
+
+    const bool bactive = (t == (g >> 1));
+    const int piece = g & 1;
+    float acc[M][4];
+#pragma unroll
+    for (int m = 0; m < M; m++) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+    float *wrec = rec + size_t(warp) * p.slots * M * 16;
+
+    // consume one chunk: multiply its records, closing a (tile, matrix) run whenever one ends
+    UnitIt cit;
+    it_set(p, cit, ua);
+    auto compute = [&](const Chunk<UNR> &ch) {
+#pragma unroll
+        for (int j = 0; j < UNR; j++) {
+            if (cit.u >= ub) break; // warp-uniform
+            float cc[M][4];
+#pragma unroll
+            for (int m = 0; m < M; m++) cc[m][0] = cc[m][1] = cc[m][2] = cc[m][3] = 0.f;
+            const uint32_t wa[4] = {ch.wa[j].x, ch.wa[j].y, ch.wa[j].z, ch.wa[j].w};
+            const uint32_t wb[4] = {ch.wb[j].x, ch.wb[j].y, ch.wb[j].z, ch.wb[j].w};
+            const int xoff = cit.kb * 128 + t * 32;
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                uint32_t ha[4], hb[4];
+                dequant8(wa[w], ha);
+                dequant8(wb[w], hb);
+#pragma unroll
+                for (int m = 0; m < M; m++) {
+                    uint4 xv = make_uint4(0, 0, 0, 0);
+                    if (bactive) xv = *reinterpret_cast<const uint4 *>(xs + size_t(m * 2 + piece) * xstride + xoff + w * 8);
+                    mma16816(cc[m], ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+                    mma16816(cc[m], ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+                }
+            }
+            const float s0 = e8m0_to_float(ch.sc[j] & 0xffu), s1 = e8m0_to_float(ch.sc[j] >> 8);
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                acc[m][0] = fmaf(cc[m][0], s0, acc[m][0]);
+                acc[m][1] = fmaf(cc[m][1], s0, acc[m][1]);
+                acc[m][2] = fmaf(cc[m][2], s1, acc[m][2]);
+                acc[m][3] = fmaf(cc[m][3], s1, acc[m][3]);
+            }
+            if (cit.kb == nkb - 1 || cit.u == ub - 1) {
+                // fold hi/lo, sum the quad (4 scale groups), gather rows 0..15 into lanes 0..15, park in this run's slot
+                float *slot = wrec + size_t(cit.tm - tm_first) * M * 16;
+#pragma unroll
+                for (int m = 0; m < M; m++) {
+                    float v0 = fmaf(acc[m][1], kLoScale, acc[m][0]);
+                    float v1 = fmaf(acc[m][3], kLoScale, acc[m][2]);
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+                    const float r0 = __shfl_sync(0xffffffffu, v0, (lane & 7) * 4);
+                    const float r1 = __shfl_sync(0xffffffffu, v1, (lane & 7) * 4);
+                    if (lane < 16) slot[m * 16 + lane] = ((lane & 8) ? r1 : r0) * inv_alpha[m];
+                    acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+                }
+            }
+            it_next(p, cit);
+        }
+    };
+
+    while (cit.u < ub) {
+        compute(A);
+        load_chunk<UNR>(p, A, lit, ub, lane);
+        if (cit.u >= ub) break;
+        compute(B);
+        load_chunk<UNR>(p, B, lit, ub, lane);
+    }
+    __syncthreads();
+
+    // ---- combine: every (tile) this CTA touched, its runs summed over the warps in warp order --------
+    float best = -3.402823466e38f;
+    int best_idx = 0x7fffffff;
+    if (b > a) {
+        const int tm_lo = a / nkb, tm_hi = (b - 1) / nkb;
+        const int row = lane & 15;
+        // tasks are tiles: a run for plain segments, the (gate, up) pair of runs for SwiGLU
+        for (int tmq = tm_lo + warp; tmq <= tm_hi; tmq += kWarps) {
+            const SegDev &s = p.seg[seg_of(p, tmq)];
+            const int local = tmq - s.tm_begin;
+            if (s.nmat == 2 && (local & 1) && tmq != tm_lo) continue; // the pair is handled from its gate run
+            const int tm0 = tmq - (s.nmat == 2 ? (local & 1) : 0);
+            const int u_begin = tm0 * nkb, u_end = (tm0 + s.nmat) * nkb;
+            for (int m = lane >> 4; m < M; m += 2) {
+                float y[2] = {0.f, 0.f};
+                for (int mat = 0; mat < s.nmat; mat++) {
+                    const int tm = tm0 + mat, lo = max(tm * nkb, a), hi = min((tm + 1) * nkb, b);
+                    float z = 0.f;
+                    if (hi > lo) {
+                        for (int w = 0; w < kWarps; w++) {
+                            const int wa_ = a + int((long long)(b - a) * w / kWarps), wb_ = a + int((long long)(b - a) * (w + 1) / kWarps);
+                            if (wb_ > wa_ && wa_ < hi && wb_ > lo)
+                                z += rec[(size_t(w) * p.slots + (tm - wa_ / nkb)) * M * 16 + m * 16 + row];
+                        }
+                    }
+                    y[mat] = z;
+                }
+                const int out_row = (tm0 - s.tm_begin) / s.nmat * 16 + row;
+                if (u_begin >= a && u_end <= b) {
+                    row_epilogue(s, out_row, m, y[0], y[1], best, best_idx);
+                } else {
+                    // cut by a CTA boundary: slot `c-1` if it started in the previous CTA, slot `c` otherwise
+                    const int bslot = u_begin < a ? c - 1 : c, side = u_begin < a ? 1 : 0;
+                    float *mine = p.sk_part + ((size_t(bslot) * 2 + side) * 2) * 64 + m * 16 + row;
+                    mine[0] = y[0];
+                    mine[64] = y[1];
+                }
+            }
+            const bool cut = !(u_begin >= a && u_end <= b);
+            if (cut) { // warp-uniform
+                const int bslot = u_begin < a ? c - 1 : c, side = u_begin < a ? 1 : 0;
+                __threadfence();
+                __syncwarp();
+                unsigned old = 0;
+                if (lane == 0) old = atomicAdd(p.sk_ticket + bslot, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == 1u) { // the other half is already there: finish the tile (lower half + upper half, always)
+                    __threadfence();
+                    for (int m = lane >> 4; m < M; m += 2) {
+                        const float *lo_ = p.sk_part + ((size_t(bslot) * 2 + 0) * 2) * 64 + m * 16 + row;
+                        const float *hi_ = p.sk_part + ((size_t(bslot) * 2 + 1) * 2) * 64 + m * 16 + row;
+                        const float y0 = __ldcg(lo_) + __ldcg(hi_), y1 = __ldcg(lo_ + 64) + __ldcg(hi_ + 64);
+                        row_epilogue(s, (tm0 - s.tm_begin) / s.nmat * 16 + row, m, y0, y1, best, best_idx);
+                    }
+                    __syncwarp();
+                    if (lane == 0) p.sk_ticket[bslot] = 0u;
+                }
+                (void)side;
+            }
+        }
+    }
+
+    // ---- arg-max over the rows this launch produced (lm_head) ----------------
+    if (p.argmax_partial) {
+        float *sv = scratch + 16;
+        int *si = reinterpret_cast<int *>(scratch + 32);
+#pragma unroll
+        for (int mk = 16; mk; mk >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, mk);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_idx, mk);
+            if (ov > best || (ov == best && oi < best_idx)) { best = ov; best_idx = oi; }
+        }
+        if (lane == 0) { sv[warp] = best; si[warp] = best_idx; }
+        __syncthreads();
+        if (tid == 0) {
+            float bv = sv[0];
+            int bi = si[0];
+            for (int w = 1; w < kWarps; w++)
+                if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+            p.argmax_partial[blockIdx.x] = make_float2(bv, __int_as_float(bi));
+            __threadfence();
+            const unsigned ticket = atomicAdd(p.argmax_ticket, 1u);
+            s_last = (ticket == gridDim.x - 1);
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            float bv = -3.402823466e38f;
+            int bi = 0x7fffffff;
+            for (int i = tid; i < G; i += kThreads) {
+                const float ev = __ldcg(reinterpret_cast<const float *>(p.argmax_partial + i));
+                const int idx = __float_as_int(__ldcg(reinterpret_cast<const float *>(p.argmax_partial + i) + 1));
+                if (ev > bv || (ev == bv && idx < bi)) { bv = ev; bi = idx; }
+            }
+#pragma unroll
+            for (int mk = 16; mk; mk >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, mk);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, mk);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            __syncthreads();
+            if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+            __syncthreads();
+            if (tid == 0) {
+                for (int w = 1; w < kWarps; w++)
+                    if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+                *p.token_out = bi;
+                if (p.token_feedback) *p.token_feedback = bi;
+                if (p.position_inout) {
+                    const int pos = *p.position_inout;
+                    if (p.token_log) p.token_log[pos] = bi;
+                    *p.position_inout = pos + 1;
+                }
+                *p.argmax_ticket = 0u;
+            }
+        }
+    }
+}
+
+// ---- host side ------------------------------------------------------------------
+namespace {
+struct Tuning {
+    int unr = 4; // records per prefetch chunk
+} g_tune;
+
+// Split-K scratch used when the caller passes none: one fixed array per device inside the library image.
+constexpr int kMaxGrid = 256;
+constexpr size_t kSkPartFloats = size_t(kMaxGrid) * 2 * 2 * 64;
+static __device__ __align__(256) float g_sk_part[kSkPartFloats];
+static __device__ __align__(256) unsigned g_sk_ticket[kMaxGrid];
+std::mutex g_sk_mutex;
+float *g_sk_part_ptr[64] = {nullptr};
+unsigned *g_sk_ticket_ptr[64] = {nullptr};
+
+int default_scratch(float **part, unsigned **ticket)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(INSG_E_LIMIT, "gemv: device ordinal beyond 63");
+    std::lock_guard<std::mutex> lock(g_sk_mutex);
+    if (!g_sk_part_ptr[dev]) {
+        void *a = nullptr, *b = nullptr;
+        if ((e = cudaGetSymbolAddress(&a, g_sk_part)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(gemv scratch)");
+        if ((e = cudaGetSymbolAddress(&b, g_sk_ticket)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(gemv ticket)");
+        g_sk_part_ptr[dev] = static_cast<float *>(a);
+        g_sk_ticket_ptr[dev] = static_cast<unsigned *>(b);
+    }
+    *part = g_sk_part_ptr[dev];
+    *ticket = g_sk_ticket_ptr[dev];
+    return INSG_OK;
+}
+
+template <int UNR, int M> int launch_variant(const GemvParams &p, int grid, size_t smem, cudaStream_t st, bool pdl)
+{
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(gemv_fused_kernel<UNR, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(gemv)");
+    return launch(gemv_fused_kernel<UNR, M>, dim3(grid), dim3(kThreads), smem, st, pdl, p);
+}
+
+template <int M> int dispatch(const GemvParams &p, int grid, size_t smem, cudaStream_t st, bool pdl)
+{
+    if (g_tune.unr == 2) return launch_variant<2, M>(p, grid, smem, st, pdl);
+    return launch_variant<4, M>(p, grid, smem, st, pdl);
+}
+} // namespace
+
+int gemv_tune(const char *key, int value)
+{
+    const std::string k = key;
+    if (k == "gemv_unr") g_tune.unr = value == 2 ? 2 : 4;
+    else return fail(INSG_E_ARG, "unknown tuning key");
+    return INSG_OK;
+}
+
+int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
+{
+    if (!op || !op->in) return fail(INSG_E_ARG, "gemv: null operand");
+    if (op->cols <= 0 || (op->cols & 127) || op->cols > kMaxVec * kThreads * 4)
+        return fail(INSG_E_SHAPE, "gemv: cols must be a multiple of 128, <= 12288");
+    if (op->n_segments < 1 || op->n_segments > 4) return fail(INSG_E_SHAPE, "gemv: 1..4 segments");
+    if (M != 1 && M != 2 && M != 4) return fail(INSG_E_SHAPE, "gemv: 1, 2 or 4 tokens per launch");
+    if ((op->prologue == INSG_PRO_RMSNORM || op->prologue == INSG_PRO_GATED_RMSNORM) && !op->norm_w)
+        return fail(INSG_E_ARG, "gemv: norm weight missing");
+    if (op->prologue >= INSG_PRO_GATED_RMSNORM && !op->aux) return fail(INSG_E_ARG, "gemv: prologue operand missing");
+    if (op->prologue == INSG_PRO_GATED_RMSNORM && (op->cols & 127)) return fail(INSG_E_SHAPE, "gemv: gated norm needs cols % 128 == 0");
+    GemvParams p = {};
+    p.in = op->in; p.aux = op->aux; p.norm_w = op->norm_w; p.x_out = op->x_out;
+    p.cols = op->cols; p.nkb = op->cols >> 7; p.prologue = op->prologue; p.nseg = op->n_segments;
+    int tm = 0, longest = 1;
+    bool logits = false;
+    for (int i = 0; i < op->n_segments; i++) {
+        const insg_gemv_segment &s = op->seg[i];
+        if (!s.packed || !s.out || s.rows <= 0 || (s.rows & 15)) return fail(INSG_E_SHAPE, "gemv: segment rows must be a positive multiple of 16");
+        if (s.epilogue == INSG_EPI_SWIGLU && !s.packed2) return fail(INSG_E_ARG, "gemv: SwiGLU needs two matrices");
+        if (s.epilogue == INSG_EPI_CONV_SILU && (!s.conv_state || !s.conv_w)) return fail(INSG_E_ARG, "gemv: conv operands missing");
+        if (s.epilogue == INSG_EPI_DECAY && (!s.A_log || !s.dt_bias)) return fail(INSG_E_ARG, "gemv: decay operands missing");
+        if (s.epilogue == INSG_EPI_LOGITS && M != 1) return fail(INSG_E_SHAPE, "gemv: the logits epilogue needs M == 1");
+        SegDev &d = p.seg[i];
+        d.packed = static_cast<const uint8_t *>(s.packed);
+        d.packed2 = static_cast<const uint8_t *>(s.packed2);
+        d.out = s.out; d.conv_state = s.conv_state; d.conv_w = s.conv_w; d.A_log = s.A_log; d.dt_bias = s.dt_bias;
+        d.nmat = s.epilogue == INSG_EPI_SWIGLU ? 2 : 1;
+        d.tm_begin = tm; tm += (s.rows >> 4) * d.nmat; d.epilogue = s.epilogue; d.rows = s.rows;
+        longest = std::max(longest, d.nmat);
+        logits |= s.epilogue == INSG_EPI_LOGITS;
+    }
+    const long long units = (long long)tm * p.nkb;
+    if (units > 0x7fffffffLL) return fail(INSG_E_LIMIT, "gemv: more than 2^31 records");
+    p.total_tm = tm;
+    p.total_units = int(units);
+    // one CTA per SM; never so many that a tile (or gate/up pair) could be cut by more than one CTA boundary
+    const int etile = longest * p.nkb;
+    const int grid = std::max(1, std::min(std::min(sm_count(), kMaxGrid), p.total_units / etile));
+    const int per_cta = (p.total_units + grid - 1) / grid;
+    p.slots = (per_cta / kWarps + 1 + p.nkb - 1) / p.nkb + 1;
+    if (logits) {
+        if (op->n_segments != 1) return fail(INSG_E_SHAPE, "gemv: the logits epilogue takes one segment");
+        if (!op->argmax_scratch || !op->token_out) return fail(INSG_E_ARG, "gemv: arg-max scratch/token missing");
+        p.argmax_ticket = static_cast<unsigned *>(op->argmax_scratch);
+        p.argmax_partial = reinterpret_cast<float2 *>(static_cast<uint8_t *>(op->argmax_scratch) + 64);
+        p.token_out = op->token_out;
+        p.token_feedback = op->token_feedback;
+        p.token_log = op->token_log;
+        p.position_inout = op->position_inout;
+    }
+    if (op->splitk_scratch) {
+        p.sk_ticket = static_cast<unsigned *>(op->splitk_scratch);
+        p.sk_part = reinterpret_cast<float *>(static_cast<uint8_t *>(op->splitk_scratch) + kMaxGrid * sizeof(unsigned));
+    } else {
+        const int rc = default_scratch(&p.sk_part, &p.sk_ticket);
+        if (rc != INSG_OK) return rc;
+    }
+    const size_t smem = size_t(M) * 2 * (op->cols + 8) * sizeof(__half) + size_t(kWarps) * p.slots * M * 16 * 4 + 64 * 4;
+    if (smem > 220 * 1024) return fail(INSG_E_LIMIT, "gemv: shared memory beyond 220 KB");
+    const bool pdl = op->pdl != 0;
+    switch (M) {
+    case 1: return dispatch<1>(p, grid, smem, st, pdl);
+    case 2: return dispatch<2>(p, grid, smem, st, pdl);
+    default: return dispatch<4>(p, grid, smem, st, pdl);
+    }
+}
+
+} // namespace insg
+
+using namespace insg;
+
+extern "C" {
+
+size_t insg_gemv_argmax_scratch_bytes(void) { return 64 + size_t(8) * kMaxGrid; }
+
+size_t insg_gemv_splitk_scratch_bytes(void) { return kMaxGrid * sizeof(unsigned) + kSkPartFloats * sizeof(float); }
+
+int insg_gemv_fused(const insg_gemv_op *op, insg_stream_t stream) { return gemv_fused_launch(op, 1, stream); }
+
+int insg_mxfp4_gemv_packed(const void *packed, const float *x, float *y, int rows, int cols, int M, insg_stream_t stream)
+{
+    if (M < 1 || M > 8) return fail(INSG_E_SHAPE, "gemv_packed: 1 <= M <= 8");
+    for (int m0 = 0; m0 < M;) {
+        const int left = M - m0;
+        const int mm = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
+        insg_gemv_op op = {};
+        op.in = x + size_t(m0) * cols;
+        op.cols = cols;
+        op.prologue = INSG_PRO_PLAIN;
+        op.n_segments = 1;
+        op.seg[0].packed = packed;
+        op.seg[0].out = y + size_t(m0) * rows;
+        op.seg[0].rows = rows;
+        op.seg[0].epilogue = INSG_EPI_STORE;
+        const int rc = gemv_fused_launch(&op, mm, stream);
+        if (rc) return rc;
+        m0 += mm;
+    }
+    return INSG_OK;
+}
+
+} // extern "C"
