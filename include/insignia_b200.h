@@ -147,14 +147,13 @@ typedef struct insg_gemv_op {
     int *token_feedback;
     int *token_log;
     int *position_inout;
-    /* Scratch for tiles cut by a CTA boundary (>= insg_gemv_splitk_scratch_bytes(), zeroed once, left zeroed by
-     * every call).  NULL selects a fixed array inside the library: then calls that overlap on one GPU race. */
-    void *splitk_scratch;
+    /* Optional profiling aid: [grid][8] u64 nanosecond timestamps written by each CTA at its phase boundaries
+     * (start, loads issued, dependency met, prologue done, streaming done, CTA barrier, combine done), or NULL. */
+    void *trace;
     int pdl;                  /* 1: launch with programmatic dependent launch          */
 } insg_gemv_op;
 
 INSG_API size_t insg_gemv_argmax_scratch_bytes(void);
-INSG_API size_t insg_gemv_splitk_scratch_bytes(void);
 INSG_API int insg_gemv_fused(const insg_gemv_op *op /* host */, insg_stream_t stream);
 
 /* ------------------------------------------------------------ DeltaNet */

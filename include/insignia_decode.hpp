@@ -56,7 +56,6 @@ public:
     int *d_next{};       // device: arg-max of the last logits
     void *attn_scratch{};
     void *argmax_scratch{};
-    void *gemv_scratch{};  // partial sums of GEMV tiles cut by a CTA boundary
     void reset(); // zero recurrent state and position, as a fresh workspace
 
 private:

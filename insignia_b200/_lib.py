@@ -23,7 +23,7 @@ class GemvSegment(C.Structure):
 class GemvOp(C.Structure):
     _fields_ = [("in_", vp), ("aux", vp), ("norm_w", vp), ("x_out", vp), ("cols", i32), ("prologue", i32),
                 ("n_segments", i32), ("seg", GemvSegment * 4), ("argmax_scratch", vp), ("token_out", vp),
-                ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("splitk_scratch", vp), ("pdl", i32)]
+                ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("trace", vp), ("pdl", i32)]
 
 
 class AttnOp(C.Structure):
@@ -52,7 +52,6 @@ SIGNATURES = {
     "insg_mxfp4_repack": (i32, [vp, vp, vp, i32, i32, vp]),
     "insg_mxfp4_gemv_packed": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "insg_gemv_argmax_scratch_bytes": (sz, []),
-    "insg_gemv_splitk_scratch_bytes": (sz, []),
     "insg_gemv_fused": (i32, [C.POINTER(GemvOp), vp]),
     "insg_deltanet_decode": (i32, [vp] * 7 + [i32, vp]),
     "insg_gqa_scratch_bytes": (sz, [i32]),

@@ -8,13 +8,14 @@
 //     record is 1088 contiguous bytes, read by a warp with two coalesced 512-byte loads + 64 scale
 //     bytes (ld.global.nc, no L1 allocation); every warp keeps two chunks of UNR records in flight,
 //     both issued BEFORE the programmatic-dependent-launch wait so they overlap the previous kernel;
-//   * work is cut "stream-K": the launch's records form one linear sequence (segment, tile, matrix,
-//     k-block) that is divided evenly over the CTAs (one per SM) and then over the 16 warps of a CTA,
-//     so every warp streams the same number of bytes whatever the matrix shape.  A warp folds each
-//     (tile, matrix) run it finishes into a shared-memory slot; after one CTA barrier the slots are
-//     summed in warp order; a tile cut by a CTA boundary is finished by whichever of its two CTAs
-//     arrives last at a ticket in global scratch, adding the two halves in a fixed order.  Nothing
-//     spins and the result does not depend on scheduling;
+//   * the launch's records form one linear sequence (segment, tile, matrix, k-block).  Output tiles
+//     are dealt evenly to the CTAs (one per SM, whole tiles only, so no CTA ever waits for another)
+//     and a CTA's records are then divided evenly over its 16 warps, so every warp of a CTA streams
+//     the same number of bytes whatever the matrix shape.  A warp folds each (tile, matrix) run it
+//     finishes into a shared-memory slot; after one CTA barrier the slots are summed in warp order,
+//     so the result does not depend on scheduling (a ticketed split of tiles across CTAs was
+//     measured: its fence + atomic + re-read chain cost ~2.5 us per launch, more than the <=15 %
+//     imbalance of whole tiles);
 //   * E2M1 nibbles become fp16 pairs with cvt.rn.f16x2.e2m1x2 (exact); the multiply-adds run on
 //     mma.sync.m16n8k16 (fp16 in, fp32 accumulate) purely as a cheap FMA engine.  The fp32 activation
 //     is split into two fp16 pieces (hi + lo * 2^-11 after an exact power-of-two pre-scale) so the
@@ -56,13 +57,24 @@ struct GemvParams {
     float *x_out;
     int cols, nkb, prologue, nseg;
     int total_units, total_tm, slots; // records in the launch, (tile, matrix) runs, shared slots per warp
+    int total_etiles, etile_units;    // output tiles (a run, or a gate/up pair of runs) and records per tile
     SegDev seg[4];
     float2 *argmax_partial; // [grid] (value, index as int bits)
     unsigned *argmax_ticket;
     int *token_out, *token_feedback, *token_log, *position_inout;
-    float *sk_part;       // [grid][2 sides][2 matrices][4 tokens][16 rows]
-    unsigned *sk_ticket;  // [grid]
+    unsigned long long *trace; // optional [grid][8] phase timestamps (ns), or null
 };
+
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define INSG_TRACE(slot)                                                   \
+    do {                                                                   \
+        if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 8 + (slot)] = global_ns(); \
+    } while (0)
 
 __device__ __forceinline__ void dequant8(uint32_t q, uint32_t (&h)[4])
 {
@@ -197,8 +209,30 @@ __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, f
         ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
     }
     float inv_rms = 1.f;
-    if (p.prologue == INSG_PRO_RMSNORM) inv_rms = rsqrtf(block_sum16(ss, scratch) / float(cols) + 1e-6f);
     float amax = 0.f;
+    if (p.prologue == INSG_PRO_RMSNORM) {
+        // one reduction round for both the sum of squares and max|x*w| (the maximum after scaling is that times inv_rms)
+        float pre = 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxVec; j++) {
+            const int i = tid + j * kThreads;
+            if (i < nvec) {
+                const uint2 wv = reinterpret_cast<const uint2 *>(p.norm_w)[i];
+                pre = fmaxf(pre, fmaxf(fmaxf(fabsf(v[j].x * bf16_bits_to_float(wv.x & 0xffff)), fabsf(v[j].y * bf16_bits_to_float(wv.x >> 16))),
+                                       fmaxf(fabsf(v[j].z * bf16_bits_to_float(wv.y & 0xffff)), fabsf(v[j].w * bf16_bits_to_float(wv.y >> 16)))));
+            }
+        }
+        ss = warp_sum(ss);
+        pre = warp_max(pre);
+        __syncthreads();
+        if (lane == 0) { scratch[tid >> 5] = ss; scratch[16 + (tid >> 5)] = pre; }
+        __syncthreads();
+        float tot = 0.f, mx = 0.f;
+#pragma unroll
+        for (int i = 0; i < kWarps; i++) { tot += scratch[i]; mx = fmaxf(mx, scratch[16 + i]); }
+        inv_rms = rsqrtf(tot / float(cols) + 1e-6f);
+        amax = mx * inv_rms;
+    }
 #pragma unroll
     for (int j = 0; j < kMaxVec; j++) {
         const int i = tid + j * kThreads;
@@ -249,7 +283,7 @@ __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, f
             if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out + size_t(m) * cols)[i] = x;
         }
     }
-    const float tmax = block_max16(amax, scratch);
+    const float tmax = p.prologue == INSG_PRO_RMSNORM ? amax : block_max16(amax, scratch);
     // alpha = 2^(12 - floor(log2(max))) puts the largest element in [2^12, 2^13): fp16 holds it with room to spare
     int eb = int((__float_as_uint(tmax) >> 23) & 0xffu);
     eb = min(max(eb, 20), 240);
@@ -319,27 +353,38 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
     float *rec = reinterpret_cast<float *>(smem_raw + size_t(M) * 2 * xstride * sizeof(__half)); // [16 warps][slots][M][16]
     float *scratch = rec + size_t(kWarps) * p.slots * M * 16;                                    // 64 floats
     __shared__ int s_last;
+    __shared__ int s_wa[kWarps + 1], s_tmf[kWarps]; // warp boundaries in the record sequence, first run of each warp
 
+    INSG_TRACE(0);
     pdl_launch_dependents();
 
     // this CTA's and this warp's share of the record sequence
     const int G = int(gridDim.x), c = int(blockIdx.x);
-    const int a = int((long long)p.total_units * c / G), b = int((long long)p.total_units * (c + 1) / G);
-    const int ua = a + int((long long)(b - a) * warp / kWarps), ub = a + int((long long)(b - a) * (warp + 1) / kWarps);
+    // CTA ranges end on tile boundaries (a tile = one run, or the gate/up pair): no tile is shared between CTAs
+    const int a = int((long long)p.total_etiles * c / G) * p.etile_units, b = int((long long)p.total_etiles * (c + 1) / G) * p.etile_units;
+    const int ua = a + (((b - a) * warp) >> 4), ub = a + (((b - a) * (warp + 1)) >> 4); // kWarps == 16
     const int tm_first = ua / nkb;
+    if (lane == 0) {
+        s_wa[warp] = ua;
+        s_tmf[warp] = tm_first;
+        if (warp == kWarps - 1) s_wa[kWarps] = ub;
+    }
 
     UnitIt lit;
     it_set(p, lit, ua);
     Chunk<UNR> A, B;
     load_chunk<UNR>(p, A, lit, ub, lane);
     load_chunk<UNR>(p, B, lit, ub, lane);
+    INSG_TRACE(1);
 
     pdl_wait();
+    INSG_TRACE(2);
 
     float inv_alpha[M];
 #pragma unroll
     for (int m = 0; m < M; m++) inv_alpha[m] = prologue(p, m, xs, xstride, scratch);
     __syncthreads();
+    INSG_TRACE(3);
 
     const bool bactive = (t == (g >> 1));
     const int piece = g & 1;
@@ -410,7 +455,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
         compute(B);
         load_chunk<UNR>(p, B, lit, ub, lane);
     }
+    INSG_TRACE(4);
     __syncthreads();
+    INSG_TRACE(5);
 
     // ---- combine: every (tile) this CTA touched, its runs summed over the warps in warp order --------
     float best = -3.402823466e38f;
@@ -422,9 +469,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
         for (int tmq = tm_lo + warp; tmq <= tm_hi; tmq += kWarps) {
             const SegDev &s = p.seg[seg_of(p, tmq)];
             const int local = tmq - s.tm_begin;
-            if (s.nmat == 2 && (local & 1) && tmq != tm_lo) continue; // the pair is handled from its gate run
+            if (s.nmat == 2 && (local & 1)) continue; // the pair is handled from its gate run
             const int tm0 = tmq - (s.nmat == 2 ? (local & 1) : 0);
-            const int u_begin = tm0 * nkb, u_end = (tm0 + s.nmat) * nkb;
             for (int m = lane >> 4; m < M; m += 2) {
                 float y[2] = {0.f, 0.f};
                 for (int mat = 0; mat < s.nmat; mat++) {
@@ -432,48 +478,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
                     float z = 0.f;
                     if (hi > lo) {
                         for (int w = 0; w < kWarps; w++) {
-                            const int wa_ = a + int((long long)(b - a) * w / kWarps), wb_ = a + int((long long)(b - a) * (w + 1) / kWarps);
+                            const int wa_ = s_wa[w], wb_ = s_wa[w + 1];
                             if (wb_ > wa_ && wa_ < hi && wb_ > lo)
-                                z += rec[(size_t(w) * p.slots + (tm - wa_ / nkb)) * M * 16 + m * 16 + row];
+                                z += rec[((w * p.slots + (tm - s_tmf[w])) * M + m) * 16 + row];
                         }
                     }
                     y[mat] = z;
                 }
-                const int out_row = (tm0 - s.tm_begin) / s.nmat * 16 + row;
-                if (u_begin >= a && u_end <= b) {
-                    row_epilogue(s, out_row, m, y[0], y[1], best, best_idx);
-                } else {
-                    // cut by a CTA boundary: slot `c-1` if it started in the previous CTA, slot `c` otherwise
-                    const int bslot = u_begin < a ? c - 1 : c, side = u_begin < a ? 1 : 0;
-                    float *mine = p.sk_part + ((size_t(bslot) * 2 + side) * 2) * 64 + m * 16 + row;
-                    mine[0] = y[0];
-                    mine[64] = y[1];
-                }
-            }
-            const bool cut = !(u_begin >= a && u_end <= b);
-            if (cut) { // warp-uniform
-                const int bslot = u_begin < a ? c - 1 : c, side = u_begin < a ? 1 : 0;
-                __threadfence();
-                __syncwarp();
-                unsigned old = 0;
-                if (lane == 0) old = atomicAdd(p.sk_ticket + bslot, 1u);
-                old = __shfl_sync(0xffffffffu, old, 0);
-                if (old == 1u) { // the other half is already there: finish the tile (lower half + upper half, always)
-                    __threadfence();
-                    for (int m = lane >> 4; m < M; m += 2) {
-                        const float *lo_ = p.sk_part + ((size_t(bslot) * 2 + 0) * 2) * 64 + m * 16 + row;
-                        const float *hi_ = p.sk_part + ((size_t(bslot) * 2 + 1) * 2) * 64 + m * 16 + row;
-                        const float y0 = __ldcg(lo_) + __ldcg(hi_), y1 = __ldcg(lo_ + 64) + __ldcg(hi_ + 64);
-                        row_epilogue(s, (tm0 - s.tm_begin) / s.nmat * 16 + row, m, y0, y1, best, best_idx);
-                    }
-                    __syncwarp();
-                    if (lane == 0) p.sk_ticket[bslot] = 0u;
-                }
-                (void)side;
+                row_epilogue(s, (tm0 - s.tm_begin) / s.nmat * 16 + row, m, y[0], y[1], best, best_idx);
             }
         }
     }
 
+    INSG_TRACE(6);
     // ---- arg-max over the rows this launch produced (lm_head) ----------------
     if (p.argmax_partial) {
         float *sv = scratch + 16;
@@ -537,33 +554,7 @@ struct Tuning {
     int unr = 4; // records per prefetch chunk
 } g_tune;
 
-// Split-K scratch used when the caller passes none: one fixed array per device inside the library image.
 constexpr int kMaxGrid = 256;
-constexpr size_t kSkPartFloats = size_t(kMaxGrid) * 2 * 2 * 64;
-static __device__ __align__(256) float g_sk_part[kSkPartFloats];
-static __device__ __align__(256) unsigned g_sk_ticket[kMaxGrid];
-std::mutex g_sk_mutex;
-float *g_sk_part_ptr[64] = {nullptr};
-unsigned *g_sk_ticket_ptr[64] = {nullptr};
-
-int default_scratch(float **part, unsigned **ticket)
-{
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-    if (dev < 0 || dev >= 64) return fail(INSG_E_LIMIT, "gemv: device ordinal beyond 63");
-    std::lock_guard<std::mutex> lock(g_sk_mutex);
-    if (!g_sk_part_ptr[dev]) {
-        void *a = nullptr, *b = nullptr;
-        if ((e = cudaGetSymbolAddress(&a, g_sk_part)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(gemv scratch)");
-        if ((e = cudaGetSymbolAddress(&b, g_sk_ticket)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(gemv ticket)");
-        g_sk_part_ptr[dev] = static_cast<float *>(a);
-        g_sk_ticket_ptr[dev] = static_cast<unsigned *>(b);
-    }
-    *part = g_sk_part_ptr[dev];
-    *ticket = g_sk_ticket_ptr[dev];
-    return INSG_OK;
-}
 
 template <int UNR, int M> int launch_variant(const GemvParams &p, int grid, size_t smem, cudaStream_t st, bool pdl)
 {
@@ -605,7 +596,7 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
     GemvParams p = {};
     p.in = op->in; p.aux = op->aux; p.norm_w = op->norm_w; p.x_out = op->x_out;
     p.cols = op->cols; p.nkb = op->cols >> 7; p.prologue = op->prologue; p.nseg = op->n_segments;
-    int tm = 0, longest = 1;
+    int tm = 0, nmat_all = 0;
     bool logits = false;
     for (int i = 0; i < op->n_segments; i++) {
         const insg_gemv_segment &s = op->seg[i];
@@ -620,17 +611,19 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
         d.out = s.out; d.conv_state = s.conv_state; d.conv_w = s.conv_w; d.A_log = s.A_log; d.dt_bias = s.dt_bias;
         d.nmat = s.epilogue == INSG_EPI_SWIGLU ? 2 : 1;
         d.tm_begin = tm; tm += (s.rows >> 4) * d.nmat; d.epilogue = s.epilogue; d.rows = s.rows;
-        longest = std::max(longest, d.nmat);
+        if (nmat_all && nmat_all != d.nmat) return fail(INSG_E_SHAPE, "gemv: SwiGLU segments cannot be mixed with others");
+        nmat_all = d.nmat;
         logits |= s.epilogue == INSG_EPI_LOGITS;
     }
     const long long units = (long long)tm * p.nkb;
     if (units > 0x7fffffffLL) return fail(INSG_E_LIMIT, "gemv: more than 2^31 records");
     p.total_tm = tm;
     p.total_units = int(units);
-    // one CTA per SM; never so many that a tile (or gate/up pair) could be cut by more than one CTA boundary
-    const int etile = longest * p.nkb;
-    const int grid = std::max(1, std::min(std::min(sm_count(), kMaxGrid), p.total_units / etile));
-    const int per_cta = (p.total_units + grid - 1) / grid;
+    // one CTA per SM, each owning whole output tiles; its 16 warps split the tiles' records evenly
+    p.etile_units = nmat_all * p.nkb;
+    p.total_etiles = tm / nmat_all;
+    const int grid = std::max(1, std::min(std::min(sm_count(), kMaxGrid), p.total_etiles));
+    const int per_cta = (p.total_etiles + grid - 1) / grid * p.etile_units;
     p.slots = (per_cta / kWarps + 1 + p.nkb - 1) / p.nkb + 1;
     if (logits) {
         if (op->n_segments != 1) return fail(INSG_E_SHAPE, "gemv: the logits epilogue takes one segment");
@@ -642,13 +635,7 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
         p.token_log = op->token_log;
         p.position_inout = op->position_inout;
     }
-    if (op->splitk_scratch) {
-        p.sk_ticket = static_cast<unsigned *>(op->splitk_scratch);
-        p.sk_part = reinterpret_cast<float *>(static_cast<uint8_t *>(op->splitk_scratch) + kMaxGrid * sizeof(unsigned));
-    } else {
-        const int rc = default_scratch(&p.sk_part, &p.sk_ticket);
-        if (rc != INSG_OK) return rc;
-    }
+    p.trace = static_cast<unsigned long long *>(op->trace);
     const size_t smem = size_t(M) * 2 * (op->cols + 8) * sizeof(__half) + size_t(kWarps) * p.slots * M * 16 * 4 + 64 * 4;
     if (smem > 220 * 1024) return fail(INSG_E_LIMIT, "gemv: shared memory beyond 220 KB");
     const bool pdl = op->pdl != 0;
@@ -666,8 +653,6 @@ using namespace insg;
 extern "C" {
 
 size_t insg_gemv_argmax_scratch_bytes(void) { return 64 + size_t(8) * kMaxGrid; }
-
-size_t insg_gemv_splitk_scratch_bytes(void) { return kMaxGrid * sizeof(unsigned) + kSkPartFloats * sizeof(float); }
 
 int insg_gemv_fused(const insg_gemv_op *op, insg_stream_t stream) { return gemv_fused_launch(op, 1, stream); }
 

@@ -76,9 +76,7 @@ void DecodeWorkspace::allocate()
     cuda_check(cudaMalloc(&attn_scratch, insg_gqa_scratch_bytes(max_context)), "cudaMalloc attention scratch");
     cuda_check(cudaMalloc(&argmax_scratch, insg_gemv_argmax_scratch_bytes()), "cudaMalloc arg-max scratch");
     cuda_check(cudaMemsetAsync(attn_scratch, 0, 64, stream), "memset");
-    cuda_check(cudaMalloc(&gemv_scratch, insg_gemv_splitk_scratch_bytes()), "cudaMalloc GEMV scratch");
     cuda_check(cudaMemsetAsync(argmax_scratch, 0, 64, stream), "memset");
-    cuda_check(cudaMemsetAsync(gemv_scratch, 0, insg_gemv_splitk_scratch_bytes(), stream), "memset");
     cuda_check(cudaMemsetAsync(d_token, 0, (4 + size_t(max_context) + 1) * sizeof(int), stream), "memset");
     // The reference leaves the KV caches uninitialised (src/decode.cu:10); rows are always written before they are read.
     reset();
@@ -96,7 +94,7 @@ DecodeWorkspace::~DecodeWorkspace()
     for (void *p : {(void *)hidden, (void *)norm, (void *)qkv, (void *)attn_gate, (void *)key, (void *)value, (void *)z, (void *)a,
                     (void *)b, (void *)core, (void *)gate, (void *)up, (void *)down, (void *)logits, (void *)delta_state,
                     (void *)conv_state, (void *)kv_keys, (void *)kv_values, (void *)mtp_keys, (void *)mtp_values, (void *)d_token,
-                    attn_scratch, argmax_scratch, gemv_scratch})
+                    attn_scratch, argmax_scratch})
         cudaFree(p);
 }
 
@@ -230,7 +228,6 @@ uint64_t gemv_bytes(const insg_gemv_op &op)
 void run_gemv(Ctx &c, insg_gemv_op &op)
 {
     op.pdl = c.pdl ? 1 : 0;
-    op.splitk_scratch = c.x.gemv_scratch;
     Timed t(c, 0, gemv_bytes(op));
     insg_check(insg_gemv_fused(&op, c.st));
     c.launches++;

@@ -75,7 +75,7 @@ def gemv_packed(packed, x, rows=None, cols=None):
     return y.reshape(*x.shape[:-1], rows)
 
 
-def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, splitk_scratch=None):
+def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, trace=None):
     """``segments``: list of dicts with packed, out, rows, epilogue (+ packed2 / conv_state, conv_w / A_log, dt_bias).
     ``argmax``: dict(scratch, token_out[, token_feedback, token_log, position]) for the logits epilogue."""
     op = GemvOp()
@@ -91,13 +91,9 @@ def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=Non
         op.argmax_scratch, op.token_out = _p(argmax["scratch"]), _p(argmax["token_out"])
         op.token_feedback, op.token_log = _p(argmax.get("token_feedback")), _p(argmax.get("token_log"))
         op.position_inout = _p(argmax.get("position"))
-    op.splitk_scratch = _p(splitk_scratch)
+    op.trace = _p(trace)
     op.pdl = int(pdl)
     check(_lib.lib().insg_gemv_fused(C.byref(op), _stream()))
-
-
-def splitk_scratch(device):
-    return torch.zeros(_lib.lib().insg_gemv_splitk_scratch_bytes(), dtype=torch.uint8, device=device)
 
 
 def argmax_scratch(device):
