@@ -63,6 +63,8 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--kv-bf16", action="store_true", help="bf16 KV cache (the default is the reference's fp32 cache)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemv", default="mma", choices=["mma", "tcgen05"], help="GEMV kernel family of the engine")
+    ap.add_argument("--tune", action="append", default=[], help="kernel tuning knob key=value (insg_tune_set)")
     return ap.parse_args()
 
 
@@ -175,7 +177,12 @@ def run_native(args, rank, world, local_rank):
 
     K, W = args.steps, args.warmup
     ctx = args.prompt + W + 2 * K + 8
-    eng = Engine(idx, max_context=ctx, budget_bytes=16 << 30, kv_bf16=args.kv_bf16, device=local_rank)
+    from insignia_b200 import ops
+
+    for kv in args.tune:
+        k, v = kv.split("=")
+        ops.tune(k, int(v))
+    eng = Engine(idx, max_context=ctx, budget_bytes=16 << 30, kv_bf16=args.kv_bf16, device=local_rank, gemv_tcgen05=args.gemv == "tcgen05")
     rng = np.random.default_rng(args.seed + 1000 * rank)
     prompt = rng.integers(0, VOCAB, args.prompt)
     for t in prompt:
@@ -227,7 +234,7 @@ def run_native(args, rank, world, local_rank):
         "data": "synthetic", "impl": "native",
         "config": {"workload": "configs[3]: 32-layer hybrid (24 DeltaNet + 8 GQA), MXFP4 weights, batch-1 greedy decode after a "
                                f"{args.prompt}-token prompt", "prompt_tokens": args.prompt, "context_at_end": final_ctx,
-                   "kv_cache": "bf16" if args.kv_bf16 else "f32", "weights": "seeded N(0,0.02) -> MXFP4, norms 1.0",
+                   "kv_cache": "bf16" if args.kv_bf16 else "f32", "gemv": args.gemv, "tune": args.tune, "weights": "seeded N(0,0.02) -> MXFP4, norms 1.0",
                    "parallelism": f"replica x{world}" if world > 1 else "single GPU",
                    "l2": "weights streamed per token (4.2 GB) exceed the 126 MB L2; no flush needed"},
         "e2e": {"value": world * K / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},

@@ -38,7 +38,9 @@ enum {
 
 INSG_API const char *insg_last_error(void);  /* host string, thread-local */
 INSG_API int insg_version(void);
-/* Kernel tuning knob ("gemv_unr": 2 or 4 records per prefetch chunk); process-wide, for benchmarking. */
+/* Kernel tuning knobs, process-wide, for benchmarking: "gemv_unr" (2|4 records per register prefetch chunk), "gemv_ring"
+ * (0 = register prefetch, 2..4 = shared-memory ring of that many stages per warp), "gemv_ctas_per_sm" (1|2, ring only),
+ * "umma_stages" / "umma_nacc" / "umma_prefetch" (tcgen05 kernel). */
 INSG_API int insg_tune_set(const char *key /* host */, int value);
 
 /* ------------------------------------------------------------------ MXFP4 */
@@ -81,6 +83,14 @@ INSG_API int insg_mxfp4_dequant_mlx(const uint32_t *weight, const uint8_t *scale
 INSG_API size_t insg_mxfp4_packed_bytes(int rows, int cols);
 INSG_API int insg_mxfp4_repack(const uint32_t *weight, const uint8_t *scales, void *packed, int rows, int cols,
                                insg_stream_t stream);
+
+/* Second packed layout, for the tcgen05 kernel: rows in tiles of 128 (padded with zero weights), K in blocks of
+ * 128, one 8704-byte record per (tile, block) = the shared-memory image tcgen05.mma kind::mxf4 reads (canonical
+ * K-major 4-bit operand, no swizzle) followed by the 512-byte scale block tcgen05.cp expects.  cols % 128 == 0.
+ * Same 17 bytes per 32 weights.  No reference counterpart. */
+INSG_API size_t insg_mxfp4_packed_umma_bytes(int rows, int cols);
+INSG_API int insg_mxfp4_repack_umma(const uint32_t *weight, const uint8_t *scales, void *packed, int rows, int cols,
+                                    insg_stream_t stream);
 
 /* y[m][rows] = W x[m] for m < M (1 <= M <= 8), W in the packed layout; x is
  * fp32 [M][cols], y fp32 [M][rows].  Plain (no fused prologue/epilogue) form of
@@ -150,6 +160,8 @@ typedef struct insg_gemv_op {
     /* Optional profiling aid: [grid][8] u64 nanosecond timestamps written by each CTA at its phase boundaries
      * (start, loads issued, dependency met, prologue done, streaming done, CTA barrier, combine done), or NULL. */
     void *trace;
+    int layout;               /* weight layout of every segment: 0 = insg_mxfp4_repack records, 1 = insg_mxfp4_repack_umma   */
+    int *error_flag;          /* set to 1 if a bounded wait inside the kernel ran out (device int), or NULL                 */
     int pdl;                  /* 1: launch with programmatic dependent launch          */
 } insg_gemv_op;
 
@@ -276,6 +288,7 @@ typedef struct insg_engine_options {
     int accurate_trig;            /* 0: fast intrinsics for RoPE as the reference; 1: sincosf   */
     int use_graph;                /* 1: capture the token step in a CUDA graph                  */
     int use_pdl;                  /* 1: programmatic dependent launch between kernels           */
+    int gemv_tcgen05;             /* 1: tcgen05 kind::mxf4 GEMV; 0: mma.sync register-streaming GEMV */
     int n_layers;                 /* 0 = 32                                                     */
     int vocab;                    /* 0 = 248320 (rows of lm_head used for logits)               */
     int device;                   /* CUDA device ordinal                                        */
@@ -304,6 +317,10 @@ INSG_API int insg_engine_generate(insg_engine *e, int first_token, int count, in
  * 2 attention, 3 embedding), the summed durations, the algorithmic bytes and the launch counts.
  * Advances the position like insg_engine_forward_token.  Synchronises.  No reference counterpart. */
 INSG_API int insg_engine_profile_token(insg_engine *e, int token, float *ms, uint64_t *bytes, int *launches);
+/* Profiling aid: every fused-GEMV launch of a token step writes its per-CTA phase timestamps (insg_gemv_op.trace) into
+ * device_buffer + launch_index * 296 * 8 * 8 bytes (162 launches fit in 3.1 MB).  Must be set before the first
+ * forward_token (the pointers are baked into the captured graph).  NULL disables. */
+INSG_API int insg_engine_set_trace(insg_engine *e, void *device_buffer);
 INSG_API int insg_engine_position(insg_engine *e);
 INSG_API int insg_engine_set_position(insg_engine *e, int position);
 /* Re-zeroes the recurrent state and position (what constructing a fresh DecodeWorkspace does). */

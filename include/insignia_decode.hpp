@@ -28,6 +28,7 @@ struct DecodeOptions {
     bool accurate_trig = false;    // false: __powf/__sinf/__cosf for RoPE (src/ops.cu:9); true: powf/sincosf
     bool use_graph = true;         // replay the token step from a CUDA graph
     bool use_pdl = true;           // programmatic dependent launch between kernels
+    bool gemv_tcgen05 = false;     // true: weights through tcgen05.mma kind::mxf4 (TMA-fed); false: the mma.sync streaming kernel
     int n_layers = Qwen35Shape::layers;
     int vocab = Qwen35Shape::vocab;
 };
@@ -56,6 +57,8 @@ public:
     int *d_next{};       // device: arg-max of the last logits
     void *attn_scratch{};
     void *argmax_scratch{};
+    void *trace{};       // optional profiling buffer: [GEMV launch of the step][296 CTAs][8] u64 timestamps (see insg_gemv_op.trace)
+    int trace_index{};   // GEMV launches enqueued since the step began
     void reset(); // zero recurrent state and position, as a fresh workspace
 
 private:

@@ -31,6 +31,7 @@ struct PackedMatrix {
     const void *data{};
     int rows{}, cols{};
     uint64_t bytes{};
+    int layout{}; // 0: 16-row records (insg_mxfp4_repack), 1: 128-row tcgen05 images (insg_mxfp4_repack_umma)
 };
 
 class INSIGNIA_API Qwen35Weights final {
@@ -45,7 +46,7 @@ public:
     TieredStorage &storage() noexcept { return storage_; }
 
     // Additive: packed copy of matrix `base` for the fused GEMV kernels (built on first call).
-    PackedMatrix packed(const std::string &base);
+    PackedMatrix packed(const std::string &base, int layout = 0);
     uint64_t packed_bytes() const noexcept { return packed_bytes_; }
 
 private:

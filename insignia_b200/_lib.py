@@ -23,7 +23,7 @@ class GemvSegment(C.Structure):
 class GemvOp(C.Structure):
     _fields_ = [("in_", vp), ("aux", vp), ("norm_w", vp), ("x_out", vp), ("cols", i32), ("prologue", i32),
                 ("n_segments", i32), ("seg", GemvSegment * 4), ("argmax_scratch", vp), ("token_out", vp),
-                ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("trace", vp), ("pdl", i32)]
+                ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("trace", vp), ("layout", i32), ("error_flag", vp), ("pdl", i32)]
 
 
 class AttnOp(C.Structure):
@@ -34,7 +34,7 @@ class AttnOp(C.Structure):
 
 class EngineOptions(C.Structure):
     _fields_ = [("device_budget_bytes", u64), ("max_context", i32), ("kv_dtype", i32), ("gate_elementwise", i32),
-                ("accurate_trig", i32), ("use_graph", i32), ("use_pdl", i32), ("n_layers", i32), ("vocab", i32),
+                ("accurate_trig", i32), ("use_graph", i32), ("use_pdl", i32), ("gemv_tcgen05", i32), ("n_layers", i32), ("vocab", i32),
                 ("device", i32)]
 
 
@@ -50,6 +50,8 @@ SIGNATURES = {
     "insg_mxfp4_dequant_mlx": (i32, [vp, vp, vp, i32, i32, vp]),
     "insg_mxfp4_packed_bytes": (sz, [i32, i32]),
     "insg_mxfp4_repack": (i32, [vp, vp, vp, i32, i32, vp]),
+    "insg_mxfp4_packed_umma_bytes": (sz, [i32, i32]),
+    "insg_mxfp4_repack_umma": (i32, [vp, vp, vp, i32, i32, vp]),
     "insg_mxfp4_gemv_packed": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "insg_gemv_argmax_scratch_bytes": (sz, []),
     "insg_gemv_fused": (i32, [C.POINTER(GemvOp), vp]),
@@ -82,6 +84,7 @@ SIGNATURES = {
     "insg_engine_mtp_draft": (i32, [vp, i32]),
     "insg_engine_generate": (i32, [vp, i32, i32, C.POINTER(i32)]),
     "insg_engine_profile_token": (i32, [vp, i32, vp, vp, vp]),
+    "insg_engine_set_trace": (i32, [vp, vp]),
     "insg_engine_position": (i32, [vp]),
     "insg_engine_set_position": (i32, [vp, i32]),
     "insg_engine_reset": (i32, [vp]),

@@ -22,7 +22,8 @@ namespace insg {
 constexpr int kAtThreads = 256;
 constexpr int kAtWarps = 8;
 constexpr int kSplits = 37;                  // 4 kv heads x 37 = 148 CTAs
-constexpr int kMinChunk = 64;                // tokens per split at least
+constexpr int kGroup = 4;                    // tokens a warp scores at once
+constexpr int kMinChunk = kAtWarps * kGroup; // tokens per split at least: one group per warp
 constexpr int kPartFloats = 8 + 4 * 256;     // m[4], l[4], acc[4][256]
 
 struct AttnParams {
@@ -40,6 +41,16 @@ struct AttnParams {
     unsigned *counters;    // [4] at the head of scratch
     float *partials;       // [4][kSplits][kPartFloats]
 };
+
+#ifdef INSG_ATTN_TRACE // development build only: stage clocks of every CTA of the last launch
+__device__ unsigned long long g_attn_trace[4 * kSplits][8];
+#define ATTN_TRACE(i)                                                                                   \
+    do {                                                                                                \
+        if (threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g_attn_trace[blockIdx.x][i])); \
+    } while (0)
+#else
+#define ATTN_TRACE(i) do { } while (0)
+#endif
 
 template <bool BF16> struct KvRow;
 template <> struct KvRow<false> {
@@ -68,16 +79,52 @@ template <> struct KvRow<true> {
     }
 };
 
+// Rows tb..tb+kGroup-1 of one kv head (those below `tend`; the rest read as zero).
+template <bool BF16>
+__device__ __forceinline__ void load_group(const void *kc, const void *vc, int kvh, int tb, int tend, int lane,
+                                           float (&kk)[kGroup][8], float (&vv)[kGroup][8])
+{
+#pragma unroll
+    for (int g = 0; g < kGroup; g++) {
+        const int t = tb + g;
+        if (t < tend) {
+            const size_t row = (size_t(t) * 4 + kvh) * 256;
+            KvRow<BF16>::load(kc, row, lane, kk[g]);
+            KvRow<BF16>::load(vc, row, lane, vv[g]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) { kk[g][j] = 0.f; vv[g][j] = 0.f; }
+        }
+    }
+}
+
+// cos/sin of the rotate-half RoPE for the 8 dims a lane owns (only lanes 0..7 rotate: dims 0..63).
+__device__ __forceinline__ void rope_table(int pos, int lane, bool fast, float (&c)[8], float (&s)[8])
+{
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int half = (lane * 8 + j) & 31;
+        if (fast) {
+            const float a = float(pos) * __powf(10000000.0f, -float(2 * half) / 64.0f);
+            c[j] = __cosf(a);
+            s[j] = __sinf(a);
+        } else {
+            const float a = float(pos) * powf(10000000.0f, -float(2 * half) / 64.0f);
+            sincosf(a, &s[j], &c[j]);
+        }
+    }
+}
+
 // RMSNorm over 256 (one warp, 8 values per lane, dims lane*8..+7) then rotate-half
 // RoPE on dims 0..63 (lanes 0..7; the partner dim i+-32 lives 4 lanes away).
-__device__ __forceinline__ void norm_rope_256(float (&v)[8], const uint16_t *w, int lane, int pos, bool fast)
+__device__ __forceinline__ void norm_rope_256(float (&v)[8], const uint4 wv, int lane, int pos, const float (&c)[8],
+                                              const float (&s)[8])
 {
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; j++) ss = fmaf(v[j], v[j], ss);
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / 256.f + 1e-6f);
-    const uint4 wv = reinterpret_cast<const uint4 *>(w)[lane];
     const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
     for (int j = 0; j < 8; j++) {
@@ -88,19 +135,7 @@ __device__ __forceinline__ void norm_rope_256(float (&v)[8], const uint16_t *w, 
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const float other = __shfl_xor_sync(0xffffffffu, v[j], 4);
-            if (lane < 8) {
-                const int i = lane * 8 + j, half = i & 31;
-                float c, s;
-                if (fast) {
-                    const float a = float(pos) * __powf(10000000.0f, -float(2 * half) / 64.0f);
-                    c = __cosf(a);
-                    s = __sinf(a);
-                } else {
-                    const float a = float(pos) * powf(10000000.0f, -float(2 * half) / 64.0f);
-                    sincosf(a, &s, &c);
-                }
-                v[j] = v[j] * c + (i < 32 ? -other : other) * s;
-            }
+            if (lane < 8) v[j] = v[j] * c[j] + (lane < 4 ? -other : other) * s[j];
         }
     }
 }
@@ -113,22 +148,56 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     __shared__ float s_m[kAtWarps][4], s_l[kAtWarps][4];
     __shared__ __align__(16) float s_acc[kAtWarps][4][256];
     __shared__ int s_last;
+    __shared__ float s_e[64][4], s_lg[4];
 
     const int kvh = blockIdx.x / kSplits, split = blockIdx.x % kSplits;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
+    ATTN_TRACE(0);
     pdl_launch_dependents();
-    pdl_wait();
 
-    int tokens = p.tokens, pos = -1;
+    // Geometry from the position as it is visible now.  Cache rows of earlier tokens never change
+    // again, so the first token group of every warp is fetched while the producer of q still runs;
+    // the position is read again after the wait and the fetch repeated if it moved.
+    int pos = -1, tokens = p.tokens;
     if constexpr (FUSED) {
         pos = __ldcg(p.position) + p.position_offset;
         tokens = pos + 1;
     }
-    if (tokens > p.max_context) tokens = p.max_context; // host checks; never index past the cache
-    const int chunk = max(kMinChunk, (tokens + kSplits - 1) / kSplits);
-    const int nsplit = (tokens + chunk - 1) / chunk;
-    const int t0 = split * chunk, t1 = min(tokens, t0 + chunk);
+    tokens = max(1, min(tokens, p.max_context)); // host checks; never index past the cache
+    int chunk = max(kMinChunk, (tokens + kSplits - 1) / kSplits);
+    int nsplit = (tokens + chunk - 1) / chunk;
+    int t0 = split * chunk, t1 = min(tokens, t0 + chunk);
+    int fresh = tokens - 1; // the row the producer (or this kernel) is still writing
+
+    float kk[kGroup][8], vv[kGroup][8];
+    load_group<BF16>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, kk, vv);
+    uint4 norm_wv = make_uint4(0u, 0u, 0u, 0u);
+    float rope_c[8], rope_s[8];
+    if constexpr (FUSED) {
+        if (warp < 5) {
+            norm_wv = reinterpret_cast<const uint4 *>(warp < 4 ? p.q_w : p.k_w)[lane];
+            if (lane < 8) rope_table(pos, lane, p.fast_trig != 0, rope_c, rope_s);
+        }
+    }
+
+    pdl_wait();
+    ATTN_TRACE(1);
+
+    if constexpr (FUSED) {
+        const int now = __ldcg(p.position) + p.position_offset;
+        if (now != pos) {
+            pos = now;
+            tokens = max(1, min(pos + 1, p.max_context));
+            chunk = max(kMinChunk, (tokens + kSplits - 1) / kSplits);
+            nsplit = (tokens + chunk - 1) / chunk;
+            t0 = split * chunk;
+            t1 = min(tokens, t0 + chunk);
+            fresh = tokens - 1;
+            load_group<BF16>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, kk, vv);
+            if (warp < 5 && lane < 8) rope_table(pos, lane, p.fast_trig != 0, rope_c, rope_s);
+        }
+    }
     const bool has_work = t0 < tokens;
 
     if (has_work) {
@@ -136,18 +205,18 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         if constexpr (FUSED) {
             if (warp < 4) {
                 float v[8];
-                const float *src = p.q + size_t(kvh * 4 + warp) * 512 + lane * 8;
-#pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = __ldcg(src + j);
-                norm_rope_256(v, p.q_w, lane, pos, p.fast_trig != 0);
+                const float4 *src = reinterpret_cast<const float4 *>(p.q + size_t(kvh * 4 + warp) * 512 + lane * 8);
+                const float4 a = __ldcg(src), b = __ldcg(src + 1);
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+                norm_rope_256(v, norm_wv, lane, pos, rope_c, rope_s);
 #pragma unroll
                 for (int j = 0; j < 8; j++) s_q[warp][lane * 8 + j] = v[j];
             } else if (warp == 4 && pos >= t0 && pos < t1) {
                 float v[8];
-                const float *src = p.k_raw + kvh * 256 + lane * 8;
-#pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = __ldcg(src + j);
-                norm_rope_256(v, p.k_w, lane, pos, p.fast_trig != 0);
+                const float4 *src = reinterpret_cast<const float4 *>(p.k_raw + kvh * 256 + lane * 8);
+                const float4 a = __ldcg(src), b = __ldcg(src + 1);
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+                norm_rope_256(v, norm_wv, lane, pos, rope_c, rope_s);
                 const size_t row = (size_t(pos) * 4 + kvh) * 256 + lane * 8;
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
@@ -168,6 +237,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         }
     }
     __syncthreads();
+    ATTN_TRACE(2);
 
     if (has_work) {
         float q[4][8];
@@ -184,37 +254,61 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
 #pragma unroll
             for (int j = 0; j < 8; j++) acc[h][j] = 0.f;
         }
-        for (int t = t0 + warp; t < t1; t += kAtWarps) {
-            float kk[8], vv[8];
-            if (FUSED && t == pos) {
+        bool first = true;
+        for (int tb = t0 + warp * kGroup; tb < t1; tb += kAtWarps * kGroup, first = false) {
+            if (!first) load_group<BF16>(p.kc, p.vc, kvh, tb, min(t1, fresh), lane, kk, vv);
+            if (fresh >= tb && fresh < tb + kGroup && fresh < t1) { // the newest row: from shared memory or, after the wait, from the cache
 #pragma unroll
-                for (int j = 0; j < 8; j++) { kk[j] = s_knew[lane * 8 + j]; vv[j] = s_vnew[lane * 8 + j]; }
-            } else {
-                const size_t row = (size_t(t) * 4 + kvh) * 256;
-                Row::load(p.kc, row, lane, kk);
-                Row::load(p.vc, row, lane, vv);
+                for (int g = 0; g < kGroup; g++) {
+                    if (tb + g != fresh) continue;
+                    if constexpr (FUSED) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) { kk[g][j] = s_knew[lane * 8 + j]; vv[g][j] = s_vnew[lane * 8 + j]; }
+                    } else {
+                        const size_t row = (size_t(fresh) * 4 + kvh) * 256;
+                        Row::load(p.kc, row, lane, kk[g]);
+                        Row::load(p.vc, row, lane, vv[g]);
+                    }
+                }
             }
-            float s[4];
+            float s[kGroup][4];
+#pragma unroll
+            for (int g = 0; g < kGroup; g++)
+#pragma unroll
+                for (int h = 0; h < 4; h++) {
+                    float z = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) z = fmaf(q[h][j], kk[g][j], z);
+                    s[g][h] = z;
+                }
+#pragma unroll
+            for (int mk = 16; mk; mk >>= 1)
+#pragma unroll
+                for (int g = 0; g < kGroup; g++)
+#pragma unroll
+                    for (int h = 0; h < 4; h++) s[g][h] += __shfl_xor_sync(0xffffffffu, s[g][h], mk);
 #pragma unroll
             for (int h = 0; h < 4; h++) {
-                float z = 0.f;
+                float mn = m[h];
 #pragma unroll
-                for (int j = 0; j < 8; j++) z = fmaf(q[h][j], kk[j], z);
-                s[h] = z;
-            }
+                for (int g = 0; g < kGroup; g++)
+                    if (tb + g < t1) mn = fmaxf(mn, s[g][h]);
+                const float corr = __expf(m[h] - mn);
+                float pr[kGroup], psum = 0.f;
 #pragma unroll
-            for (int mk = 16; mk; mk >>= 1) {
-#pragma unroll
-                for (int h = 0; h < 4; h++) s[h] += __shfl_xor_sync(0xffffffffu, s[h], mk);
-            }
-#pragma unroll
-            for (int h = 0; h < 4; h++) {
-                const float mn = fmaxf(m[h], s[h]);
-                const float corr = __expf(m[h] - mn), pr = __expf(s[h] - mn);
+                for (int g = 0; g < kGroup; g++) {
+                    pr[g] = tb + g < t1 ? __expf(s[g][h] - mn) : 0.f;
+                    psum += pr[g];
+                }
                 m[h] = mn;
-                l[h] = fmaf(l[h], corr, pr);
+                l[h] = fmaf(l[h], corr, psum);
 #pragma unroll
-                for (int j = 0; j < 8; j++) acc[h][j] = fmaf(acc[h][j], corr, pr * vv[j]);
+                for (int j = 0; j < 8; j++) {
+                    float a = acc[h][j] * corr;
+#pragma unroll
+                    for (int g = 0; g < kGroup; g++) a = fmaf(pr[g], vv[g][j], a);
+                    acc[h][j] = a;
+                }
             }
         }
         // ---- fold the 8 warps --------------------------------------------------------
@@ -226,6 +320,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         }
     }
     __syncthreads();
+    ATTN_TRACE(3);
     float *part = p.partials + size_t(kvh * kSplits + split) * kPartFloats;
     if (has_work) {
         const int d = tid;
@@ -246,31 +341,52 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         }
     }
     // ---- last CTA of this kv head folds the splits -----------------------------------
+    ATTN_TRACE(4);
     __threadfence();
     __syncthreads();
+    ATTN_TRACE(5);
     if (tid == 0) {
         const unsigned ticket = atomicAdd(p.counters + kvh, 1u);
         s_last = (ticket == kSplits - 1);
     }
     __syncthreads();
+    ATTN_TRACE(6);
     if (s_last) {
         __threadfence();
-        const volatile float *pp = p.partials + size_t(kvh * kSplits) * kPartFloats;
-        const int d = tid;
-#pragma unroll
-        for (int h = 0; h < 4; h++) {
-            float mg = -3.0e38f;
-            for (int s = 0; s < nsplit; s++) mg = fmaxf(mg, pp[size_t(s) * kPartFloats + h]);
-            float lg = 0.f, a = 0.f;
-            for (int s = 0; s < nsplit; s++) {
-                const float e = __expf(pp[size_t(s) * kPartFloats + h] - mg);
-                lg = fmaf(pp[size_t(s) * kPartFloats + 4 + h], e, lg);
-                a = fmaf(pp[size_t(s) * kPartFloats + 8 + h * 256 + d], e, a);
-            }
-            p.out[size_t(kvh * 4 + h) * 256 + d] = a / lg;
+        const float *pp = p.partials + size_t(kvh * kSplits) * kPartFloats;
+        // weights of the splits: warp h takes query head h, a lane takes splits lane and lane+32
+        if (warp < 4) {
+            const int h = warp, sa = lane, sb = lane + 32;
+            const float ma = sa < nsplit ? __ldcg(pp + size_t(sa) * kPartFloats + h) : -3.0e38f;
+            const float mb = sb < nsplit ? __ldcg(pp + size_t(sb) * kPartFloats + h) : -3.0e38f;
+            const float la = sa < nsplit ? __ldcg(pp + size_t(sa) * kPartFloats + 4 + h) : 0.f;
+            const float lb = sb < nsplit ? __ldcg(pp + size_t(sb) * kPartFloats + 4 + h) : 0.f;
+            const float mg = warp_max(fmaxf(ma, mb));
+            const float ea = sa < nsplit ? __expf(ma - mg) : 0.f, eb = sb < nsplit ? __expf(mb - mg) : 0.f;
+            const float lg = warp_sum(fmaf(la, ea, lb * eb));
+            s_e[sa][h] = ea;
+            if (sb < kSplits) s_e[sb][h] = eb;
+            if (lane == 0) s_lg[h] = lg;
         }
+        __syncthreads();
+        // a thread owns four output dims of one head; the loads of different splits are independent
+        const int h = tid >> 6, c4 = tid & 63;
+        const float4 *src = reinterpret_cast<const float4 *>(pp + 8 + h * 256) + c4;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int s = 0; s < nsplit; s++) {
+            const float4 v = __ldcg(src + size_t(s) * (kPartFloats / 4));
+            const float e = s_e[s][h];
+            a.x = fmaf(v.x, e, a.x);
+            a.y = fmaf(v.y, e, a.y);
+            a.z = fmaf(v.z, e, a.z);
+            a.w = fmaf(v.w, e, a.w);
+        }
+        const float inv = 1.0f / s_lg[h];
+        reinterpret_cast<float4 *>(p.out + size_t(kvh * 4 + h) * 256)[c4] = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
         if (tid == 0) p.counters[kvh] = 0u;
     }
+    ATTN_TRACE(7);
 }
 
 template <bool BF16, bool FUSED> int launch_attn(const AttnParams &p, cudaStream_t st, bool pdl)
@@ -343,6 +459,13 @@ int insg_gqa_decode_noalloc(const float *q, const void *k_cache, const void *v_c
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(static attention scratch)");
     return attn_plain_launch(q, k_cache, v_cache, out, tokens, kv_dtype, scratch, stream);
 }
+
+#ifdef INSG_ATTN_TRACE
+__attribute__((visibility("default"))) int insg_debug_attn_trace(unsigned long long *host)
+{
+    return cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(g_attn_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 size_t insg_gqa_scratch_bytes(int tokens)
 {

@@ -38,6 +38,7 @@ int sm_count()
 }
 
 int gemv_tune(const char *key, int value);
+int umma_tune(const char *key, int value);
 
 } // namespace insg
 
@@ -48,6 +49,7 @@ int insg_version(void) { return 100; }
 int insg_tune_set(const char *key, int value)
 {
     if (!key) return insg::fail(INSG_E_ARG, "tune: null key");
+    if (insg::umma_tune(key, value) == INSG_OK) return INSG_OK;
     return insg::gemv_tune(key, value);
 }
 

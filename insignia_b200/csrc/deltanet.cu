@@ -52,6 +52,9 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
         qv = __ldcg(q16 + kh * 128 + tid);
         kv = __ldcg(k16 + kh * 128 + tid);
     }
+    // every dependent input is requested now, so the later stages do not each pay a trip to L2
+    const float g_in = __ldcg(g32 + head), beta = __ldcg(beta32 + head);
+    const float v_in = tid < 32 ? __ldcg(v32 + head * 128 + slice * 32 + tid) : 0.f;
     float qn = warp_sum(qv * qv), kn = warp_sum(kv * kv);
     if (lane == 0) { s_red[warp] = qn; s_red[8 + warp] = kn; }
     __syncthreads();
@@ -61,8 +64,7 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
     if (tid < 128) { s_q[tid] = qv * qs; s_k[tid] = kv * ks; }
     __syncthreads();
 
-    const float decay = expf(__ldcg(g32 + head));
-    const float beta = __ldcg(beta32 + head);
+    const float decay = expf(g_in);
 
     // mem_v = sum_i (S*d) * k
     float4 pm = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -88,7 +90,7 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
         float mem = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; w++) mem += s_part[w][tid];
-        s_delta[tid] = (__ldcg(v32 + head * 128 + slice * 32 + tid) - mem) * beta;
+        s_delta[tid] = (v_in - mem) * beta;
     }
     __syncthreads();
     const float4 dl = *reinterpret_cast<const float4 *>(&s_delta[vq * 4]);

@@ -26,6 +26,7 @@
 //     prologues on the activation, residual / conv+SiLU / decay / beta / SwiGLU / logits+arg-max
 //     epilogues on the rows.
 #include "common.cuh"
+#include "gemv_prologue.cuh"
 #include "host_util.h"
 
 #include <algorithm>
@@ -36,7 +37,6 @@ namespace insg {
 constexpr int kRec = 1088;  // bytes per (16-row tile, 128-k block) record
 constexpr int kWarps = 16;  // warps per CTA, one CTA per SM
 constexpr int kThreads = kWarps * 32;
-constexpr int kMaxVec = 6;  // float4 per thread the prologue holds in registers (cols <= 12288)
 constexpr float kLoScale = 1.0f / 2048.0f;
 
 struct SegDev {
@@ -63,6 +63,7 @@ struct GemvParams {
     unsigned *argmax_ticket;
     int *token_out, *token_feedback, *token_log, *position_inout;
     unsigned long long *trace; // optional [grid][8] phase timestamps (ns), or null
+    int *error_flag;           // RING: raised when a bounded wait expires
 };
 
 __device__ __forceinline__ unsigned long long global_ns()
@@ -167,123 +168,38 @@ template <int UNR> __device__ __forceinline__ void load_chunk(const GemvParams &
     }
 }
 
-__device__ __forceinline__ float block_sum16(float v, float *scratch)
+// ---- shared-memory ring helpers (RING variant) ----------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void ring_bar_init(uint64_t *b) { asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(b))); }
+// one record HBM -> shared memory; the stage's mbarrier completes when all 1088 bytes have landed
+__device__ __forceinline__ void ring_issue(void *dst, const void *src, uint64_t *bar)
 {
-    v = warp_sum(v);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float t = 0.f;
-#pragma unroll
-    for (int i = 0; i < kWarps; i++) t += scratch[i];
-    return t;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(kRec) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(dst)), "l"(src), "r"(kRec), "r"(smem_addr(bar)) : "memory");
 }
-__device__ __forceinline__ float block_max16(float v, float *scratch)
+// bounded wait; false (and the CTA-wide abort flag raised) if the data never arrives
+__device__ __forceinline__ bool ring_wait(uint64_t *bar, uint32_t parity, int *abort_flag)
 {
-    v = warp_max(v);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float t = scratch[0];
-#pragma unroll
-    for (int i = 1; i < kWarps; i++) t = fmaxf(t, scratch[i]);
-    return t;
+    for (uint32_t it = 0; it < (1u << 22); it++) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred q;\nmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\nselp.u32 %0, 1, 0, q;\n}"
+                     : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    *abort_flag = 1;
+    return false;
 }
 
 // ---- activation prologue: fp32 vector -> two fp16 pieces in shared memory ----
-// One pass: the vector is read once (ld.global.cg: under programmatic dependent launch this CTA may
-// have been resident, and its L1 filled, before the producer wrote it), kept in registers through
-// the reductions, and written as hi/lo halves.  Returns 1/alpha, which undoes the pre-scale.
-__device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, float *scratch)
+// Returns 1/alpha, which undoes the power-of-two pre-scale.
+__device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, const uint2 (&wpre)[kPreVec], float *scratch)
 {
-    const int cols = p.cols, tid = threadIdx.x, lane = tid & 31;
-    const float *in = p.in + size_t(m) * cols;
-    const int nvec = cols >> 2;
+    const ProIn pin{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue};
     float4 v[kMaxVec];
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < kMaxVec; j++) {
-        const int i = tid + j * kThreads;
-        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (i < nvec) v[j] = __ldcg(reinterpret_cast<const float4 *>(in) + i);
-        ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
-    }
-    float inv_rms = 1.f;
-    float amax = 0.f;
-    if (p.prologue == INSG_PRO_RMSNORM) {
-        // one reduction round for both the sum of squares and max|x*w| (the maximum after scaling is that times inv_rms)
-        float pre = 0.f;
-#pragma unroll
-        for (int j = 0; j < kMaxVec; j++) {
-            const int i = tid + j * kThreads;
-            if (i < nvec) {
-                const uint2 wv = reinterpret_cast<const uint2 *>(p.norm_w)[i];
-                pre = fmaxf(pre, fmaxf(fmaxf(fabsf(v[j].x * bf16_bits_to_float(wv.x & 0xffff)), fabsf(v[j].y * bf16_bits_to_float(wv.x >> 16))),
-                                       fmaxf(fabsf(v[j].z * bf16_bits_to_float(wv.y & 0xffff)), fabsf(v[j].w * bf16_bits_to_float(wv.y >> 16)))));
-            }
-        }
-        ss = warp_sum(ss);
-        pre = warp_max(pre);
-        __syncthreads();
-        if (lane == 0) { scratch[tid >> 5] = ss; scratch[16 + (tid >> 5)] = pre; }
-        __syncthreads();
-        float tot = 0.f, mx = 0.f;
-#pragma unroll
-        for (int i = 0; i < kWarps; i++) { tot += scratch[i]; mx = fmaxf(mx, scratch[16 + i]); }
-        inv_rms = rsqrtf(tot / float(cols) + 1e-6f);
-        amax = mx * inv_rms;
-    }
-#pragma unroll
-    for (int j = 0; j < kMaxVec; j++) {
-        const int i = tid + j * kThreads;
-        if (i < nvec) { // warp-uniform: nvec is a multiple of 32
-            float4 x = v[j];
-            const int k = i << 2;
-            switch (p.prologue) {
-            case INSG_PRO_RMSNORM: {
-                const uint2 wv = reinterpret_cast<const uint2 *>(p.norm_w)[i];
-                x.x = x.x * inv_rms * bf16_bits_to_float(wv.x & 0xffff);
-                x.y = x.y * inv_rms * bf16_bits_to_float(wv.x >> 16);
-                x.z = x.z * inv_rms * bf16_bits_to_float(wv.y & 0xffff);
-                x.w = x.w * inv_rms * bf16_bits_to_float(wv.y >> 16);
-                break;
-            }
-            case INSG_PRO_GATED_RMSNORM: {
-                // a warp covers one 128-wide head per j (32 lanes x float4)
-                const float hs = warp_sum(fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w))));
-                const float inv = rsqrtf(hs / 128.f + 1e-6f);
-                const uint2 wv = reinterpret_cast<const uint2 *>(p.norm_w)[lane];
-                const float4 z = __ldcg(reinterpret_cast<const float4 *>(p.aux + size_t(m) * cols) + i);
-                x.x = x.x * inv * bf16_bits_to_float(wv.x & 0xffff) * fast_silu(z.x);
-                x.y = x.y * inv * bf16_bits_to_float(wv.x >> 16) * fast_silu(z.y);
-                x.z = x.z * inv * bf16_bits_to_float(wv.y & 0xffff) * fast_silu(z.z);
-                x.w = x.w * inv * bf16_bits_to_float(wv.y >> 16) * fast_silu(z.w);
-                break;
-            }
-            case INSG_PRO_SIGMOID_GATE: {
-                const float4 g = __ldcg(reinterpret_cast<const float4 *>(p.aux + size_t(m) * cols) + i);
-                x.x *= fast_sigmoid(g.x); x.y *= fast_sigmoid(g.y); x.z *= fast_sigmoid(g.z); x.w *= fast_sigmoid(g.w);
-                break;
-            }
-            case INSG_PRO_SIGMOID_GATE_HEAD0: {
-                const float g = fast_sigmoid(__ldcg(p.aux + size_t(m) * 2 * cols + (k >> 8) * 512 + 256));
-                x.x *= g; x.y *= g; x.z *= g; x.w *= g;
-                break;
-            }
-            case INSG_PRO_SIGMOID_GATE_QPROJ: {
-                const float4 g =
-                    __ldcg(reinterpret_cast<const float4 *>(p.aux + size_t(m) * 2 * cols + (k >> 8) * 512 + 256 + (k & 255)));
-                x.x *= fast_sigmoid(g.x); x.y *= fast_sigmoid(g.y); x.z *= fast_sigmoid(g.z); x.w *= fast_sigmoid(g.w);
-                break;
-            }
-            default: break;
-            }
-            v[j] = x;
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
-            if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out + size_t(m) * cols)[i] = x;
-        }
-    }
-    const float tmax = p.prologue == INSG_PRO_RMSNORM ? amax : block_max16(amax, scratch);
+    load_activation(pin, m, v);
+    const float tmax = transform_activation(pin, m, v, wpre, scratch);
+    const int tid = threadIdx.x, nvec = p.cols >> 2;
     // alpha = 2^(12 - floor(log2(max))) puts the largest element in [2^12, 2^13): fp16 holds it with room to spare
     int eb = int((__float_as_uint(tmax) >> 23) & 0xffu);
     eb = min(max(eb, 20), 240);
@@ -341,8 +257,12 @@ __device__ __forceinline__ void row_epilogue(const SegDev &s, int row, int m, fl
     }
 }
 
-template <int UNR, int M>
-__global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_constant__ GemvParams p)
+// RING = false: weights prefetched into registers (two chunks of UNR records per warp).
+// RING = true : weights prefetched into a per-warp shared-memory ring of UNR stages by cp.async.bulk with mbarrier
+//               completion; the kernel then needs half the registers, so two CTAs (this launch's and, under programmatic
+//               dependent launch, the next one's, already filling its ring) fit on an SM.
+template <int UNR, int M, bool RING>
+__global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(const __grid_constant__ GemvParams p)
 {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -354,6 +274,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
     float *scratch = rec + size_t(kWarps) * p.slots * M * 16;                                    // 64 floats
     __shared__ int s_last;
     __shared__ int s_wa[kWarps + 1], s_tmf[kWarps]; // warp boundaries in the record sequence, first run of each warp
+    __shared__ __align__(8) uint64_t s_bar[RING ? kWarps * UNR : 1];
+    __shared__ int s_abort;
+    uint8_t *wring = reinterpret_cast<uint8_t *>(scratch + 64) + size_t(warp) * UNR * kRec; // RING: this warp's stages
 
     INSG_TRACE(0);
     pdl_launch_dependents();
@@ -372,9 +295,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
 
     UnitIt lit;
     it_set(p, lit, ua);
-    Chunk<UNR> A, B;
-    load_chunk<UNR>(p, A, lit, ub, lane);
-    load_chunk<UNR>(p, B, lit, ub, lane);
+    Chunk<RING ? 1 : UNR> A, B;
+    if constexpr (RING) {
+        if (tid == 0) s_abort = 0;
+        if (lane == 0) {
+            for (int d = 0; d < UNR; d++) ring_bar_init(&s_bar[warp * UNR + d]);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+        // weights do not depend on the previous kernel: fill the ring before the dependency wait
+        for (int d = 0; d < UNR; d++) {
+            if (lit.u < ub) {
+                if (lane == 0) ring_issue(wring + size_t(d) * kRec, lit.ptr, &s_bar[warp * UNR + d]);
+                it_next(p, lit);
+            }
+        }
+    } else {
+        load_chunk<UNR>(p, A, lit, ub, lane);
+        load_chunk<UNR>(p, B, lit, ub, lane);
+    }
+    uint2 wpre[kPreVec];
+    preload_norm_weights(ProIn{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue}, wpre);
     INSG_TRACE(1);
 
     pdl_wait();
@@ -382,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
 
     float inv_alpha[M];
 #pragma unroll
-    for (int m = 0; m < M; m++) inv_alpha[m] = prologue(p, m, xs, xstride, scratch);
+    for (int m = 0; m < M; m++) inv_alpha[m] = prologue(p, m, xs, xstride, wpre, scratch);
     __syncthreads();
     INSG_TRACE(3);
 
@@ -396,9 +337,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
     // consume one chunk: multiply its records, closing a (tile, matrix) run whenever one ends
     UnitIt cit;
     it_set(p, cit, ua);
-    auto compute = [&](const Chunk<UNR> &ch) {
+    auto compute = [&](const Chunk<RING ? 1 : UNR> &ch) {
 #pragma unroll
-        for (int j = 0; j < UNR; j++) {
+        for (int j = 0; j < (RING ? 1 : UNR); j++) {
             if (cit.u >= ub) break; // warp-uniform
             float cc[M][4];
 #pragma unroll
@@ -448,12 +389,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
         }
     };
 
-    while (cit.u < ub) {
-        compute(A);
-        load_chunk<UNR>(p, A, lit, ub, lane);
-        if (cit.u >= ub) break;
-        compute(B);
-        load_chunk<UNR>(p, B, lit, ub, lane);
+    if constexpr (RING) {
+        for (int idx = 0; cit.u < ub; idx++) {
+            const int st = idx % UNR;
+            uint64_t *bar = &s_bar[warp * UNR + st];
+            if (!ring_wait(bar, (idx / UNR) & 1, &s_abort)) break;
+            const uint8_t *stage = wring + size_t(st) * kRec;
+            A.wa[0] = *reinterpret_cast<const uint4 *>(stage + lane * 16);
+            A.wb[0] = *reinterpret_cast<const uint4 *>(stage + 512 + lane * 16);
+            A.sc[0] = *reinterpret_cast<const uint16_t *>(stage + 1024 + lane * 2);
+            __syncwarp(); // every lane has its copy: the stage may be overwritten
+            if (lit.u < ub) {
+                if (lane == 0) ring_issue(wring + size_t(st) * kRec, lit.ptr, bar);
+                it_next(p, lit);
+            }
+            compute(A);
+        }
+    } else {
+        while (cit.u < ub) {
+            compute(A);
+            load_chunk<UNR>(p, A, lit, ub, lane);
+            if (cit.u >= ub) break;
+            compute(B);
+            load_chunk<UNR>(p, B, lit, ub, lane);
+        }
+    }
+    if constexpr (RING) {
+        if (tid == 0 && s_abort && p.error_flag) *p.error_flag = 1;
     }
     INSG_TRACE(4);
     __syncthreads();
@@ -485,6 +447,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
                     }
                     y[mat] = z;
                 }
+                if (tmq == tm_lo) INSG_TRACE(7);
                 row_epilogue(s, (tm0 - s.tm_begin) / s.nmat * 16 + row, m, y[0], y[1], best, best_idx);
             }
         }
@@ -551,33 +514,45 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fused_kernel(const __grid_co
 // ---- host side ------------------------------------------------------------------
 namespace {
 struct Tuning {
-    int unr = 4; // records per prefetch chunk
+    int unr = 4;  // records per prefetch chunk (register variant)
+    int ring = 0; // > 0: shared-memory ring variant with up to this many stages per warp
+    int ctas_per_sm = 1;
 } g_tune;
 
-constexpr int kMaxGrid = 256;
+constexpr int kMaxGrid = 296;
 
-template <int UNR, int M> int launch_variant(const GemvParams &p, int grid, size_t smem, cudaStream_t st, bool pdl)
+template <int UNR, int M, bool RING> int launch_variant(const GemvParams &p, int grid, size_t smem, cudaStream_t st, bool pdl)
 {
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(gemv_fused_kernel<UNR, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        attr_err = cudaFuncSetAttribute(gemv_fused_kernel<UNR, M, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(gemv)");
-    return launch(gemv_fused_kernel<UNR, M>, dim3(grid), dim3(kThreads), smem, st, pdl, p);
+    return launch(gemv_fused_kernel<UNR, M, RING>, dim3(grid), dim3(kThreads), smem + (RING ? size_t(kWarps) * UNR * kRec : 0), st, pdl, p);
 }
 
 template <int M> int dispatch(const GemvParams &p, int grid, size_t smem, cudaStream_t st, bool pdl)
 {
-    if (g_tune.unr == 2) return launch_variant<2, M>(p, grid, smem, st, pdl);
-    return launch_variant<4, M>(p, grid, smem, st, pdl);
+    if (g_tune.ring) {
+        // stages per warp: as deep as fits next to the activation copy while leaving room for a second CTA on the SM
+        if (smem + size_t(kWarps) * 4 * kRec <= 112 * 1024 && g_tune.ring >= 4) return launch_variant<4, M, true>(p, grid, smem, st, pdl);
+        if (smem + size_t(kWarps) * 3 * kRec <= 112 * 1024 && g_tune.ring >= 3) return launch_variant<3, M, true>(p, grid, smem, st, pdl);
+        return launch_variant<2, M, true>(p, grid, smem, st, pdl);
+    }
+    if (g_tune.unr == 2) return launch_variant<2, M, false>(p, grid, smem, st, pdl);
+    return launch_variant<4, M, false>(p, grid, smem, st, pdl);
 }
 } // namespace
+
+int gemv_umma_launch(const insg_gemv_op *op, cudaStream_t st);
 
 int gemv_tune(const char *key, int value)
 {
     const std::string k = key;
     if (k == "gemv_unr") g_tune.unr = value == 2 ? 2 : 4;
+    else if (k == "gemv_ring") g_tune.ring = std::max(0, std::min(value, 4));
+    else if (k == "gemv_ctas_per_sm") g_tune.ctas_per_sm = std::max(1, std::min(value, 2));
     else return fail(INSG_E_ARG, "unknown tuning key");
     return INSG_OK;
 }
@@ -622,7 +597,7 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
     // one CTA per SM, each owning whole output tiles; its 16 warps split the tiles' records evenly
     p.etile_units = nmat_all * p.nkb;
     p.total_etiles = tm / nmat_all;
-    const int grid = std::max(1, std::min(std::min(sm_count(), kMaxGrid), p.total_etiles));
+    const int grid = std::max(1, std::min(std::min(sm_count() * (g_tune.ring ? g_tune.ctas_per_sm : 1), kMaxGrid), p.total_etiles));
     const int per_cta = (p.total_etiles + grid - 1) / grid * p.etile_units;
     p.slots = (per_cta / kWarps + 1 + p.nkb - 1) / p.nkb + 1;
     if (logits) {
@@ -636,6 +611,7 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
         p.position_inout = op->position_inout;
     }
     p.trace = static_cast<unsigned long long *>(op->trace);
+    p.error_flag = op->error_flag;
     const size_t smem = size_t(M) * 2 * (op->cols + 8) * sizeof(__half) + size_t(kWarps) * p.slots * M * 16 * 4 + 64 * 4;
     if (smem > 220 * 1024) return fail(INSG_E_LIMIT, "gemv: shared memory beyond 220 KB");
     const bool pdl = op->pdl != 0;
@@ -652,9 +628,13 @@ using namespace insg;
 
 extern "C" {
 
-size_t insg_gemv_argmax_scratch_bytes(void) { return 64 + size_t(8) * kMaxGrid; }
+size_t insg_gemv_argmax_scratch_bytes(void) { return 64 + size_t(8) * 512; }
 
-int insg_gemv_fused(const insg_gemv_op *op, insg_stream_t stream) { return gemv_fused_launch(op, 1, stream); }
+int insg_gemv_fused(const insg_gemv_op *op, insg_stream_t stream)
+{
+    if (op && op->layout == 1) return gemv_umma_launch(op, stream);
+    return gemv_fused_launch(op, 1, stream);
+}
 
 int insg_mxfp4_gemv_packed(const void *packed, const float *x, float *y, int rows, int cols, int M, insg_stream_t stream)
 {

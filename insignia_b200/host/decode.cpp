@@ -170,9 +170,10 @@ struct Loader {
         return v.data;
     }
     const uint16_t *bf16(const std::string &name, uint64_t n) { return static_cast<const uint16_t *>(small(name, DType::bf16, n * 2)); }
+    int layout;
     PackedMatrix mat(const std::string &base, int rows, int cols)
     {
-        PackedMatrix m = w.packed(base);
+        PackedMatrix m = w.packed(base, layout);
         if (m.rows != rows || m.cols != cols) throw std::runtime_error("unexpected matrix shape: " + base);
         return m;
     }
@@ -228,6 +229,9 @@ uint64_t gemv_bytes(const insg_gemv_op &op)
 void run_gemv(Ctx &c, insg_gemv_op &op)
 {
     op.pdl = c.pdl ? 1 : 0;
+    op.layout = c.x.options.gemv_tcgen05 ? 1 : 0;
+    op.error_flag = c.x.d_token + 3;
+    if (c.x.trace) op.trace = static_cast<uint8_t *>(c.x.trace) + size_t(c.x.trace_index++) * 296 * 8 * 8;
     Timed t(c, 0, gemv_bytes(op));
     insg_check(insg_gemv_fused(&op, c.st));
     c.launches++;
@@ -428,7 +432,7 @@ void Qwen35Decode::enqueue_delta(int l)
     Plan &p = plan();
     Plan::Block &b = p.layers[l];
     if (!b.ready) {
-        Loader L{w_, p.pinned};
+        Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
         load_delta(L, std::string(kLM) + ".model.layers." + std::to_string(l), b);
     }
     Ctx c{x_, p.stream, x_.options.use_pdl && !prof_, launches_, prof_};
@@ -440,7 +444,7 @@ void Qwen35Decode::enqueue_attention(int l)
     Plan &p = plan();
     Plan::Block &b = p.layers[l];
     if (!b.ready) {
-        Loader L{w_, p.pinned};
+        Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
         load_attention(L, std::string(kLM) + ".model.layers." + std::to_string(l), b);
     }
     const size_t esz = x_.options.kv_bf16 ? 2 : 4;
@@ -453,9 +457,9 @@ void Qwen35Decode::enqueue_head()
 {
     Plan &p = plan();
     if (!p.head_ready) {
-        Loader L{w_, p.pinned};
+        Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
         p.final_norm = L.bf16(std::string(kLM) + ".model.norm.weight", kHidden);
-        p.lm_head = w_.packed(std::string(kLM) + ".lm_head");
+        p.lm_head = w_.packed(std::string(kLM) + ".lm_head", x_.options.gemv_tcgen05 ? 1 : 0);
         if (p.lm_head.cols != kHidden || p.lm_head.rows < x_.options.vocab) throw std::runtime_error("unexpected matrix shape: language_model.lm_head");
         p.head_ready = true;
     }
@@ -505,6 +509,7 @@ void Qwen35Decode::layer(int l)
 // embed, all layers, head: what one graph replay does
 void Qwen35Decode::enqueue_token_step()
 {
+    x_.trace_index = 0;
     enqueue_embed();
     for (int l = 0; l < x_.options.n_layers; l++) {
         if (Qwen35Shape::full_attention(l)) enqueue_attention(l);
@@ -565,10 +570,11 @@ int Qwen35Decode::logits_argmax()
         insg_check(insg_argmax_logits(x_.logits, x_.options.vocab, x_.d_next, p.stream));
         launches_++;
     }
-    int result = -1;
-    cuda_check(cudaMemcpyAsync(&result, x_.d_next, sizeof(int), cudaMemcpyDeviceToHost, p.stream), "read token");
+    int result[2] = {-1, 0}; // next token, kernel wait-expired flag
+    cuda_check(cudaMemcpyAsync(result, x_.d_next, 2 * sizeof(int), cudaMemcpyDeviceToHost, p.stream), "read token");
     cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
-    return result;
+    if (result[1]) throw std::runtime_error("a bounded wait inside a GPU kernel expired");
+    return result[0];
 }
 
 int Qwen35Decode::decode_token(int token)
@@ -634,7 +640,7 @@ int Qwen35Decode::mtp_draft(int token)
     Plan &p = plan();
     const std::string m = std::string(kLM) + ".mtp";
     if (!p.mtp_ready) {
-        Loader L{w_, p.pinned};
+        Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
         p.mtp_fc = L.bf16(m + ".fc.weight", size_t(kHidden) * 2 * kHidden);
         p.mtp_norm_e = L.bf16(m + ".pre_fc_norm_embedding.weight", kHidden);
         p.mtp_norm_h = L.bf16(m + ".pre_fc_norm_hidden.weight", kHidden);

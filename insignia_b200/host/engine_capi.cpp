@@ -80,6 +80,7 @@ insg_engine *insg_engine_create(const char *index_path, const insg_engine_option
         d.accurate_trig = o.accurate_trig != 0;
         d.use_graph = o.use_graph != 0;
         d.use_pdl = o.use_pdl != 0;
+        d.gemv_tcgen05 = o.gemv_tcgen05 != 0;
         if (o.n_layers > 0) d.n_layers = o.n_layers;
         if (o.vocab > 0) d.vocab = o.vocab;
         if (d.n_layers > insignia::Qwen35Shape::layers || d.vocab > insignia::Qwen35Shape::vocab || (d.vocab & 15))
@@ -152,6 +153,12 @@ int insg_engine_profile_token(insg_engine *e, int token, float *ms, uint64_t *by
         e->dec->profile_token(token, ms, bytes, launches);
         return int(INSG_OK);
     });
+}
+int insg_engine_set_trace(insg_engine *e, void *device_buffer)
+{
+    if (!e) return insg::fail(INSG_E_ARG, "null engine");
+    e->ws->trace = device_buffer;
+    return INSG_OK;
 }
 int insg_engine_position(insg_engine *e) { return e ? e->ws->position : INSG_E_ARG; }
 int insg_engine_set_position(insg_engine *e, int position)

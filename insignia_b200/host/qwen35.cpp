@@ -55,14 +55,16 @@ void Qwen35Weights::embed(int token, float *device_hidden)
     if (rc != INSG_OK) throw std::runtime_error(insg_last_error());
 }
 
-PackedMatrix Qwen35Weights::packed(const std::string &base)
+PackedMatrix Qwen35Weights::packed(const std::string &base, int layout)
 {
-    if (auto it = packed_.find(base); it != packed_.end()) return it->second;
+    const std::string key = base + (layout ? "#umma" : "#rec");
+    if (auto it = packed_.find(key); it != packed_.end()) return it->second;
     QuantMatrix m = matrix(base);
     PackedMatrix p;
     p.rows = m.rows;
     p.cols = m.cols;
-    p.bytes = insg_mxfp4_packed_bytes(m.rows, m.cols);
+    p.layout = layout;
+    p.bytes = layout ? insg_mxfp4_packed_umma_bytes(m.rows, m.cols) : insg_mxfp4_packed_bytes(m.rows, m.cols);
     if (p.bytes == 0) {
         release(base);
         throw std::runtime_error("matrix shape not packable (rows % 16, cols % 128): " + base);
@@ -73,8 +75,9 @@ PackedMatrix Qwen35Weights::packed(const std::string &base)
         release(base);
         throw std::runtime_error(std::string("cudaMalloc packed matrix: ") + cudaGetErrorString(e));
     }
-    const int rc = insg_mxfp4_repack(static_cast<const uint32_t *>(m.weight.data), static_cast<const uint8_t *>(m.scales.data), d,
-                                     m.rows, m.cols, stream_);
+    const auto *wp = static_cast<const uint32_t *>(m.weight.data);
+    const auto *sp = static_cast<const uint8_t *>(m.scales.data);
+    const int rc = layout ? insg_mxfp4_repack_umma(wp, sp, d, m.rows, m.cols, stream_) : insg_mxfp4_repack(wp, sp, d, m.rows, m.cols, stream_);
     e = cudaStreamSynchronize(stream_);
     release(base); // the MLX copy becomes evictable again
     if (rc != INSG_OK || e != cudaSuccess) {
@@ -83,7 +86,7 @@ PackedMatrix Qwen35Weights::packed(const std::string &base)
     }
     p.data = d;
     packed_bytes_ += p.bytes;
-    packed_.emplace(base, p);
+    packed_.emplace(key, p);
     return p;
 }
 

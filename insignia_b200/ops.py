@@ -66,6 +66,18 @@ def repack(weight, scales):
     return packed
 
 
+def repack_umma(weight, scales):
+    """Weights in the layout of the tcgen05 kernel (pass ``layout=1`` to :func:`gemv_fused`)."""
+    rows, cols = weight.shape[0], weight.shape[1] * 8
+    n = _lib.lib().insg_mxfp4_packed_umma_bytes(rows, cols)
+    if n == 0:
+        raise ValueError("cols % 128 must be 0")
+    packed = torch.empty(n, dtype=torch.uint8, device=weight.device)
+    check(_lib.lib().insg_mxfp4_repack_umma(_p(weight), _p(scales), _p(packed), rows, cols, _stream()))
+    packed.rows, packed.cols = rows, cols
+    return packed
+
+
 def gemv_packed(packed, x, rows=None, cols=None):
     rows = rows or packed.rows
     cols = cols or packed.cols
@@ -75,7 +87,7 @@ def gemv_packed(packed, x, rows=None, cols=None):
     return y.reshape(*x.shape[:-1], rows)
 
 
-def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, trace=None):
+def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, trace=None, layout=0, error_flag=None):
     """``segments``: list of dicts with packed, out, rows, epilogue (+ packed2 / conv_state, conv_w / A_log, dt_bias).
     ``argmax``: dict(scratch, token_out[, token_feedback, token_log, position]) for the logits epilogue."""
     op = GemvOp()
@@ -92,6 +104,8 @@ def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=Non
         op.token_feedback, op.token_log = _p(argmax.get("token_feedback")), _p(argmax.get("token_log"))
         op.position_inout = _p(argmax.get("position"))
     op.trace = _p(trace)
+    op.layout = layout
+    op.error_flag = _p(error_flag)
     op.pdl = int(pdl)
     check(_lib.lib().insg_gemv_fused(C.byref(op), _stream()))
 

@@ -93,6 +93,21 @@ def test_generate_equals_decode_token_loop_bitwise(cuda, golden_ckpt):
         assert np.array_equal(state, base[2]), (graph, pdl, gen)
 
 
+def test_tcgen05_and_mma_sync_gemv_paths_agree(cuda, golden_ckpt):
+    """The two GEMV kernels (tcgen05 kind::mxf4 with a fixed-point activation, mma.sync with an fp16-pair activation)
+    decode the same tokens and stay within rounding of each other."""
+    from insignia_b200.checkpoint_io import SafetensorsReader
+
+    m = orc.OracleModel(SafetensorsReader(golden_ckpt[0]), max_context=64, gate="broadcast", n_layers=4)
+    with small_engine(golden_ckpt[1], gemv_tcgen05=True) as a, small_engine(golden_ckpt[1], gemv_tcgen05=False) as b:
+        for i, t in enumerate([42, 7, 63, 0, 21, 5, 33, 60]):
+            ta, tb, tm = a.decode_token(t), b.decode_token(t), m.decode_token(t)
+            assert ta == tb == tm, i
+            ha, hb = a.read("hidden"), b.read("hidden")
+            assert np.max(np.abs(ha - hb)) <= 2e-4 * np.abs(hb).max(), i
+            assert close(ha, m.hidden, 1e-3) and close(hb, m.hidden, 1e-3), i
+
+
 def test_kv_bf16_and_accurate_trig_modes(cuda, golden_ckpt):
     from insignia_b200.checkpoint_io import SafetensorsReader
 
