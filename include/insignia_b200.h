@@ -73,6 +73,21 @@ INSG_API int insg_set_scalars(int *device_token, int token, int *device_position
 INSG_API int insg_mxfp4_dequant_mlx(const uint32_t *weight, const uint8_t *scales, float *out, int rows, int cols,
                                     insg_stream_t stream);
 
+/* y[rows] = W x with W as 17-byte blocks {E8M0 scale, 16 bytes}: byte i of a block holds element i in its low
+ * nibble and element 16+i in its high nibble; block b of row r sits at byte (r * cols/32 + b) * 17.  A scale byte
+ * of 255 decodes to NaN in this layout's helper.  Replaces mxfp4_gemv (include/insignia_layout.cuh:11-15,45,
+ * src/mxfp4.cu:5-35), which the token loop never calls (checkpoints are MLX layout) but the reference's
+ * kernel test does (src/test_mxfp4.cu:31). */
+INSG_API int insg_mxfp4_gemv_blocks(const void *blocks, const float *x, float *y, int rows, int cols, insg_stream_t stream);
+
+/* The reference's int8 experiment (its microbenchmark only, src/bench_mxfp4_mlx.cu:9-11): quantise x per group
+ * of 32 to int8 with scale max|x|/127 (1 for an all-zero group), then y = W x with integer dot products of the
+ * doubled E2M1 codes.  Replace quantize_q8_groups and mxfp4_gemv_dp4a (include/insignia_layout.cuh:49-50,
+ * src/mxfp4.cu:83-127); warps_per_row is dropped.  Results differ from the fp32 GEMV by the int8 rounding of x. */
+INSG_API int insg_quantize_q8_groups(const float *x, int8_t *qx, float *qscale, int cols, insg_stream_t stream);
+INSG_API int insg_mxfp4_gemv_dp4a(const uint32_t *weight, const uint8_t *scales, const int8_t *qx, const float *qscale,
+                                  float *y, int rows, int cols, insg_stream_t stream);
+
 /* Tile-interleaved weight layout used by the fused GEMV kernels.  Same
  * information and the same byte count as the MLX layout (17 bytes per 32
  * weights): rows are grouped in tiles of 16, K in blocks of 128, and each
@@ -247,6 +262,9 @@ INSG_API int insg_rmsnorm_bf16(const float *x, const uint16_t *w, const float *g
 /* src/ops.cu:6 (rmsnorm_zero_centered, fp32 weight, 1+w) */
 INSG_API int insg_rmsnorm_zero_centered(const float *x, const float *w, float *y, int rows, int cols, float eps,
                                         insg_stream_t stream);
+/* src/ops.cu:6 (rmsnorm_gated_silu: fp32 weight used as is, result times silu(gate)) */
+INSG_API int insg_rmsnorm_gated_silu(const float *x, const float *w, const float *gate, float *y, int rows, int cols,
+                                     float eps, insg_stream_t stream);
 /* src/qwen_kernels.cu:8 */
 INSG_API int insg_causal_conv4_silu(float *x, float *state, const uint16_t *w, int channels, insg_stream_t stream);
 /* src/qwen_kernels.cu:10 */
@@ -317,6 +335,11 @@ INSG_API int insg_engine_generate(insg_engine *e, int first_token, int count, in
  * 2 attention, 3 embedding), the summed durations, the algorithmic bytes and the launch counts.
  * Advances the position like insg_engine_forward_token.  Synchronises.  No reference counterpart. */
 INSG_API int insg_engine_profile_token(insg_engine *e, int token, float *ms, uint64_t *bytes, int *launches);
+/* The fused-GEMV launches of one token step alone, captured as a CUDA graph with dependent-launch overlap and
+ * replayed `replays` (1..64) times between two CUDA events: *ms_per_token = time of one replay, *bytes = the
+ * algorithmic weight bytes of those launches, *launches = their count.  Needs one forwarded token first.  The
+ * sequence state is meaningless afterwards (call insg_engine_reset).  Synchronises.  No reference counterpart. */
+INSG_API int insg_engine_profile_gemv_chain(insg_engine *e, int replays, float *ms_per_token, uint64_t *bytes, int *launches);
 /* Profiling aid: every fused-GEMV launch of a token step writes its per-CTA phase timestamps (insg_gemv_op.trace) into
  * device_buffer + launch_index * 296 * 8 * 8 bytes (162 launches fit in 3.1 MB).  Must be set before the first
  * forward_token (the pointers are baked into the captured graph).  NULL disables. */

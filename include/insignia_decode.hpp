@@ -84,6 +84,11 @@ public:
     // Additive: one token step run eagerly with an event pair around every launch.  Index 0: fused GEMV,
     // 1: DeltaNet step, 2: attention, 3: embedding.  ms = summed durations, bytes = algorithmic bytes moved.
     void profile_token(int token, float ms[4], uint64_t bytes[4], int launches[4]);
+    // Additive: the fused-GEMV launches of one token step alone (no DeltaNet, attention or embedding kernels between
+    // them), captured as a graph with dependent-launch overlap and replayed `replays` times between two events.
+    // Gives the average in-flow duration of the dominant kernel.  The sequence state (hidden, convolution history)
+    // is meaningless afterwards: reset the workspace before decoding again.
+    void profile_gemv_chain(int replays, float *ms_per_token, uint64_t *bytes, int *launches);
     struct Plan; // resolved weight pointers + captured graph (opaque)
 
 private:

@@ -45,6 +45,9 @@ SIGNATURES = {
     "insg_tune_set": (i32, [C.c_char_p, i32]),
     "insg_mxfp4_gemv_mlx": (i32, [vp, vp, vp, vp, i32, i32, vp]),
     "insg_mxfp4_get_row_mlx": (i32, [vp, vp, vp, i32, i32, vp]),
+    "insg_mxfp4_gemv_blocks": (i32, [vp, vp, vp, i32, i32, vp]),
+    "insg_quantize_q8_groups": (i32, [vp, vp, vp, i32, vp]),
+    "insg_mxfp4_gemv_dp4a": (i32, [vp, vp, vp, vp, vp, i32, i32, vp]),
     "insg_mxfp4_embed": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "insg_set_scalars": (i32, [vp, i32, vp, i32, vp]),
     "insg_mxfp4_dequant_mlx": (i32, [vp, vp, vp, i32, i32, vp]),
@@ -62,6 +65,7 @@ SIGNATURES = {
     "insg_attention_step": (i32, [C.POINTER(AttnOp), vp]),
     "insg_rmsnorm_bf16": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "insg_rmsnorm_zero_centered": (i32, [vp, vp, vp, i32, i32, C.c_float, vp]),
+    "insg_rmsnorm_gated_silu": (i32, [vp, vp, vp, vp, i32, i32, C.c_float, vp]),
     "insg_causal_conv4_silu": (i32, [vp, vp, vp, i32, vp]),
     "insg_deltanet_parameters": (i32, [vp, vp, vp, vp, i32, vp]),
     "insg_qk_norm_rope": (i32, [vp, vp, vp, vp, i32, i32, vp]),
@@ -84,6 +88,7 @@ SIGNATURES = {
     "insg_engine_mtp_draft": (i32, [vp, i32]),
     "insg_engine_generate": (i32, [vp, i32, i32, C.POINTER(i32)]),
     "insg_engine_profile_token": (i32, [vp, i32, vp, vp, vp]),
+    "insg_engine_profile_gemv_chain": (i32, [vp, i32, vp, vp, vp]),
     "insg_engine_set_trace": (i32, [vp, vp]),
     "insg_engine_position": (i32, [vp]),
     "insg_engine_set_position": (i32, [vp, i32]),

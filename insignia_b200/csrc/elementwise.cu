@@ -225,6 +225,13 @@ int insg_rmsnorm_zero_centered(const float *x, const float *w, float *y, int row
     rmsnorm_kernel<true><<<rows, 256, 0, stream>>>(x, w, nullptr, y, cols, 1, eps);
     return check_launch("rmsnorm_zero_centered");
 }
+int insg_rmsnorm_gated_silu(const float *x, const float *w, const float *gate, float *y, int rows, int cols, float eps,
+                            insg_stream_t stream)
+{
+    if (!x || !w || !gate || !y || rows <= 0 || cols <= 0) return fail(INSG_E_ARG, "rmsnorm_gated_silu: bad argument");
+    rmsnorm_kernel<true><<<rows, 256, 0, stream>>>(x, w, gate, y, cols, 0, eps);
+    return check_launch("rmsnorm_gated_silu");
+}
 int insg_causal_conv4_silu(float *x, float *state, const uint16_t *w, int channels, insg_stream_t stream)
 {
     if (!x || !state || !w || channels <= 0) return fail(INSG_E_ARG, "causal_conv4_silu: bad argument");

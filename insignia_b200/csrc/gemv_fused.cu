@@ -427,6 +427,11 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
     if (b > a) {
         const int tm_lo = a / nkb, tm_hi = (b - 1) / nkb;
         const int row = lane & 15;
+        // warp boundaries into registers once: the sums below then issue their shared-memory reads together
+        int wr[kWarps + 1], tf[kWarps];
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) { wr[w] = s_wa[w]; tf[w] = s_tmf[w]; }
+        wr[kWarps] = s_wa[kWarps];
         // tasks are tiles: a run for plain segments, the (gate, up) pair of runs for SwiGLU
         for (int tmq = tm_lo + warp; tmq <= tm_hi; tmq += kWarps) {
             const SegDev &s = p.seg[seg_of(p, tmq)];
@@ -437,14 +442,15 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
                 float y[2] = {0.f, 0.f};
                 for (int mat = 0; mat < s.nmat; mat++) {
                     const int tm = tm0 + mat, lo = max(tm * nkb, a), hi = min((tm + 1) * nkb, b);
-                    float z = 0.f;
-                    if (hi > lo) {
-                        for (int w = 0; w < kWarps; w++) {
-                            const int wa_ = s_wa[w], wb_ = s_wa[w + 1];
-                            if (wb_ > wa_ && wa_ < hi && wb_ > lo)
-                                z += rec[((w * p.slots + (tm - s_tmf[w])) * M + m) * 16 + row];
-                        }
+                    float part[kWarps];
+#pragma unroll
+                    for (int w = 0; w < kWarps; w++) {
+                        const bool on = hi > lo && wr[w + 1] > wr[w] && wr[w] < hi && wr[w + 1] > lo;
+                        part[w] = on ? rec[((w * p.slots + (tm - tf[w])) * M + m) * 16 + row] : 0.f;
                     }
+                    float z = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kWarps; w++) z += part[w]; // warp order, whatever the schedule
                     y[mat] = z;
                 }
                 if (tmq == tm_lo) INSG_TRACE(7);

@@ -74,6 +74,12 @@ class Engine:
         names = ("gemv", "deltanet", "attention", "embed")
         return {n: {"ms": ms[i], "bytes": by[i], "launches": ln[i]} for i, n in enumerate(names)}
 
+    def profile_gemv_chain(self, replays: int = 8) -> dict:
+        """The token step's fused-GEMV launches alone as a replayed graph; the sequence state is garbage afterwards (reset())."""
+        ms, by, ln = C.c_float(), C.c_uint64(), C.c_int()
+        check(_lib.lib().insg_engine_profile_gemv_chain(self._h, replays, C.byref(ms), C.byref(by), C.byref(ln)))
+        return {"ms_per_token": ms.value, "bytes": by.value, "launches": ln.value}
+
     @property
     def position(self) -> int:
         return _lib.lib().insg_engine_position(self._h)

@@ -180,6 +180,19 @@ struct Loader {
 };
 } // namespace
 
+// Keeps the stream busy for a fixed time (bounded by the clock, not by another kernel) so that a
+// whole token's launches and their event pairs can be queued behind it: the events then bracket
+// device-side durations instead of the host's enqueue pace.
+__global__ void hold_stream_kernel(unsigned long long ns)
+{
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    do {
+        __nanosleep(2000);
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    } while (t - t0 < ns);
+}
+
 // --------------------------------------------------------------- enqueue helpers
 struct StepProfile {
     struct Ev {
@@ -188,6 +201,9 @@ struct StepProfile {
         uint64_t bytes;
     };
     std::vector<Ev> events;
+    bool gemv_only = false; // chain pass: only the fused GEMV launches are issued, no events
+    uint64_t gemv_bytes = 0;
+    int gemv_launches = 0;
 };
 
 namespace {
@@ -203,7 +219,7 @@ struct Ctx {
 struct Timed {
     StepProfile *p;
     cudaStream_t st;
-    Timed(Ctx &c, int cls, uint64_t bytes) : p(c.prof), st(c.st)
+    Timed(Ctx &c, int cls, uint64_t bytes) : p(c.prof && !c.prof->gemv_only ? c.prof : nullptr), st(c.st)
     {
         if (!p) return;
         cudaEvent_t a, b;
@@ -233,6 +249,10 @@ void run_gemv(Ctx &c, insg_gemv_op &op)
     op.error_flag = c.x.d_token + 3;
     if (c.x.trace) op.trace = static_cast<uint8_t *>(c.x.trace) + size_t(c.x.trace_index++) * 296 * 8 * 8;
     Timed t(c, 0, gemv_bytes(op));
+    if (c.prof && c.prof->gemv_only) {
+        c.prof->gemv_bytes += gemv_bytes(op);
+        c.prof->gemv_launches++;
+    }
     insg_check(insg_gemv_fused(&op, c.st));
     c.launches++;
 }
@@ -291,7 +311,7 @@ static void enqueue_delta_block(Ctx &c, const Qwen35Decode::Plan::Block &b, int 
     in.seg[3] = seg(b.b, x.b, INSG_EPI_BETA);
     run_gemv(c, in);
 
-    {
+    if (!(c.prof && c.prof->gemv_only)) {
         Timed t(c, 1, uint64_t(2) * 32 * 128 * 128 * 4); // state read + write
         insg_check(insg_deltanet_decode(x.delta_state + size_t(di) * 32 * 128 * 128, x.qkv, x.qkv + 2048, x.qkv + 4096, x.a, x.b,
                                         x.core, c.pdl ? 1 : 0, c.st));
@@ -343,7 +363,7 @@ static void enqueue_attention_block(Ctx &c, const Qwen35Decode::Plan::Block &b, 
     at.scratch = x.attn_scratch;
     at.scratch_bytes = insg_gqa_scratch_bytes(x.max_context);
     at.pdl = c.pdl ? 1 : 0;
-    {
+    if (!(c.prof && c.prof->gemv_only)) {
         Timed t(c, 2, uint64_t(x.position + 1) * 1024 * 2 * (x.options.kv_bf16 ? 2 : 4)); // K and V rows read
         insg_check(insg_attention_step(&at, c.st));
         c.launches++;
@@ -420,7 +440,8 @@ void Qwen35Decode::enqueue_embed()
         if (p.embed.cols != kHidden) throw std::runtime_error("unexpected matrix shape: " + base);
         p.embed_ready = true;
     }
-    Ctx c{x_, p.stream, x_.options.use_pdl && !prof_, launches_, prof_};
+    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_};
+    if (prof_ && prof_->gemv_only) return;
     Timed t(c, 3, uint64_t(kHidden) * 17 / 32);
     insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
                                 x_.hidden, x_.d_token, p.embed.rows, kHidden, c.pdl ? 1 : 0, p.stream));
@@ -435,7 +456,7 @@ void Qwen35Decode::enqueue_delta(int l)
         Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
         load_delta(L, std::string(kLM) + ".model.layers." + std::to_string(l), b);
     }
-    Ctx c{x_, p.stream, x_.options.use_pdl && !prof_, launches_, prof_};
+    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_};
     enqueue_delta_block(c, b, l - l / 4);
 }
 
@@ -449,7 +470,7 @@ void Qwen35Decode::enqueue_attention(int l)
     }
     const size_t esz = x_.options.kv_bf16 ? 2 : 4;
     const size_t off = size_t(l / 4) * x_.max_context * 1024 * esz;
-    Ctx c{x_, p.stream, x_.options.use_pdl && !prof_, launches_, prof_};
+    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_};
     enqueue_attention_block(c, b, reinterpret_cast<uint8_t *>(x_.kv_keys) + off, reinterpret_cast<uint8_t *>(x_.kv_values) + off, 0);
 }
 
@@ -463,7 +484,7 @@ void Qwen35Decode::enqueue_head()
         if (p.lm_head.cols != kHidden || p.lm_head.rows < x_.options.vocab) throw std::runtime_error("unexpected matrix shape: language_model.lm_head");
         p.head_ready = true;
     }
-    Ctx c{x_, p.stream, x_.options.use_pdl && !prof_, launches_, prof_};
+    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_};
     insg_gemv_op op = {};
     op.in = x_.hidden;
     op.norm_w = p.final_norm;
@@ -611,6 +632,7 @@ void Qwen35Decode::profile_token(int token, float ms[4], uint64_t bytes[4], int 
     StepProfile prof;
     sync_scalars(token);
     prof_ = &prof;
+    hold_stream_kernel<<<1, 1, 0, p.stream>>>(4000000ull); // 4 ms: longer than the host needs to queue one token
     try {
         enqueue_token_step(); // eager, one event pair per launch, no dependent-launch overlap
     } catch (...) {
@@ -631,6 +653,53 @@ void Qwen35Decode::profile_token(int token, float ms[4], uint64_t bytes[4], int 
         cudaEventDestroy(e.start);
         cudaEventDestroy(e.stop);
     }
+}
+
+void Qwen35Decode::profile_gemv_chain(int replays, float *ms_per_token, uint64_t *bytes, int *launches)
+{
+    Plan &p = plan();
+    if (!p.capturing && !p.exec) throw std::runtime_error("profile_gemv_chain needs a forwarded token (weights resident)");
+    replays = std::max(1, std::min(replays, 64));
+    StepProfile only;
+    only.gemv_only = true;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    const uint64_t before = launches_;
+    prof_ = &only;
+    cuda_check(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal), "begin graph capture");
+    try {
+        enqueue_token_step();
+    } catch (...) {
+        prof_ = nullptr;
+        cudaStreamEndCapture(p.stream, &graph);
+        if (graph) cudaGraphDestroy(graph);
+        throw;
+    }
+    prof_ = nullptr;
+    launches_ = before;
+    cuda_check(cudaStreamEndCapture(p.stream, &graph), "end graph capture");
+    cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    cuda_check(e, "instantiate graph");
+    cudaEvent_t a, b;
+    cuda_check(cudaEventCreate(&a), "event");
+    cuda_check(cudaEventCreate(&b), "event");
+    cudaGraphLaunch(exec, p.stream); // warm
+    cudaEventRecord(a, p.stream);
+    for (int i = 0; i < replays; i++) cudaGraphLaunch(exec, p.stream);
+    cudaEventRecord(b, p.stream);
+    e = cudaStreamSynchronize(p.stream);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, a, b);
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    cudaGraphExecDestroy(exec);
+    cuda_check(e, "synchronize");
+    *ms_per_token = ms / float(replays);
+    *bytes = only.gemv_bytes;
+    *launches = only.gemv_launches;
+    fused_token_valid_ = false;
+    sync_scalars(-1); // the head launches advanced the device-side position; put the host's view back
 }
 
 int Qwen35Decode::mtp_draft(int token)

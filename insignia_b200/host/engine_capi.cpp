@@ -154,6 +154,14 @@ int insg_engine_profile_token(insg_engine *e, int token, float *ms, uint64_t *by
         return int(INSG_OK);
     });
 }
+int insg_engine_profile_gemv_chain(insg_engine *e, int replays, float *ms_per_token, uint64_t *bytes, int *launches)
+{
+    return guarded(e, [&] {
+        if (!ms_per_token || !bytes || !launches) return insg::fail(INSG_E_ARG, "null output");
+        e->dec->profile_gemv_chain(replays, ms_per_token, bytes, launches);
+        return int(INSG_OK);
+    });
+}
 int insg_engine_set_trace(insg_engine *e, void *device_buffer)
 {
     if (!e) return insg::fail(INSG_E_ARG, "null engine");

@@ -121,3 +121,31 @@ def test_golden_checkpoint_is_reproducible(golden_ckpt):
     t = SafetensorsReader(golden_ckpt[0])
     h = hashlib.sha256(t.get("language_model.model.layers.0.linear_attn.in_proj_qkv.weight").tobytes()).hexdigest()
     assert h == open(os.path.join(GOLD, "golden4_qkv_sha256.txt")).read().strip()
+
+
+def test_dropin_headers_compile_standalone(tmp_path):
+    """Every header of include/ compiles on its own and together (the kernel-level ones are inline wrappers over the C ABI)."""
+    import shutil
+    import subprocess
+
+    if not shutil.which("nvcc"):
+        pytest.skip("nvcc not on PATH")
+    inc = os.path.join(ROOT, "include")
+    headers = sorted(f for f in os.listdir(inc) if f != "insignia_posix_shim.hpp")
+    assert {"insignia_layout.cuh", "insignia_attention.cuh", "insignia_deltanet.cuh", "insignia_ops.cuh", "insignia_qwen_kernels.cuh",
+            "insignia_model.hpp", "insignia_storage.hpp", "insignia_qwen35.hpp", "insignia_decode.hpp", "insignia_b200.h"} <= set(headers)
+    src = tmp_path / "all.cu"
+    src.write_text("".join(f'#include "{h}"\n' for h in headers) + """
+static_assert(sizeof(insignia::MxFp4Block) == 17, "block size");
+int probe() {
+    insignia::MxFp4Block b{127, {0x21}};
+    return insignia::mxfp4_value(b, 0) == 0.5f && insignia::mxfp4_value(b, 16) == 1.0f && insignia::fp4_e2m1(15) == -6.0f
+        && insignia::e8m0(0) == 0.0f && insignia::e8m0(255) != insignia::e8m0(255);
+}
+int main() { return probe() ? 0 : 1; }
+""")
+    exe = tmp_path / "all"
+    subprocess.check_call(["nvcc", "-std=c++20", "-gencode", "arch=compute_100a,code=sm_100a", "-I", inc, str(src),
+                           "-L", os.path.join(ROOT, "insignia_b200", "lib"), "-linsignia_b200", "-o", str(exe)])
+    env = dict(os.environ, LD_LIBRARY_PATH=os.path.join(ROOT, "insignia_b200", "lib") + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+    assert subprocess.run([str(exe)], env=env).returncode == 0  # host-only helpers: runs without a GPU

@@ -497,3 +497,50 @@ def test_kernels_vs_compiled_reference(cuda):
     refengine.call("ref_gqa_decode", qq.data_ptr(), kk.data_ptr(), vv.data_ptr(), oref.data_ptr(), T)
     o = ops.gqa_decode(qq, kk, vv, T)
     assert float((o - oref).abs().max()) <= 3e-5
+
+
+# ------------------------------------------------------------------------ launchers outside the token loop
+def test_block_layout_gemv_vs_scalar_decode(cuda):
+    """include/insignia_layout.cuh:11-15 blocks: low nibbles are elements 0..15, high nibbles 16..31."""
+    from insignia_b200 import _lib
+
+    rng = np.random.default_rng(11)
+    rows, cols = 37, 256
+    blocks = rng.integers(0, 256, (rows, cols // 32, 17), dtype=np.uint8)
+    blocks[:, :, 0] = rng.integers(118, 132, (rows, cols // 32))
+    x = rng.standard_normal(cols).astype(np.float32)
+    lut = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], np.float64)
+    codes = np.concatenate([blocks[:, :, 1:] & 15, blocks[:, :, 1:] >> 4], axis=2)  # [rows][blocks][32]
+    w = lut[codes] * np.exp2(blocks[:, :, :1].astype(np.float64) - 127)
+    expected = (w.reshape(rows, cols) * x).sum(1)
+    y, db, dx = torch.zeros(rows, device="cuda"), dev(blocks), dev(x)
+    _lib.check(_lib.lib().insg_mxfp4_gemv_blocks(db.data_ptr(), dx.data_ptr(), y.data_ptr(), rows, cols, None))
+    assert np.max(np.abs(host(y) - expected)) <= 1e-5 * np.abs(expected).max()
+    assert _lib.lib().insg_mxfp4_gemv_blocks(db.data_ptr(), dx.data_ptr(), y.data_ptr(), rows, 48, None) < 0
+
+
+def test_int8_activation_path(cuda):
+    """src/mxfp4.cu:83-127: per-32 absmax int8 quantisation, then integer dot products with doubled E2M1 codes."""
+    from insignia_b200 import _lib, mxfp4
+
+    rng = np.random.default_rng(12)
+    rows, cols = 130, 512
+    w, s = rand_matrix(rng, rows, cols)
+    x = rng.standard_normal(cols).astype(np.float32)
+    x[64:96] = 0.0  # an all-zero group keeps scale 1
+    L = _lib.lib()
+    dx, qx, qs, y = dev(x), torch.zeros(cols, dtype=torch.int8, device="cuda"), torch.zeros(cols // 32, device="cuda"), torch.zeros(rows, device="cuda")
+    _lib.check(L.insg_quantize_q8_groups(dx.data_ptr(), qx.data_ptr(), qs.data_ptr(), cols, None))
+    g = x.reshape(-1, 32)
+    amax = np.abs(g).max(1)
+    scale = np.where(amax > 0, amax * np.float32(1.0 / 127.0), np.float32(1.0)).astype(np.float32)
+    q = np.rint(g / scale[:, None]).astype(np.int8)
+    assert np.array_equal(host(qs), scale)
+    assert np.max(np.abs(host(qx).astype(np.int32) - q.reshape(-1).astype(np.int32))) <= 1  # division rounding at exact halves
+    dw, ds = dev(w), dev(s)
+    _lib.check(L.insg_mxfp4_gemv_dp4a(dw.data_ptr(), ds.data_ptr(), qx.data_ptr(), qs.data_ptr(), y.data_ptr(), rows, cols, None))
+    deq = mxfp4.dequantize(w, s).astype(np.float64)
+    xq = (host(qx).astype(np.float64).reshape(-1, 32) * host(qs).astype(np.float64)[:, None]).reshape(-1)
+    expected = deq @ xq  # exact given the quantised activations
+    assert np.max(np.abs(host(y) - expected)) <= 1e-5 * np.abs(expected).max()
+    assert np.max(np.abs(host(y) - deq @ x)) <= 3e-2 * np.abs(deq @ x).max()  # int8 rounding of x
