@@ -284,7 +284,10 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
     // this CTA's and this warp's share of the record sequence
     const int G = int(gridDim.x), c = int(blockIdx.x);
     // CTA ranges end on tile boundaries (a tile = one run, or the gate/up pair): no tile is shared between CTAs
-    const int a = int((long long)p.total_etiles * c / G) * p.etile_units, b = int((long long)p.total_etiles * (c + 1) / G) * p.etile_units;
+    // The CTAs that get one tile more are the lowest-numbered ones: those are placed first, on the SMs the previous
+    // kernel left first, so the extra tile goes where the head start is (and the stragglers' SMs get the short ranges).
+    const int tq = p.total_etiles / G, tr = p.total_etiles % G;
+    const int a = (c * tq + min(c, tr)) * p.etile_units, b = ((c + 1) * tq + min(c + 1, tr)) * p.etile_units;
     const int ua = a + (((b - a) * warp) >> 4), ub = a + (((b - a) * (warp + 1)) >> 4); // kWarps == 16
     const int tm_first = ua / nkb;
     if (lane == 0) {
