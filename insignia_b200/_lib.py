@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libinsignia_b200.so")
+# INSIGNIA_B200_LIB points at another build of the same library (e.g. one compiled with a development macro)
+LIB_PATH = os.environ.get("INSIGNIA_B200_LIB") or os.path.join(_HERE, "lib", "libinsignia_b200.so")
 _lib = None
 
 vp, i32, u64, sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t

@@ -26,6 +26,12 @@
 //     prologues on the activation, residual / conv+SiLU / decay / beta / SwiGLU / logits+arg-max
 //     epilogues on the rows.
 #include "common.cuh"
+#ifdef INSG_PRO_TRACE // development build: slots 5 and 7 of the phase trace are taken inside the prologue instead
+#define PRO_TRACE(slot)                                                                                  \
+    do {                                                                                                 \
+        if (p.trace && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(p.trace[blockIdx.x * 8 + (slot)])); \
+    } while (0)
+#endif
 #include "gemv_prologue.cuh"
 #include "host_util.h"
 
@@ -193,11 +199,14 @@ __device__ __forceinline__ bool ring_wait(uint64_t *bar, uint32_t parity, int *a
 
 // ---- activation prologue: fp32 vector -> two fp16 pieces in shared memory ----
 // Returns 1/alpha, which undoes the power-of-two pre-scale.
-__device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, const uint2 (&wpre)[kPreVec], float *scratch)
+template <typename Between>
+__device__ __forceinline__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, const uint2 (&wpre)[kPreVec], float *scratch,
+                                          Between &&between)
 {
-    const ProIn pin{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue};
+    const ProIn pin{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue, p.trace};
     float4 v[kMaxVec];
     load_activation(pin, m, v);
+    between();
     const float tmax = transform_activation(pin, m, v, wpre, scratch);
     const int tid = threadIdx.x, nvec = p.cols >> 2;
     // alpha = 2^(12 - floor(log2(max))) puts the largest element in [2^12, 2^13): fp16 holds it with room to spare
@@ -280,6 +289,13 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
 
     INSG_TRACE(0);
     pdl_launch_dependents();
+    {
+        // The parameter block is cold in the constant cache at every launch and its 64-byte lines would be fetched
+        // one after the other, each at first use.  Touch them all at once, one line per warp.
+        constexpr int kWords = int(sizeof(GemvParams) / 4);
+        const uint32_t warm = reinterpret_cast<const uint32_t *>(&p)[min(warp * 16, kWords - 1)];
+        asm volatile("" ::"r"(warm));
+    }
 
     // this CTA's and this warp's share of the record sequence
     const int G = int(gridDim.x), c = int(blockIdx.x);
@@ -315,10 +331,12 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
         }
     } else {
         load_chunk<UNR>(p, A, lit, ub, lane);
+#ifndef INSG_SPLIT_PREFETCH
         load_chunk<UNR>(p, B, lit, ub, lane);
+#endif
     }
     uint2 wpre[kPreVec];
-    preload_norm_weights(ProIn{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue}, wpre);
+    preload_norm_weights(ProIn{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue, p.trace}, wpre);
     INSG_TRACE(1);
 
     pdl_wait();
@@ -326,7 +344,14 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
 
     float inv_alpha[M];
 #pragma unroll
-    for (int m = 0; m < M; m++) inv_alpha[m] = prologue(p, m, xs, xstride, wpre, scratch);
+    for (int m = 0; m < M; m++)
+        inv_alpha[m] = prologue(p, m, xs, xstride, wpre, scratch, [&] {
+#ifdef INSG_SPLIT_PREFETCH
+            if constexpr (!RING) {
+                if (m == 0) load_chunk<UNR>(p, B, lit, ub, lane);
+            }
+#endif
+        });
     __syncthreads();
     INSG_TRACE(3);
 
@@ -422,7 +447,9 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
     }
     INSG_TRACE(4);
     __syncthreads();
+#ifndef INSG_PRO_TRACE
     INSG_TRACE(5);
+#endif
 
     // ---- combine: every (tile) this CTA touched, its runs summed over the warps in warp order --------
     float best = -3.402823466e38f;
@@ -456,7 +483,9 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
                     for (int w = 0; w < kWarps; w++) z += part[w]; // warp order, whatever the schedule
                     y[mat] = z;
                 }
+#ifndef INSG_PRO_TRACE
                 if (tmq == tm_lo) INSG_TRACE(7);
+#endif
                 row_epilogue(s, (tm0 - s.tm_begin) / s.nmat * 16 + row, m, y[0], y[1], best, best_idx);
             }
         }

@@ -27,16 +27,18 @@ class Engine:
         o = EngineOptions(budget_bytes, max_context, int(kv_bf16), int(gate_elementwise), int(accurate_trig),
                           int(use_graph), int(use_pdl), int(gemv_tcgen05), n_layers, vocab, device)
         self.vocab = vocab
+        self._destroy = _lib.lib().insg_engine_destroy  # held here: module globals may be gone when __del__ runs at exit
         self._h = _lib.lib().insg_engine_create(index_path.encode(), C.byref(o))
         if not self._h:
             raise InsigniaError(_lib.lib().insg_last_error().decode())
 
     def close(self):
-        if getattr(self, "_h", None):
-            _lib.lib().insg_engine_destroy(self._h)
-            self._h = None
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._destroy(h)
 
-    __del__ = close
+    def __del__(self):
+        self.close()
 
     def __enter__(self):
         return self
