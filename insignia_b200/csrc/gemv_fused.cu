@@ -199,14 +199,11 @@ __device__ __forceinline__ bool ring_wait(uint64_t *bar, uint32_t parity, int *a
 
 // ---- activation prologue: fp32 vector -> two fp16 pieces in shared memory ----
 // Returns 1/alpha, which undoes the power-of-two pre-scale.
-template <typename Between>
-__device__ __forceinline__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, const uint2 (&wpre)[kPreVec], float *scratch,
-                                          Between &&between)
+__device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, const uint2 (&wpre)[kPreVec], float *scratch)
 {
     const ProIn pin{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue, p.trace};
     float4 v[kMaxVec];
     load_activation(pin, m, v);
-    between();
     const float tmax = transform_activation(pin, m, v, wpre, scratch);
     const int tid = threadIdx.x, nvec = p.cols >> 2;
     // alpha = 2^(12 - floor(log2(max))) puts the largest element in [2^12, 2^13): fp16 holds it with room to spare
@@ -289,13 +286,6 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
 
     INSG_TRACE(0);
     pdl_launch_dependents();
-    {
-        // The parameter block is cold in the constant cache at every launch and its 64-byte lines would be fetched
-        // one after the other, each at first use.  Touch them all at once, one line per warp.
-        constexpr int kWords = int(sizeof(GemvParams) / 4);
-        const uint32_t warm = reinterpret_cast<const uint32_t *>(&p)[min(warp * 16, kWords - 1)];
-        asm volatile("" ::"r"(warm));
-    }
 
     // this CTA's and this warp's share of the record sequence
     const int G = int(gridDim.x), c = int(blockIdx.x);
@@ -330,10 +320,14 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
             }
         }
     } else {
-        load_chunk<UNR>(p, A, lit, ub, lane);
-#ifndef INSG_SPLIT_PREFETCH
-        load_chunk<UNR>(p, B, lit, ub, lane);
+#ifdef INSG_SETUP_TRACE
+        INSG_TRACE(5);
 #endif
+        load_chunk<UNR>(p, A, lit, ub, lane);
+#ifdef INSG_SETUP_TRACE
+        INSG_TRACE(7);
+#endif
+        load_chunk<UNR>(p, B, lit, ub, lane);
     }
     uint2 wpre[kPreVec];
     preload_norm_weights(ProIn{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue, p.trace}, wpre);
@@ -344,14 +338,7 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
 
     float inv_alpha[M];
 #pragma unroll
-    for (int m = 0; m < M; m++)
-        inv_alpha[m] = prologue(p, m, xs, xstride, wpre, scratch, [&] {
-#ifdef INSG_SPLIT_PREFETCH
-            if constexpr (!RING) {
-                if (m == 0) load_chunk<UNR>(p, B, lit, ub, lane);
-            }
-#endif
-        });
+    for (int m = 0; m < M; m++) inv_alpha[m] = prologue(p, m, xs, xstride, wpre, scratch);
     __syncthreads();
     INSG_TRACE(3);
 
@@ -447,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
     }
     INSG_TRACE(4);
     __syncthreads();
-#ifndef INSG_PRO_TRACE
+#if !defined(INSG_PRO_TRACE) && !defined(INSG_SETUP_TRACE)
     INSG_TRACE(5);
 #endif
 
@@ -483,7 +470,7 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
                     for (int w = 0; w < kWarps; w++) z += part[w]; // warp order, whatever the schedule
                     y[mat] = z;
                 }
-#ifndef INSG_PRO_TRACE
+#if !defined(INSG_PRO_TRACE) && !defined(INSG_SETUP_TRACE)
                 if (tmq == tm_lo) INSG_TRACE(7);
 #endif
                 row_epilogue(s, (tm0 - s.tm_begin) / s.nmat * 16 + row, m, y[0], y[1], best, best_idx);
