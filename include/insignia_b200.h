@@ -107,9 +107,10 @@ INSG_API size_t insg_mxfp4_packed_umma_bytes(int rows, int cols);
 INSG_API int insg_mxfp4_repack_umma(const uint32_t *weight, const uint8_t *scales, void *packed, int rows, int cols,
                                     insg_stream_t stream);
 
-/* y[m][rows] = W x[m] for m < M (1 <= M <= 8), W in the packed layout; x is
+/* y[m][rows] = W x[m] for m < M (1 <= M <= 4096), W in the packed layout; x is
  * fp32 [M][cols], y fp32 [M][rows].  Plain (no fused prologue/epilogue) form of
- * the kernel the engine runs; replaces Qwen35Decode::linear (src/decode.cu:13). */
+ * the kernel the engine runs; replaces Qwen35Decode::linear (src/decode.cu:13).
+ * Tokens go through in passes of four (the weights are streamed once per pass). */
 INSG_API int insg_mxfp4_gemv_packed(const void *packed, const float *x, float *y, int rows, int cols, int M,
                                     insg_stream_t stream);
 
@@ -352,6 +353,9 @@ INSG_API int insg_engine_reset(insg_engine *e);
 INSG_API int insg_engine_read(insg_engine *e, const char *field, float *out /* host */, uint64_t count);
 /* Device pointer of a workspace buffer (for callers that post-process on the GPU). */
 INSG_API void *insg_engine_buffer(insg_engine *e, const char *field);
+/* Counterpart of insg_engine_read: copies `count` floats from host memory into a workspace buffer (the reference's
+ * drivers write x.hidden directly, src/test_full_model.cu:6).  Synchronises. */
+INSG_API int insg_engine_write(insg_engine *e, const char *field, const float *in /* host */, uint64_t count);
 INSG_API insg_stream_t insg_engine_stream(insg_engine *e);
 /* Kernel launches issued by the engine since creation (own kernels only). */
 INSG_API uint64_t insg_engine_launch_count(insg_engine *e);

@@ -95,6 +95,7 @@ SIGNATURES = {
     "insg_engine_set_position": (i32, [vp, i32]),
     "insg_engine_reset": (i32, [vp]),
     "insg_engine_read": (i32, [vp, C.c_char_p, vp, u64]),
+    "insg_engine_write": (i32, [vp, C.c_char_p, vp, u64]),
     "insg_engine_buffer": (vp, [vp, C.c_char_p]),
     "insg_engine_stream": (vp, [vp]),
     "insg_engine_launch_count": (u64, [vp]),

@@ -663,7 +663,7 @@ int insg_gemv_fused(const insg_gemv_op *op, insg_stream_t stream)
 
 int insg_mxfp4_gemv_packed(const void *packed, const float *x, float *y, int rows, int cols, int M, insg_stream_t stream)
 {
-    if (M < 1 || M > 8) return fail(INSG_E_SHAPE, "gemv_packed: 1 <= M <= 8");
+    if (M < 1 || M > 4096) return fail(INSG_E_SHAPE, "gemv_packed: 1 <= M <= 4096");
     for (int m0 = 0; m0 < M;) {
         const int left = M - m0;
         const int mm = left >= 4 ? 4 : (left >= 2 ? 2 : 1);

@@ -99,6 +99,10 @@ class Engine:
         check(_lib.lib().insg_engine_read(self._h, field.encode(), out.ctypes.data, n))
         return out
 
+    def write(self, field: str, values: np.ndarray):
+        v = np.ascontiguousarray(values, np.float32)
+        check(_lib.lib().insg_engine_write(self._h, field.encode(), v.ctypes.data, v.size))
+
     def buffer(self, field: str) -> int:
         return _lib.lib().insg_engine_buffer(self._h, field.encode())
 

@@ -196,6 +196,18 @@ int insg_engine_read(insg_engine *e, const char *field, float *out, uint64_t cou
         return int(INSG_OK);
     });
 }
+int insg_engine_write(insg_engine *e, const char *field, const float *in, uint64_t count)
+{
+    return guarded(e, [&] {
+        float *dst = field ? field_ptr(*e->ws, field) : nullptr;
+        if (!dst || !in) return insg::fail(INSG_E_ARG, "unknown workspace field");
+        cudaStream_t st = e->dec->execution_stream();
+        if (cudaMemcpyAsync(dst, in, count * sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess ||
+            cudaStreamSynchronize(st) != cudaSuccess)
+            return insg::fail(INSG_E_CUDA, cudaGetErrorString(cudaGetLastError()));
+        return int(INSG_OK);
+    });
+}
 void *insg_engine_buffer(insg_engine *e, const char *field)
 {
     if (!e || !field) return nullptr;
