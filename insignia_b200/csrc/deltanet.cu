@@ -14,6 +14,9 @@
 // once (coalesced 128-byte row segments, issued before the dependent-launch wait
 // because the state was last written a whole token ago), does both reductions
 // over k on chip, and writes the slice back once: 2 x 2 MiB of traffic per layer.
+// The step is a latency chain, so it is kept short: all inputs are requested
+// together, every warp normalises q and k for itself, and only the two sums over
+// the eight warps cross a CTA barrier.
 #include "common.cuh"
 #include "host_util.h"
 
@@ -27,10 +30,8 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
                                                                    const float *__restrict__ g32, const float *__restrict__ beta32,
                                                                    float *__restrict__ out32)
 {
-    __shared__ float s_q[128], s_k[128];
-    __shared__ float s_part[8][32];
-    __shared__ float s_red[16];
-    __shared__ float s_delta[32];
+    __shared__ __align__(16) float s_qk[8][2][128]; // per warp: its own copy of the normalised q and k (no block barrier)
+    __shared__ __align__(16) float s_part[2][8][32]; // per-warp partial sums over k: [0] memory read-out, [1] output
 
     const int head = blockIdx.x / kSlices, slice = blockIdx.x % kSlices, kh = head >> 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -46,37 +47,36 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
 
     pdl_wait();
 
-    // L2 norms of q and k over 128 (eps added to the sum, as the reference)
-    float qv = 0.f, kv = 0.f;
-    if (tid < 128) {
-        qv = __ldcg(q16 + kh * 128 + tid);
-        kv = __ldcg(k16 + kh * 128 + tid);
-    }
-    // every dependent input is requested now, so the later stages do not each pay a trip to L2
+    // Every dependent input is requested at once.  Each warp reads the whole q and k of the key head (four values per
+    // lane) and normalises them itself: L2 norms over 128 with eps added to the sum, as the reference.
+    const float4 q4 = __ldcg(reinterpret_cast<const float4 *>(q16 + kh * 128) + lane);
+    const float4 k4 = __ldcg(reinterpret_cast<const float4 *>(k16 + kh * 128) + lane);
+    const float4 v4 = __ldcg(reinterpret_cast<const float4 *>(v32 + head * 128 + slice * 32) + vq); // this thread's columns
     const float g_in = __ldcg(g32 + head), beta = __ldcg(beta32 + head);
-    const float v_in = tid < 32 ? __ldcg(v32 + head * 128 + slice * 32 + tid) : 0.f;
-    float qn = warp_sum(qv * qv), kn = warp_sum(kv * kv);
-    if (lane == 0) { s_red[warp] = qn; s_red[8 + warp] = kn; }
-    __syncthreads();
-    const float qa = s_red[0] + s_red[1] + s_red[2] + s_red[3];
-    const float ka = s_red[8] + s_red[9] + s_red[10] + s_red[11];
-    const float qs = rsqrtf(qa + 1e-6f) * 0.08838834764831845f, ks = rsqrtf(ka + 1e-6f);
-    if (tid < 128) { s_q[tid] = qv * qs; s_k[tid] = kv * ks; }
-    __syncthreads();
-
+    const float qn = warp_sum(fmaf(q4.x, q4.x, fmaf(q4.y, q4.y, fmaf(q4.z, q4.z, q4.w * q4.w))));
+    const float kn = warp_sum(fmaf(k4.x, k4.x, fmaf(k4.y, k4.y, fmaf(k4.z, k4.z, k4.w * k4.w))));
+    const float qs = rsqrtf(qn + 1e-6f) * 0.08838834764831845f, ks = rsqrtf(kn + 1e-6f);
+    reinterpret_cast<float4 *>(s_qk[warp][0])[lane] = make_float4(q4.x * qs, q4.y * qs, q4.z * qs, q4.w * qs);
+    reinterpret_cast<float4 *>(s_qk[warp][1])[lane] = make_float4(k4.x * ks, k4.y * ks, k4.z * ks, k4.w * ks);
+    __syncwarp();
+    float qq[4], kk[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        qq[j] = s_qk[warp][0][kr + 32 * j];
+        kk[j] = s_qk[warp][1][kr + 32 * j];
+    }
     const float decay = expf(g_in);
 
     // mem_v = sum_i (S*d) * k
     float4 pm = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        const float kk = s_k[kr + 32 * j];
-        pm.x = fmaf(cell[j].x * decay, kk, pm.x);
-        pm.y = fmaf(cell[j].y * decay, kk, pm.y);
-        pm.z = fmaf(cell[j].z * decay, kk, pm.z);
-        pm.w = fmaf(cell[j].w * decay, kk, pm.w);
+        pm.x = fmaf(cell[j].x * decay, kk[j], pm.x);
+        pm.y = fmaf(cell[j].y * decay, kk[j], pm.y);
+        pm.z = fmaf(cell[j].z * decay, kk[j], pm.z);
+        pm.w = fmaf(cell[j].w * decay, kk[j], pm.w);
     }
-    // a warp holds 4 k-rows (lane>>3) x 8 column groups: fold the rows, then the 8 warps
+    // a warp holds 4 k-rows (lane>>3) x 8 column groups: fold the rows, then every thread folds the 8 warps itself
 #pragma unroll
     for (int m = 8; m <= 16; m <<= 1) {
         pm.x += __shfl_xor_sync(0xffffffffu, pm.x, m);
@@ -84,30 +84,28 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
         pm.z += __shfl_xor_sync(0xffffffffu, pm.z, m);
         pm.w += __shfl_xor_sync(0xffffffffu, pm.w, m);
     }
-    if (lane < 8) *reinterpret_cast<float4 *>(&s_part[warp][lane * 4]) = pm;
+    if (lane < 8) *reinterpret_cast<float4 *>(&s_part[0][warp][lane * 4]) = pm;
     __syncthreads();
-    if (tid < 32) {
-        float mem = 0.f;
+    float4 mem = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int w = 0; w < 8; w++) mem += s_part[w][tid];
-        s_delta[tid] = (v_in - mem) * beta;
+    for (int w = 0; w < 8; w++) {
+        const float4 t = *reinterpret_cast<const float4 *>(&s_part[0][w][vq * 4]);
+        mem.x += t.x; mem.y += t.y; mem.z += t.z; mem.w += t.w;
     }
-    __syncthreads();
-    const float4 dl = *reinterpret_cast<const float4 *>(&s_delta[vq * 4]);
+    const float4 dl = make_float4((v4.x - mem.x) * beta, (v4.y - mem.y) * beta, (v4.z - mem.z) * beta, (v4.w - mem.w) * beta);
 
     // S = S*d + k*delta ; out_v = sum_i S * q
     float4 po = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        const float kk = s_k[kr + 32 * j], qq = s_q[kr + 32 * j];
-        cell[j].x = fmaf(cell[j].x, decay, kk * dl.x);
-        cell[j].y = fmaf(cell[j].y, decay, kk * dl.y);
-        cell[j].z = fmaf(cell[j].z, decay, kk * dl.z);
-        cell[j].w = fmaf(cell[j].w, decay, kk * dl.w);
-        po.x = fmaf(cell[j].x, qq, po.x);
-        po.y = fmaf(cell[j].y, qq, po.y);
-        po.z = fmaf(cell[j].z, qq, po.z);
-        po.w = fmaf(cell[j].w, qq, po.w);
+        cell[j].x = fmaf(cell[j].x, decay, kk[j] * dl.x);
+        cell[j].y = fmaf(cell[j].y, decay, kk[j] * dl.y);
+        cell[j].z = fmaf(cell[j].z, decay, kk[j] * dl.z);
+        cell[j].w = fmaf(cell[j].w, decay, kk[j] * dl.w);
+        po.x = fmaf(cell[j].x, qq[j], po.x);
+        po.y = fmaf(cell[j].y, qq[j], po.y);
+        po.z = fmaf(cell[j].z, qq[j], po.z);
+        po.w = fmaf(cell[j].w, qq[j], po.w);
         *reinterpret_cast<float4 *>(S + size_t(kr + 32 * j) * 128 + v0) = cell[j];
     }
 #pragma unroll
@@ -117,13 +115,12 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
         po.z += __shfl_xor_sync(0xffffffffu, po.z, m);
         po.w += __shfl_xor_sync(0xffffffffu, po.w, m);
     }
-    __syncthreads(); // s_part is reused
-    if (lane < 8) *reinterpret_cast<float4 *>(&s_part[warp][lane * 4]) = po;
+    if (lane < 8) *reinterpret_cast<float4 *>(&s_part[1][warp][lane * 4]) = po;
     __syncthreads();
     if (tid < 32) {
         float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; w++) o += s_part[w][tid];
+        for (int w = 0; w < 8; w++) o += s_part[1][w][tid];
         out32[head * 128 + slice * 32 + tid] = o;
     }
 }
