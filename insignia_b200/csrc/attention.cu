@@ -52,21 +52,33 @@ __device__ unsigned long long g_attn_trace[4 * kSplits][8];
 #define ATTN_TRACE(i) do { } while (0)
 #endif
 
+// A lane's 8 dims of one cache row, as loaded (converted only when used, so that two token groups can be in flight).
 template <bool BF16> struct KvRow;
 template <> struct KvRow<false> {
-    static __device__ __forceinline__ void load(const void *base, size_t row_elems, int lane, float (&o)[8])
+    struct Raw { float4 a, b; };
+    static __device__ __forceinline__ Raw load_raw(const void *base, size_t row_elems, int lane)
     {
         const float4 *p = reinterpret_cast<const float4 *>(static_cast<const float *>(base) + row_elems) + lane * 2;
-        const float4 a = __ldcg(p), b = __ldcg(p + 1);
-        o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+        return Raw{__ldcg(p), __ldcg(p + 1)};
+    }
+    static __device__ __forceinline__ Raw zero() { return Raw{make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)}; }
+    static __device__ __forceinline__ void unpack(const Raw &r, float (&o)[8])
+    {
+        o[0] = r.a.x; o[1] = r.a.y; o[2] = r.a.z; o[3] = r.a.w; o[4] = r.b.x; o[5] = r.b.y; o[6] = r.b.z; o[7] = r.b.w;
     }
     static __device__ __forceinline__ float round(float v) { return v; }
     static __device__ __forceinline__ void store(void *base, size_t idx, float v) { static_cast<float *>(base)[idx] = v; }
 };
 template <> struct KvRow<true> {
-    static __device__ __forceinline__ void load(const void *base, size_t row_elems, int lane, float (&o)[8])
+    struct Raw { uint4 r; };
+    static __device__ __forceinline__ Raw load_raw(const void *base, size_t row_elems, int lane)
     {
-        const uint4 r = __ldcg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + row_elems) + lane);
+        return Raw{__ldcg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + row_elems) + lane)};
+    }
+    static __device__ __forceinline__ Raw zero() { return Raw{make_uint4(0u, 0u, 0u, 0u)}; }
+    static __device__ __forceinline__ void unpack(const Raw &w, float (&o)[8])
+    {
+        const uint4 r = w.r;
         o[0] = __uint_as_float(r.x << 16); o[1] = __uint_as_float(r.x & 0xffff0000u);
         o[2] = __uint_as_float(r.y << 16); o[3] = __uint_as_float(r.y & 0xffff0000u);
         o[4] = __uint_as_float(r.z << 16); o[5] = __uint_as_float(r.z & 0xffff0000u);
@@ -79,21 +91,24 @@ template <> struct KvRow<true> {
     }
 };
 
+template <bool BF16> struct GroupRaw {
+    typename KvRow<BF16>::Raw k[kGroup], v[kGroup];
+};
+
 // Rows tb..tb+kGroup-1 of one kv head (those below `tend`; the rest read as zero).
 template <bool BF16>
-__device__ __forceinline__ void load_group(const void *kc, const void *vc, int kvh, int tb, int tend, int lane,
-                                           float (&kk)[kGroup][8], float (&vv)[kGroup][8])
+__device__ __forceinline__ void load_group(const void *kc, const void *vc, int kvh, int tb, int tend, int lane, GroupRaw<BF16> &g)
 {
 #pragma unroll
-    for (int g = 0; g < kGroup; g++) {
-        const int t = tb + g;
+    for (int i = 0; i < kGroup; i++) {
+        const int t = tb + i;
         if (t < tend) {
             const size_t row = (size_t(t) * 4 + kvh) * 256;
-            KvRow<BF16>::load(kc, row, lane, kk[g]);
-            KvRow<BF16>::load(vc, row, lane, vv[g]);
+            g.k[i] = KvRow<BF16>::load_raw(kc, row, lane);
+            g.v[i] = KvRow<BF16>::load_raw(vc, row, lane);
         } else {
-#pragma unroll
-            for (int j = 0; j < 8; j++) { kk[g][j] = 0.f; vv[g][j] = 0.f; }
+            g.k[i] = KvRow<BF16>::zero();
+            g.v[i] = KvRow<BF16>::zero();
         }
     }
 }
@@ -170,8 +185,9 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     int t0 = split * chunk, t1 = min(tokens, t0 + chunk);
     int fresh = tokens - 1; // the row the producer (or this kernel) is still writing
 
-    float kk[kGroup][8], vv[kGroup][8];
-    load_group<BF16>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, kk, vv);
+    GroupRaw<BF16> ga, gb; // this warp's next two token groups, in flight while it works on earlier ones
+    load_group<BF16>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
+    load_group<BF16>(p.kc, p.vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
     uint4 norm_wv = make_uint4(0u, 0u, 0u, 0u);
     float rope_c[8], rope_s[8];
     if constexpr (FUSED) {
@@ -194,7 +210,8 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
             t0 = split * chunk;
             t1 = min(tokens, t0 + chunk);
             fresh = tokens - 1;
-            load_group<BF16>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, kk, vv);
+            load_group<BF16>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
+            load_group<BF16>(p.kc, p.vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
             if (warp < 5 && lane < 8) rope_table(pos, lane, p.fast_trig != 0, rope_c, rope_s);
         }
     }
@@ -254,20 +271,24 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
 #pragma unroll
             for (int j = 0; j < 8; j++) acc[h][j] = 0.f;
         }
-        bool first = true;
-        for (int tb = t0 + warp * kGroup; tb < t1; tb += kAtWarps * kGroup, first = false) {
-            if (!first) load_group<BF16>(p.kc, p.vc, kvh, tb, min(t1, fresh), lane, kk, vv);
-            if (fresh >= tb && fresh < tb + kGroup && fresh < t1) { // the newest row: from shared memory or, after the wait, from the cache
+        // one token group: scores of its (up to) four tokens for the four query heads, one online-softmax update
+        auto process = [&](const GroupRaw<BF16> &grp, int tb) {
+            float kk[kGroup][8];
+#pragma unroll
+            for (int g = 0; g < kGroup; g++) Row::unpack(grp.k[g], kk[g]);
+            const bool has_fresh = fresh >= tb && fresh < tb + kGroup && fresh < t1; // warp-uniform
+            typename Row::Raw vfresh = Row::zero();
+            if (has_fresh) { // the newest row: from shared memory or, now that the wait is over, from the cache
 #pragma unroll
                 for (int g = 0; g < kGroup; g++) {
                     if (tb + g != fresh) continue;
                     if constexpr (FUSED) {
 #pragma unroll
-                        for (int j = 0; j < 8; j++) { kk[g][j] = s_knew[lane * 8 + j]; vv[g][j] = s_vnew[lane * 8 + j]; }
+                        for (int j = 0; j < 8; j++) kk[g][j] = s_knew[lane * 8 + j];
                     } else {
                         const size_t row = (size_t(fresh) * 4 + kvh) * 256;
-                        Row::load(p.kc, row, lane, kk[g]);
-                        Row::load(p.vc, row, lane, vv[g]);
+                        Row::unpack(Row::load_raw(p.kc, row, lane), kk[g]);
+                        vfresh = Row::load_raw(p.vc, row, lane);
                     }
                 }
             }
@@ -287,28 +308,51 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
                 for (int g = 0; g < kGroup; g++)
 #pragma unroll
                     for (int h = 0; h < 4; h++) s[g][h] += __shfl_xor_sync(0xffffffffu, s[g][h], mk);
+            float pr[kGroup][4], corr[4];
 #pragma unroll
             for (int h = 0; h < 4; h++) {
                 float mn = m[h];
 #pragma unroll
                 for (int g = 0; g < kGroup; g++)
                     if (tb + g < t1) mn = fmaxf(mn, s[g][h]);
-                const float corr = __expf(m[h] - mn);
-                float pr[kGroup], psum = 0.f;
+                corr[h] = __expf(m[h] - mn);
+                float psum = 0.f;
 #pragma unroll
                 for (int g = 0; g < kGroup; g++) {
-                    pr[g] = tb + g < t1 ? __expf(s[g][h] - mn) : 0.f;
-                    psum += pr[g];
+                    pr[g][h] = tb + g < t1 ? __expf(s[g][h] - mn) : 0.f;
+                    psum += pr[g][h];
                 }
                 m[h] = mn;
-                l[h] = fmaf(l[h], corr, psum);
+                l[h] = fmaf(l[h], corr[h], psum);
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    float a = acc[h][j] * corr;
+                for (int j = 0; j < 8; j++) acc[h][j] *= corr[h];
+            }
 #pragma unroll
-                    for (int g = 0; g < kGroup; g++) a = fmaf(pr[g], vv[g][j], a);
-                    acc[h][j] = a;
+            for (int g = 0; g < kGroup; g++) {
+                float vv[8];
+                Row::unpack(grp.v[g], vv);
+                if (has_fresh && tb + g == fresh) {
+                    if constexpr (FUSED) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) vv[j] = s_vnew[lane * 8 + j];
+                    } else {
+                        Row::unpack(vfresh, vv);
+                    }
                 }
+#pragma unroll
+                for (int h = 0; h < 4; h++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[h][j] = fmaf(pr[g][h], vv[j], acc[h][j]);
+            }
+        };
+        const int tend = min(t1, fresh);
+        for (int tb = t0 + warp * kGroup; tb < t1; tb += 2 * kAtWarps * kGroup) {
+            process(ga, tb);
+            load_group<BF16>(p.kc, p.vc, kvh, tb + 2 * kAtWarps * kGroup, tend, lane, ga);
+            const int tb2 = tb + kAtWarps * kGroup;
+            if (tb2 < t1) {
+                process(gb, tb2);
+                load_group<BF16>(p.kc, p.vc, kvh, tb2 + 2 * kAtWarps * kGroup, tend, lane, gb);
             }
         }
         // ---- fold the 8 warps --------------------------------------------------------
