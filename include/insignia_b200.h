@@ -125,8 +125,13 @@ enum {
     INSG_PRO_SIGMOID_GATE_HEAD0 = 4, /* x = in * sigmoid(aux[(i>>8)*512+256]) : gate element 0 of the head
                                   broadcast over its 256 lanes; aux is the interleaved q_proj output
                                   (src/qwen_kernels.cu:31,36) */
-    INSG_PRO_SIGMOID_GATE_QPROJ = 5 /* x = in * sigmoid(aux[(i>>8)*512+256+(i&255)]) : element-wise gate read
+    INSG_PRO_SIGMOID_GATE_QPROJ = 5, /* x = in * sigmoid(aux[(i>>8)*512+256+(i&255)]) : element-wise gate read
                                   from the interleaved q_proj output */
+    INSG_PRO_PREPARED = 6      /* `in` is not fp32 but the fp16 image [2][cols] an earlier launch left through
+                                  insg_gemv_segment.prep (already multiplied by that launch's prep_w); with
+                                  prep_partials != NULL the product is also scaled by
+                                  rsqrt(sum(prep_partials[0..295]) / cols + 1e-6), which makes the pair the RMSNorm of
+                                  INSG_PRO_RMSNORM without this launch reducing anything.  One token per launch. */
 };
 
 /* What is done with each output row. */
@@ -151,12 +156,20 @@ typedef struct insg_gemv_segment {
     const uint16_t *conv_w;  /* CONV_SILU: bf16 [rows][4]                              */
     const float *A_log;      /* DECAY: fp32 [rows]                                     */
     const uint16_t *dt_bias; /* DECAY: bf16 [rows]                                     */
+    /* RESIDUAL / SWIGLU, optional: besides out[], leave the vector ready for a later INSG_PRO_PREPARED launch.
+     * prep: fp16 [2][rows] = the two half-precision pieces of out[row] * prep_w[row] / 16 (values beyond
+     * +-1e6 saturate).  prep_w: bf16 [rows] multiplier, the weight of the RMSNorm that follows, or NULL for 1.
+     * prep_partials (RESIDUAL, single-segment launches): fp32 [296], entry c = this launch's CTA c's sum of
+     * out[row]^2 over its rows, unused entries zero. */
+    void *prep;
+    const uint16_t *prep_w;
+    float *prep_partials;
 } insg_gemv_segment;
 
 /* A fused launch: prologue on the shared input vector, up to 4 matrices that
  * all multiply it, an epilogue per matrix.  cols % 128 == 0, cols <= 12288. */
 typedef struct insg_gemv_op {
-    const float *in;          /* fp32 [cols]                                           */
+    const float *in;          /* fp32 [cols] (INSG_PRO_PREPARED: the fp16 image [2][cols]) */
     const float *aux;         /* prologue operand (gate / z), or NULL                  */
     const uint16_t *norm_w;   /* bf16 norm weight for the RMSNorm prologues, or NULL   */
     float *x_out;             /* optional: the prologue's result fp32 [cols], or NULL  */
@@ -179,6 +192,7 @@ typedef struct insg_gemv_op {
     int layout;               /* weight layout of every segment: 0 = insg_mxfp4_repack records, 1 = insg_mxfp4_repack_umma   */
     int *error_flag;          /* set to 1 if a bounded wait inside the kernel ran out (device int), or NULL                 */
     int pdl;                  /* 1: launch with programmatic dependent launch          */
+    const float *prep_partials; /* INSG_PRO_PREPARED: the producer's prep_partials [296], or NULL for no RMS scaling      */
 } insg_gemv_op;
 
 INSG_API size_t insg_gemv_argmax_scratch_bytes(void);
@@ -311,6 +325,8 @@ typedef struct insg_engine_options {
     int n_layers;                 /* 0 = 32                                                     */
     int vocab;                    /* 0 = 248320 (rows of lm_head used for logits)               */
     int device;                   /* CUDA device ordinal                                        */
+    int gemv_unprepared;          /* 0: a GEMV that writes the residual stream or the SwiGLU output leaves the next
+                                     GEMV's input prepared (insg_gemv_segment.prep); 1: every GEMV converts its own */
 } insg_engine_options;
 
 INSG_API insg_engine *insg_engine_create(const char *index_path /* host, UTF-8 */, const insg_engine_options *opt);

@@ -29,6 +29,9 @@ struct DecodeOptions {
     bool use_graph = true;         // replay the token step from a CUDA graph
     bool use_pdl = true;           // programmatic dependent launch between kernels
     bool gemv_tcgen05 = false;     // true: weights through tcgen05.mma kind::mxf4 (TMA-fed); false: the mma.sync streaming kernel
+    bool prepared_inputs = true;   // a GEMV that writes the residual stream or the SwiGLU output also leaves the next GEMV's
+                                   // input ready as fp16 pieces (and its sum of squares), so that one starts streaming
+                                   // without normalising or converting anything; false: every GEMV prepares its own input
     int n_layers = Qwen35Shape::layers;
     int vocab = Qwen35Shape::vocab;
 };
@@ -57,6 +60,7 @@ public:
     int *d_next{};       // device: arg-max of the last logits
     void *attn_scratch{};
     void *argmax_scratch{};
+    void *prep{};        // device: prepared GEMV inputs, fp16 [2][4096] + fp16 [2][12288] + fp32 [296] sums of squares
     void *trace{};       // optional profiling buffer: [GEMV launch of the step][296 CTAs][8] u64 timestamps (see insg_gemv_op.trace)
     int trace_index{};   // GEMV launches enqueued since the step began
     void reset(); // zero recurrent state and position, as a fresh workspace
@@ -95,9 +99,13 @@ private:
     Plan &plan();
     void sync_scalars(int token);
     void enqueue_embed();
-    void enqueue_delta(int layer);
-    void enqueue_attention(int layer);
-    void enqueue_head();
+    // hidden_prepared: the launch before left this block's input prepared; next_norm: weight of the RMSNorm that reads
+    // this block's output next (the block then leaves that input prepared), or null when the caller may touch hidden
+    void load_block(int layer);
+    void load_head();
+    void enqueue_delta(int layer, bool hidden_prepared = false, const uint16_t *next_norm = nullptr);
+    void enqueue_attention(int layer, bool hidden_prepared = false, const uint16_t *next_norm = nullptr);
+    void enqueue_head(bool hidden_prepared = false);
     void enqueue_token_step();
     void replay_token_step();
     Qwen35Weights &w_;

@@ -18,13 +18,14 @@ vp, i32, u64, sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t
 
 class GemvSegment(C.Structure):
     _fields_ = [("packed", vp), ("packed2", vp), ("out", vp), ("rows", i32), ("epilogue", i32), ("conv_state", vp),
-                ("conv_w", vp), ("A_log", vp), ("dt_bias", vp)]
+                ("conv_w", vp), ("A_log", vp), ("dt_bias", vp), ("prep", vp), ("prep_w", vp), ("prep_partials", vp)]
 
 
 class GemvOp(C.Structure):
     _fields_ = [("in_", vp), ("aux", vp), ("norm_w", vp), ("x_out", vp), ("cols", i32), ("prologue", i32),
                 ("n_segments", i32), ("seg", GemvSegment * 4), ("argmax_scratch", vp), ("token_out", vp),
-                ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("trace", vp), ("layout", i32), ("error_flag", vp), ("pdl", i32)]
+                ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("trace", vp), ("layout", i32), ("error_flag", vp), ("pdl", i32),
+                ("prep_partials", vp)]
 
 
 class AttnOp(C.Structure):
@@ -36,7 +37,7 @@ class AttnOp(C.Structure):
 class EngineOptions(C.Structure):
     _fields_ = [("device_budget_bytes", u64), ("max_context", i32), ("kv_dtype", i32), ("gate_elementwise", i32),
                 ("accurate_trig", i32), ("use_graph", i32), ("use_pdl", i32), ("gemv_tcgen05", i32), ("n_layers", i32), ("vocab", i32),
-                ("device", i32)]
+                ("device", i32), ("gemv_unprepared", i32)]
 
 
 # name -> (restype, argtypes); every symbol include/insignia_b200.h declares

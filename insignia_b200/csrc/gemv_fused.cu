@@ -44,6 +44,11 @@ constexpr int kRec = 1088;  // bytes per (16-row tile, 128-k block) record
 constexpr int kWarps = 16;  // warps per CTA, one CTA per SM
 constexpr int kThreads = kWarps * 32;
 constexpr float kLoScale = 1.0f / 2048.0f;
+constexpr int kMaxGrid = 296;
+// Fixed pre-scale of a prepared activation image: the producer cannot know the vector's maximum, so instead of the
+// adaptive power of two of the in-kernel prologue the image holds x / 16.  fp16 then covers |x| from 1e-3 (below that
+// the low piece loses bits that are far under the fp32 rounding of a 4096-term dot product) to 1e6 (saturating).
+constexpr float kPrepScale = 0.0625f, kPrepInv = 16.0f;
 
 struct SegDev {
     const uint8_t *packed, *packed2;
@@ -55,6 +60,8 @@ struct SegDev {
     int tm_begin; // first (tile, matrix) index of the segment
     int nmat;     // 1, or 2 for the gate/up pair of SwiGLU
     int epilogue, rows;
+    __half *prep;            // optional fp16 image [2][rows] of out * prep_w / 16 for a later INSG_PRO_PREPARED launch
+    const uint16_t *prep_w;  // bf16 [rows] or null
 };
 
 struct GemvParams {
@@ -70,6 +77,8 @@ struct GemvParams {
     int *token_out, *token_feedback, *token_log, *position_inout;
     unsigned long long *trace; // optional [grid][8] phase timestamps (ns), or null
     int *error_flag;           // RING: raised when a bounded wait expires
+    const float *prep_partials_in; // INSG_PRO_PREPARED: [kMaxGrid] per-CTA sums of squares of the producer, or null
+    float *prep_partials_out;      // RESIDUAL with prep: [kMaxGrid], this launch's per-CTA sums of out^2
 };
 
 __device__ __forceinline__ unsigned long long global_ns()
@@ -230,12 +239,30 @@ __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, c
 }
 
 // One output row of one token through the epilogue of its segment.
-__device__ __forceinline__ void row_epilogue(const SegDev &s, int row, int m, float y0, float y1, float &best, int &best_idx)
+// The two fp16 pieces of v * w / 16 (see kPrepScale) into a prepared image of `rows` elements.
+__device__ __forceinline__ void prep_store(const SegDev &s, int row, float v)
+{
+    const float w = s.prep_w ? bf16_bits_to_float(s.prep_w[row]) : 1.0f;
+    const float e = fminf(fmaxf(v * w * kPrepScale, -65504.0f), 65504.0f);
+    const __half hi = __float2half_rn(e);
+    s.prep[row] = hi;
+    s.prep[s.rows + row] = __float2half_rn((e - __half2float(hi)) * 2048.0f);
+}
+
+__device__ __forceinline__ void row_epilogue(const SegDev &s, int row, int m, float y0, float y1, float &best, int &best_idx, float &ss)
 {
     float *out = s.out + size_t(m) * s.rows;
     switch (s.epilogue) {
     case INSG_EPI_STORE: out[row] = y0; break;
-    case INSG_EPI_RESIDUAL: out[row] = __ldcg(out + row) + y0; break;
+    case INSG_EPI_RESIDUAL: {
+        const float h = __ldcg(out + row) + y0;
+        out[row] = h;
+        if (s.prep) {
+            prep_store(s, row, h);
+            ss = fmaf(h, h, ss);
+        }
+        break;
+    }
     case INSG_EPI_CONV_SILU: {
         float *st = s.conv_state + size_t(row) * 3;
         const uint2 wv = reinterpret_cast<const uint2 *>(s.conv_w)[row];
@@ -254,7 +281,12 @@ __device__ __forceinline__ void row_epilogue(const SegDev &s, int row, int m, fl
         out[row] = -__expf(s.A_log[row]) * soft;
         break;
     }
-    case INSG_EPI_SWIGLU: out[row] = fast_silu(y0) * y1; break;
+    case INSG_EPI_SWIGLU: {
+        const float act = fast_silu(y0) * y1;
+        out[row] = act;
+        if (s.prep) prep_store(s, row, act);
+        break;
+    }
     case INSG_EPI_LOGITS:
         out[row] = y0;
         if (y0 > best || (y0 == best && row < best_idx)) { best = y0; best_idx = row; }
@@ -323,11 +355,13 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
 #ifdef INSG_SETUP_TRACE
         INSG_TRACE(5);
 #endif
+#ifndef INSG_NO_PREFETCH
         load_chunk<UNR>(p, A, lit, ub, lane);
 #ifdef INSG_SETUP_TRACE
         INSG_TRACE(7);
 #endif
         load_chunk<UNR>(p, B, lit, ub, lane);
+#endif
     }
     uint2 wpre[kPreVec];
     preload_norm_weights(ProIn{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue, p.trace}, wpre);
@@ -337,10 +371,45 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
     INSG_TRACE(2);
 
     float inv_alpha[M];
+    if (p.prologue == INSG_PRO_PREPARED) {
+        // The producer left both fp16 pieces ready: copy them (16-byte asynchronous copies through L2, no registers,
+        // no reductions) and fold the RMS factor, when there is one, into the output scale.
+        const int n16 = p.cols >> 3; // 16-byte chunks per piece
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.in);
+        for (int i = tid; i < 2 * n16; i += kThreads) {
+            const int piece = i >= n16, k = i - piece * n16;
+            const uint32_t dst = smem_addr(xs + size_t(piece) * xstride + k * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + i) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (warp == 0) {
+            float f = 1.0f;
+            if (p.prep_partials_in) {
+                float a = 0.f;
 #pragma unroll
-    for (int m = 0; m < M; m++) inv_alpha[m] = prologue(p, m, xs, xstride, wpre, scratch);
+                for (int j = 0; j < (kMaxGrid + 31) / 32; j++)
+                    if (lane + 32 * j < kMaxGrid) a += __ldcg(p.prep_partials_in + lane + 32 * j);
+                a = warp_sum(a);
+                f = rsqrtf(a / float(p.cols) + 1e-6f);
+            }
+            if (lane == 0) scratch[0] = f * kPrepInv;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+#pragma unroll
+        for (int m = 0; m < M; m++) inv_alpha[m] = scratch[0];
+    } else {
+#pragma unroll
+        for (int m = 0; m < M; m++) inv_alpha[m] = prologue(p, m, xs, xstride, wpre, scratch);
+    }
     __syncthreads();
     INSG_TRACE(3);
+#ifdef INSG_NO_PREFETCH // development experiment: weights requested only after the prologue
+    if constexpr (!RING) {
+        load_chunk<UNR>(p, A, lit, ub, lane);
+        load_chunk<UNR>(p, B, lit, ub, lane);
+    }
+#endif
 
     const bool bactive = (t == (g >> 1));
     const int piece = g & 1;
@@ -441,6 +510,7 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
     // ---- combine: every (tile) this CTA touched, its runs summed over the warps in warp order --------
     float best = -3.402823466e38f;
     int best_idx = 0x7fffffff;
+    float ss = 0.f; // sum of squares of the residual-stream rows this thread produced (prepared output only)
     if (b > a) {
         const int tm_lo = a / nkb, tm_hi = (b - 1) / nkb;
         const int row = lane & 15;
@@ -473,12 +543,27 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
 #if !defined(INSG_PRO_TRACE) && !defined(INSG_SETUP_TRACE)
                 if (tmq == tm_lo) INSG_TRACE(7);
 #endif
-                row_epilogue(s, (tm0 - s.tm_begin) / s.nmat * 16 + row, m, y[0], y[1], best, best_idx);
+                row_epilogue(s, (tm0 - s.tm_begin) / s.nmat * 16 + row, m, y[0], y[1], best, best_idx, ss);
             }
         }
     }
 
     INSG_TRACE(6);
+    // ---- this CTA's share of sum(out^2), for the RMSNorm of the launch that consumes the prepared image ----
+    if (p.prep_partials_out) {
+        ss = warp_sum(ss);
+        __syncthreads(); // scratch[0] was the prologue's
+        if (lane == 0) scratch[warp] = ss;
+        __syncthreads();
+        if (tid == 0) {
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; w++) tot += scratch[w];
+            p.prep_partials_out[blockIdx.x] = tot;
+        }
+        if (blockIdx.x == 0)
+            for (int i = G + tid; i < kMaxGrid; i += kThreads) p.prep_partials_out[i] = 0.f;
+    }
     // ---- arg-max over the rows this launch produced (lm_head) ----------------
     if (p.argmax_partial) {
         float *sv = scratch + 16;
@@ -544,7 +629,6 @@ struct Tuning {
     int ctas_per_sm = 1;
 } g_tune;
 
-constexpr int kMaxGrid = 296;
 
 template <int UNR, int M, bool RING> int launch_variant(const GemvParams &p, int grid, size_t smem, cudaStream_t st, bool pdl)
 {
@@ -591,7 +675,10 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
     if (M != 1 && M != 2 && M != 4) return fail(INSG_E_SHAPE, "gemv: 1, 2 or 4 tokens per launch");
     if ((op->prologue == INSG_PRO_RMSNORM || op->prologue == INSG_PRO_GATED_RMSNORM) && !op->norm_w)
         return fail(INSG_E_ARG, "gemv: norm weight missing");
-    if (op->prologue >= INSG_PRO_GATED_RMSNORM && !op->aux) return fail(INSG_E_ARG, "gemv: prologue operand missing");
+    if (op->prologue >= INSG_PRO_GATED_RMSNORM && op->prologue != INSG_PRO_PREPARED && !op->aux)
+        return fail(INSG_E_ARG, "gemv: prologue operand missing");
+    if (op->prologue < 0 || op->prologue > INSG_PRO_PREPARED) return fail(INSG_E_ARG, "gemv: unknown prologue");
+    if (op->prologue == INSG_PRO_PREPARED && M != 1) return fail(INSG_E_SHAPE, "gemv: a prepared input carries one token");
     if (op->prologue == INSG_PRO_GATED_RMSNORM && (op->cols & 127)) return fail(INSG_E_SHAPE, "gemv: gated norm needs cols % 128 == 0");
     GemvParams p = {};
     p.in = op->in; p.aux = op->aux; p.norm_w = op->norm_w; p.x_out = op->x_out;
@@ -609,6 +696,15 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
         d.packed = static_cast<const uint8_t *>(s.packed);
         d.packed2 = static_cast<const uint8_t *>(s.packed2);
         d.out = s.out; d.conv_state = s.conv_state; d.conv_w = s.conv_w; d.A_log = s.A_log; d.dt_bias = s.dt_bias;
+        if (s.prep) {
+            if (s.epilogue != INSG_EPI_RESIDUAL && s.epilogue != INSG_EPI_SWIGLU) return fail(INSG_E_ARG, "gemv: prepared output needs the residual or SwiGLU epilogue");
+            if (M != 1) return fail(INSG_E_SHAPE, "gemv: a prepared output carries one token");
+            if (s.prep_partials && (s.epilogue != INSG_EPI_RESIDUAL || op->n_segments != 1))
+                return fail(INSG_E_ARG, "gemv: sums of squares come from a single residual segment");
+            d.prep = static_cast<__half *>(s.prep);
+            d.prep_w = s.prep_w;
+            if (s.prep_partials) p.prep_partials_out = s.prep_partials;
+        }
         d.nmat = s.epilogue == INSG_EPI_SWIGLU ? 2 : 1;
         d.tm_begin = tm; tm += (s.rows >> 4) * d.nmat; d.epilogue = s.epilogue; d.rows = s.rows;
         if (nmat_all && nmat_all != d.nmat) return fail(INSG_E_SHAPE, "gemv: SwiGLU segments cannot be mixed with others");
@@ -637,6 +733,7 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
     }
     p.trace = static_cast<unsigned long long *>(op->trace);
     p.error_flag = op->error_flag;
+    p.prep_partials_in = op->prologue == INSG_PRO_PREPARED ? op->prep_partials : nullptr;
     const size_t smem = size_t(M) * 2 * (op->cols + 8) * sizeof(__half) + size_t(kWarps) * p.slots * M * 16 * 4 + 64 * 4;
     if (smem > 220 * 1024) return fail(INSG_E_LIMIT, "gemv: shared memory beyond 220 KB");
     const bool pdl = op->pdl != 0;

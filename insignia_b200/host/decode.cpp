@@ -19,6 +19,9 @@ namespace insignia {
 namespace {
 
 constexpr int kHidden = Qwen35Shape::hidden, kInter = Qwen35Shape::intermediate;
+// DecodeWorkspace::prep: fp16 image of the normalised-to-be hidden vector, fp16 image of the SwiGLU output, sums of squares
+constexpr size_t kPrepHidden = 0, kPrepAct = size_t(2) * kHidden * 2, kPrepSums = kPrepAct + size_t(2) * kInter * 2;
+constexpr size_t kPrepBytes = kPrepSums + 296 * sizeof(float);
 const char *const kLM = "language_model";
 
 void cuda_check(cudaError_t e, const char *what)
@@ -75,6 +78,8 @@ void DecodeWorkspace::allocate()
     d_next = d_token + 2;
     cuda_check(cudaMalloc(&attn_scratch, insg_gqa_scratch_bytes(max_context)), "cudaMalloc attention scratch");
     cuda_check(cudaMalloc(&argmax_scratch, insg_gemv_argmax_scratch_bytes()), "cudaMalloc arg-max scratch");
+    cuda_check(cudaMalloc(&prep, kPrepBytes), "cudaMalloc prepared inputs");
+    cuda_check(cudaMemsetAsync(prep, 0, kPrepBytes, stream), "memset");
     cuda_check(cudaMemsetAsync(attn_scratch, 0, 64, stream), "memset");
     cuda_check(cudaMemsetAsync(argmax_scratch, 0, 64, stream), "memset");
     cuda_check(cudaMemsetAsync(d_token, 0, (4 + size_t(max_context) + 1) * sizeof(int), stream), "memset");
@@ -94,7 +99,7 @@ DecodeWorkspace::~DecodeWorkspace()
     for (void *p : {(void *)hidden, (void *)norm, (void *)qkv, (void *)attn_gate, (void *)key, (void *)value, (void *)z, (void *)a,
                     (void *)b, (void *)core, (void *)gate, (void *)up, (void *)down, (void *)logits, (void *)delta_state,
                     (void *)conv_state, (void *)kv_keys, (void *)kv_values, (void *)mtp_keys, (void *)mtp_values, (void *)d_token,
-                    attn_scratch, argmax_scratch})
+                    attn_scratch, argmax_scratch, prep})
         cudaFree(p);
 }
 
@@ -213,7 +218,38 @@ struct Ctx {
     bool pdl;
     uint64_t &launches;
     StepProfile *prof;
+    bool hidden_prepared = false;        // the previous block left this block's first input prepared
+    const uint16_t *next_norm = nullptr; // weight of the RMSNorm that reads this block's output next, when known
+    void *prep_hidden() const { return static_cast<uint8_t *>(x.prep) + kPrepHidden; }
+    void *prep_act() const { return static_cast<uint8_t *>(x.prep) + kPrepAct; }
+    float *prep_sums() const { return reinterpret_cast<float *>(static_cast<uint8_t *>(x.prep) + kPrepSums); }
+    bool prepared() const { return x.options.prepared_inputs && !x.options.gemv_tcgen05; }
 };
+
+// The block's first GEMV: RMSNorm of the residual stream, from the fp32 vector or from the image the previous block left.
+void rmsnorm_input(const Ctx &c, insg_gemv_op &op, const uint16_t *norm_w)
+{
+    op.cols = kHidden;
+    if (c.prepared() && c.hidden_prepared) {
+        op.in = static_cast<const float *>(c.prep_hidden());
+        op.prologue = INSG_PRO_PREPARED;
+        op.prep_partials = c.prep_sums();
+    } else {
+        op.in = c.x.hidden;
+        op.norm_w = norm_w;
+        op.x_out = c.x.norm;
+        op.prologue = INSG_PRO_RMSNORM;
+    }
+}
+
+// A GEMV that adds into the residual stream leaves the input of the RMSNorm + GEMV that follows prepared.
+void residual_output(const Ctx &c, insg_gemv_segment &s, const uint16_t *following_norm_w)
+{
+    if (!c.prepared() || !following_norm_w) return;
+    s.prep = c.prep_hidden();
+    s.prep_w = following_norm_w;
+    s.prep_partials = c.prep_sums();
+}
 
 // Brackets one launch with events when a profile is being taken (never during graph capture).
 struct Timed {
@@ -271,23 +307,24 @@ insg_gemv_segment seg(const PackedMatrix &m, float *out, int epilogue)
 // The three kernels shared by both block types: post-norm + gate/up + SwiGLU, down + residual.
 static void enqueue_mlp_block(Ctx &c, const Qwen35Decode::Plan::Block &b)
 {
+    // the block's out/o_proj launch has just left the post-norm input prepared (when that mode is on)
+    Ctx mid = c;
+    mid.hidden_prepared = true;
     insg_gemv_op op = {};
-    op.in = c.x.hidden;
-    op.norm_w = b.post_norm;
-    op.x_out = c.x.norm;
-    op.cols = kHidden;
-    op.prologue = INSG_PRO_RMSNORM;
+    rmsnorm_input(mid, op, b.post_norm);
     op.n_segments = 1;
     op.seg[0] = seg(b.gate, c.x.gate, INSG_EPI_SWIGLU);
     op.seg[0].packed2 = b.up.data;
+    if (c.prepared()) op.seg[0].prep = c.prep_act();
     run_gemv(c, op);
 
     insg_gemv_op dn = {};
-    dn.in = c.x.gate;
+    dn.in = c.prepared() ? static_cast<const float *>(c.prep_act()) : c.x.gate;
     dn.cols = kInter;
-    dn.prologue = INSG_PRO_PLAIN;
+    dn.prologue = c.prepared() ? INSG_PRO_PREPARED : INSG_PRO_PLAIN;
     dn.n_segments = 1;
     dn.seg[0] = seg(b.down, c.x.hidden, INSG_EPI_RESIDUAL);
+    residual_output(c, dn.seg[0], c.next_norm);
     run_gemv(c, dn);
 }
 
@@ -295,11 +332,7 @@ static void enqueue_delta_block(Ctx &c, const Qwen35Decode::Plan::Block &b, int 
 {
     DecodeWorkspace &x = c.x;
     insg_gemv_op in = {};
-    in.in = x.hidden;
-    in.norm_w = b.in_norm;
-    in.x_out = x.norm;
-    in.cols = kHidden;
-    in.prologue = INSG_PRO_RMSNORM;
+    rmsnorm_input(c, in, b.in_norm);
     in.n_segments = 4;
     in.seg[0] = seg(b.qkv, x.qkv, INSG_EPI_CONV_SILU);
     in.seg[0].conv_state = x.conv_state + size_t(di) * 8192 * 3;
@@ -326,6 +359,7 @@ static void enqueue_delta_block(Ctx &c, const Qwen35Decode::Plan::Block &b, int 
     out.prologue = INSG_PRO_GATED_RMSNORM;
     out.n_segments = 1;
     out.seg[0] = seg(b.out, x.hidden, INSG_EPI_RESIDUAL);
+    residual_output(c, out.seg[0], b.post_norm);
     run_gemv(c, out);
 
     enqueue_mlp_block(c, b);
@@ -335,11 +369,7 @@ static void enqueue_attention_block(Ctx &c, const Qwen35Decode::Plan::Block &b, 
 {
     DecodeWorkspace &x = c.x;
     insg_gemv_op in = {};
-    in.in = x.hidden;
-    in.norm_w = b.in_norm;
-    in.x_out = x.norm;
-    in.cols = kHidden;
-    in.prologue = INSG_PRO_RMSNORM;
+    rmsnorm_input(c, in, b.in_norm);
     in.n_segments = 3;
     in.seg[0] = seg(b.q, x.gate, INSG_EPI_STORE); // interleaved [16][q256|gate256], as the reference (src/decode.cu:19)
     in.seg[1] = seg(b.k, x.key, INSG_EPI_STORE);
@@ -376,6 +406,7 @@ static void enqueue_attention_block(Ctx &c, const Qwen35Decode::Plan::Block &b, 
     o.prologue = x.options.gate_elementwise ? INSG_PRO_SIGMOID_GATE_QPROJ : INSG_PRO_SIGMOID_GATE_HEAD0;
     o.n_segments = 1;
     o.seg[0] = seg(b.o, x.hidden, INSG_EPI_RESIDUAL);
+    residual_output(c, o.seg[0], b.post_norm);
     run_gemv(c, o);
 
     enqueue_mlp_block(c, b);
@@ -448,49 +479,53 @@ void Qwen35Decode::enqueue_embed()
     launches_++;
 }
 
-void Qwen35Decode::enqueue_delta(int l)
+void Qwen35Decode::load_block(int l)
 {
     Plan &p = plan();
     Plan::Block &b = p.layers[l];
-    if (!b.ready) {
-        Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
-        load_delta(L, std::string(kLM) + ".model.layers." + std::to_string(l), b);
-    }
-    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_};
-    enqueue_delta_block(c, b, l - l / 4);
+    if (b.ready) return;
+    Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
+    const std::string name = std::string(kLM) + ".model.layers." + std::to_string(l);
+    if (Qwen35Shape::full_attention(l)) load_attention(L, name, b);
+    else load_delta(L, name, b);
 }
 
-void Qwen35Decode::enqueue_attention(int l)
+void Qwen35Decode::load_head()
 {
     Plan &p = plan();
-    Plan::Block &b = p.layers[l];
-    if (!b.ready) {
-        Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
-        load_attention(L, std::string(kLM) + ".model.layers." + std::to_string(l), b);
-    }
+    if (p.head_ready) return;
+    Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
+    p.final_norm = L.bf16(std::string(kLM) + ".model.norm.weight", kHidden);
+    p.lm_head = w_.packed(std::string(kLM) + ".lm_head", x_.options.gemv_tcgen05 ? 1 : 0);
+    if (p.lm_head.cols != kHidden || p.lm_head.rows < x_.options.vocab) throw std::runtime_error("unexpected matrix shape: language_model.lm_head");
+    p.head_ready = true;
+}
+
+void Qwen35Decode::enqueue_delta(int l, bool hidden_prepared, const uint16_t *next_norm)
+{
+    Plan &p = plan();
+    load_block(l);
+    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_, hidden_prepared, next_norm};
+    enqueue_delta_block(c, p.layers[l], l - l / 4);
+}
+
+void Qwen35Decode::enqueue_attention(int l, bool hidden_prepared, const uint16_t *next_norm)
+{
+    Plan &p = plan();
+    load_block(l);
     const size_t esz = x_.options.kv_bf16 ? 2 : 4;
     const size_t off = size_t(l / 4) * x_.max_context * 1024 * esz;
-    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_};
-    enqueue_attention_block(c, b, reinterpret_cast<uint8_t *>(x_.kv_keys) + off, reinterpret_cast<uint8_t *>(x_.kv_values) + off, 0);
+    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_, hidden_prepared, next_norm};
+    enqueue_attention_block(c, p.layers[l], reinterpret_cast<uint8_t *>(x_.kv_keys) + off, reinterpret_cast<uint8_t *>(x_.kv_values) + off, 0);
 }
 
-void Qwen35Decode::enqueue_head()
+void Qwen35Decode::enqueue_head(bool hidden_prepared)
 {
     Plan &p = plan();
-    if (!p.head_ready) {
-        Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
-        p.final_norm = L.bf16(std::string(kLM) + ".model.norm.weight", kHidden);
-        p.lm_head = w_.packed(std::string(kLM) + ".lm_head", x_.options.gemv_tcgen05 ? 1 : 0);
-        if (p.lm_head.cols != kHidden || p.lm_head.rows < x_.options.vocab) throw std::runtime_error("unexpected matrix shape: language_model.lm_head");
-        p.head_ready = true;
-    }
-    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_};
+    load_head();
+    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_, hidden_prepared, nullptr};
     insg_gemv_op op = {};
-    op.in = x_.hidden;
-    op.norm_w = p.final_norm;
-    op.x_out = x_.norm;
-    op.cols = kHidden;
-    op.prologue = INSG_PRO_RMSNORM;
+    rmsnorm_input(c, op, p.final_norm);
     op.n_segments = 1;
     op.seg[0] = seg(p.lm_head, x_.logits, INSG_EPI_LOGITS);
     op.seg[0].rows = x_.options.vocab;
@@ -531,12 +566,18 @@ void Qwen35Decode::layer(int l)
 void Qwen35Decode::enqueue_token_step()
 {
     x_.trace_index = 0;
+    Plan &p = plan();
+    const int n = x_.options.n_layers;
+    for (int l = 0; l < n; l++) load_block(l); // every block's norm weight is needed by the block before it
+    load_head();
     enqueue_embed();
-    for (int l = 0; l < x_.options.n_layers; l++) {
-        if (Qwen35Shape::full_attention(l)) enqueue_attention(l);
-        else enqueue_delta(l);
+    for (int l = 0; l < n; l++) {
+        // inside the token step nobody touches hidden between two blocks: each block leaves the next one's input prepared
+        const uint16_t *next_norm = l + 1 < n ? p.layers[l + 1].in_norm : p.final_norm;
+        if (Qwen35Shape::full_attention(l)) enqueue_attention(l, l > 0, next_norm);
+        else enqueue_delta(l, l > 0, next_norm);
     }
-    enqueue_head();
+    enqueue_head(n > 0);
 }
 
 void Qwen35Decode::replay_token_step()

@@ -81,6 +81,7 @@ insg_engine *insg_engine_create(const char *index_path, const insg_engine_option
         d.use_graph = o.use_graph != 0;
         d.use_pdl = o.use_pdl != 0;
         d.gemv_tcgen05 = o.gemv_tcgen05 != 0;
+        d.prepared_inputs = o.gemv_unprepared == 0;
         if (o.n_layers > 0) d.n_layers = o.n_layers;
         if (o.vocab > 0) d.vocab = o.vocab;
         if (d.n_layers > insignia::Qwen35Shape::layers || d.vocab > insignia::Qwen35Shape::vocab || (d.vocab & 15))

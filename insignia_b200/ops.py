@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ._lib import AttnOp, GemvOp, check
 
-PRO = {"plain": 0, "rmsnorm": 1, "gated_rmsnorm": 2, "sigmoid_gate": 3, "sigmoid_gate_head0": 4, "sigmoid_gate_qproj": 5}
+PRO = {"plain": 0, "rmsnorm": 1, "gated_rmsnorm": 2, "sigmoid_gate": 3, "sigmoid_gate_head0": 4, "sigmoid_gate_qproj": 5, "prepared": 6}
 EPI = {"store": 0, "residual": 1, "conv_silu": 2, "beta": 3, "decay": 4, "swiglu": 5, "logits": 6}
 KV_F32, KV_BF16 = 0, 1
 
@@ -87,18 +87,22 @@ def gemv_packed(packed, x, rows=None, cols=None):
     return y.reshape(*x.shape[:-1], rows)
 
 
-def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, trace=None, layout=0, error_flag=None):
-    """``segments``: list of dicts with packed, out, rows, epilogue (+ packed2 / conv_state, conv_w / A_log, dt_bias).
-    ``argmax``: dict(scratch, token_out[, token_feedback, token_log, position]) for the logits epilogue."""
+def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, trace=None, layout=0, error_flag=None,
+               prep_partials=None, cols=None):
+    """``segments``: list of dicts with packed, out, rows, epilogue (+ packed2 / conv_state, conv_w / A_log, dt_bias /
+    prep, prep_w, prep_partials).  ``argmax``: dict(scratch, token_out[, token_feedback, token_log, position]) for the
+    logits epilogue.  With ``prologue="prepared"`` ``inp`` is the fp16 image [2][cols] a producer left through ``prep``."""
     op = GemvOp()
     op.in_, op.aux, op.norm_w, op.x_out = _p(inp), _p(aux), _p(norm_w), _p(x_out)
-    op.cols, op.prologue, op.n_segments = inp.shape[-1], PRO[prologue], len(segments)
+    op.cols, op.prologue, op.n_segments = cols or inp.shape[-1], PRO[prologue], len(segments)
+    op.prep_partials = _p(prep_partials)
     for i, s in enumerate(segments):
         g = op.seg[i]
         g.packed, g.packed2, g.out = _p(s["packed"]), _p(s.get("packed2")), _p(s["out"])
         g.rows, g.epilogue = s["rows"], EPI[s["epilogue"]]
         g.conv_state, g.conv_w = _p(s.get("conv_state")), _p(s.get("conv_w"))
         g.A_log, g.dt_bias = _p(s.get("A_log")), _p(s.get("dt_bias"))
+        g.prep, g.prep_w, g.prep_partials = _p(s.get("prep")), _p(s.get("prep_w")), _p(s.get("prep_partials"))
     if argmax:
         op.argmax_scratch, op.token_out = _p(argmax["scratch"]), _p(argmax["token_out"])
         op.token_feedback, op.token_log = _p(argmax.get("token_feedback")), _p(argmax.get("token_log"))

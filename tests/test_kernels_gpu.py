@@ -544,3 +544,59 @@ def test_int8_activation_path(cuda):
     expected = deq @ xq  # exact given the quantised activations
     assert np.max(np.abs(host(y) - expected)) <= 1e-5 * np.abs(expected).max()
     assert np.max(np.abs(host(y) - deq @ x)) <= 3e-2 * np.abs(deq @ x).max()  # int8 rounding of x
+
+
+def test_gemv_fused_prepared_chain_matches_in_kernel_prologues(cuda):
+    """out_proj (residual, leaves the next RMSNorm's input ready) -> gate|up (prepared input, leaves its SwiGLU output
+    ready) -> down (prepared input, residual): against the oracle chain and against the same three launches with the
+    in-kernel prologues."""
+    from insignia_b200 import ops
+
+    rng = np.random.default_rng(31)
+    wo, so = rand_matrix(rng, 4096, 4096)
+    wg, sg = rand_matrix(rng, 12288, 4096)
+    wu, su = rand_matrix(rng, 12288, 4096)
+    wd, sd = rand_matrix(rng, 4096, 12288)
+    po, pg, pu, pd = (ops.repack(dev(w), dev(s)) for w, s in ((wo, so), (wg, sg), (wu, su), (wd, sd)))
+    nw = bf16(rng, 4096)
+    x0 = rng.standard_normal(4096).astype(np.float32)
+    h0 = (rng.standard_normal(4096) * 3).astype(np.float32)
+    h0[7] = 250.0  # an outlier in the residual stream
+    # oracle
+    h1 = h0 + orc.gemv_mlx_f64(wo, so, x0)
+    n = orc.rmsnorm_bf16(h1.astype(np.float32), nw)
+    g, u = orc.gemv_mlx_f64(wg, sg, n), orc.gemv_mlx_f64(wu, su, n)
+    act = g / (1 + np.exp(-g)) * u
+    h2 = h1 + orc.gemv_mlx_f64(wd, sd, act.astype(np.float32))
+
+    def run(prepared):
+        hidden = dev(h0.copy())
+        act_d = torch.zeros(12288, device="cuda")
+        img_h = torch.zeros(2 * 4096, dtype=torch.float16, device="cuda")
+        img_a = torch.zeros(2 * 12288, dtype=torch.float16, device="cuda")
+        parts = torch.full((296,), 7.0, device="cuda")  # stale values must be overwritten
+        if prepared:
+            ops.gemv_fused(dev(x0), [dict(packed=po, out=hidden, rows=4096, epilogue="residual", prep=img_h, prep_w=dev(nw),
+                                          prep_partials=parts)])
+            ops.gemv_fused(img_h, [dict(packed=pg, packed2=pu, out=act_d, rows=12288, epilogue="swiglu", prep=img_a)],
+                           prologue="prepared", prep_partials=parts, cols=4096)
+            ops.gemv_fused(img_a, [dict(packed=pd, out=hidden, rows=4096, epilogue="residual")], prologue="prepared", cols=12288)
+        else:
+            ops.gemv_fused(dev(x0), [dict(packed=po, out=hidden, rows=4096, epilogue="residual")])
+            ops.gemv_fused(hidden, [dict(packed=pg, packed2=pu, out=act_d, rows=12288, epilogue="swiglu")], prologue="rmsnorm",
+                           norm_w=dev(nw))
+            ops.gemv_fused(act_d, [dict(packed=pd, out=hidden, rows=4096, epilogue="residual")])
+        return host(hidden), host(act_d), host(parts)
+
+    hp, ap, parts = run(True)
+    hn, an, _ = run(False)
+    assert np.max(np.abs(ap - act)) <= 3e-5 * np.abs(act).max()
+    assert np.max(np.abs(hp - h2)) <= 2e-5 * np.abs(h2).max()
+    assert np.max(np.abs(ap - an)) <= 2e-5 * np.abs(an).max() and np.max(np.abs(hp - hn)) <= 1e-5 * np.abs(hn).max()
+    assert abs(parts.sum() - float((h1.astype(np.float64) ** 2).sum())) <= 1e-5 * float((h1 ** 2).sum())
+    assert np.count_nonzero(parts) <= 148
+    # a prepared input is one token wide, and only residual / SwiGLU rows can be left prepared
+    from insignia_b200 import _lib
+    with pytest.raises(_lib.InsigniaError):
+        ops.gemv_fused(dev(x0), [dict(packed=po, out=torch.zeros(4096, device="cuda"), rows=4096, epilogue="store",
+                                      prep=torch.zeros(8192, dtype=torch.float16, device="cuda"))])

@@ -108,6 +108,28 @@ def test_tcgen05_and_mma_sync_gemv_paths_agree(cuda, golden_ckpt):
             assert close(ha, m.hidden, 1e-3) and close(hb, m.hidden, 1e-3), i
 
 
+def test_prepared_inputs_on_and_off_agree(cuda, golden_ckpt):
+    """With prepared inputs each residual / SwiGLU launch hands the next GEMV its input as fp16 pieces plus sums of
+    squares; without, every GEMV normalises and converts for itself.  Same tokens, hidden states within rounding, and
+    both within the oracle's tolerance."""
+    from insignia_b200.checkpoint_io import SafetensorsReader
+
+    m = orc.OracleModel(SafetensorsReader(golden_ckpt[0]), max_context=64, gate="broadcast", n_layers=4)
+    with small_engine(golden_ckpt[1], prepared_inputs=True) as a, small_engine(golden_ckpt[1], prepared_inputs=False) as b:
+        for i, t in enumerate([42, 7, 63, 0, 21, 5, 33, 60, 11, 12]):
+            ta, tb, tm = a.decode_token(t), b.decode_token(t), m.decode_token(t)
+            assert ta == tb == tm, i
+            ha, hb = a.read("hidden"), b.read("hidden")
+            assert np.max(np.abs(ha - hb)) <= 1e-4 * np.abs(hb).max(), i
+            assert close(ha, m.hidden, 1e-3) and close(hb, m.hidden, 1e-3), i
+        # the per-layer entry points take hidden from the caller: they must not read a stale prepared image
+        a.write("hidden", b.read("hidden") * 0.5)
+        b.write("hidden", b.read("hidden") * 0.5)
+        for l in range(4):
+            a.layer(l), b.layer(l)
+        assert np.max(np.abs(a.read("hidden") - b.read("hidden"))) <= 1e-4 * np.abs(b.read("hidden")).max()
+
+
 def test_kv_bf16_and_accurate_trig_modes(cuda, golden_ckpt):
     from insignia_b200.checkpoint_io import SafetensorsReader
 
