@@ -128,10 +128,13 @@ enum {
     INSG_PRO_SIGMOID_GATE_QPROJ = 5, /* x = in * sigmoid(aux[(i>>8)*512+256+(i&255)]) : element-wise gate read
                                   from the interleaved q_proj output */
     INSG_PRO_PREPARED = 6      /* `in` is not fp32 but the fp16 image [2][cols] an earlier launch left through
-                                  insg_gemv_segment.prep (already multiplied by that launch's prep_w); with
-                                  prep_partials != NULL the product is also scaled by
-                                  rsqrt(sum(prep_partials[0..295]) / cols + 1e-6), which makes the pair the RMSNorm of
-                                  INSG_PRO_RMSNORM without this launch reducing anything.  One token per launch. */
+                                  insg_gemv_segment.prep (already multiplied by that launch's prep_w).  With prep_rms
+                                  the product is also scaled by rsqrt(sum(prep_partials[0..295]) / cols + 1e-6), which
+                                  makes the pair the RMSNorm of INSG_PRO_RMSNORM without this launch reducing anything.
+                                  The image has a fixed scale; when the producer's sums say it is not trustworthy (root
+                                  mean square outside [1e-3, 1e5], or a value that did not fit) and `aux` is given, the
+                                  launch reads the fp32 vector `aux` instead (RMSNorm with norm_w if that is set, else
+                                  as is).  One token per launch. */
 };
 
 /* What is done with each output row. */
@@ -159,8 +162,8 @@ typedef struct insg_gemv_segment {
     /* RESIDUAL / SWIGLU, optional: besides out[], leave the vector ready for a later INSG_PRO_PREPARED launch.
      * prep: fp16 [2][rows] = the two half-precision pieces of out[row] * prep_w[row] / 16 (values beyond
      * +-1e6 saturate).  prep_w: bf16 [rows] multiplier, the weight of the RMSNorm that follows, or NULL for 1.
-     * prep_partials (RESIDUAL, single-segment launches): fp32 [296], entry c = this launch's CTA c's sum of
-     * out[row]^2 over its rows, unused entries zero. */
+     * prep_partials (single-segment launches): fp32 [296], entry c = this launch's CTA c's sum of out[row]^2 over
+     * its rows (infinite if a value did not fit the image), unused entries zero. */
     void *prep;
     const uint16_t *prep_w;
     float *prep_partials;
@@ -192,7 +195,8 @@ typedef struct insg_gemv_op {
     int layout;               /* weight layout of every segment: 0 = insg_mxfp4_repack records, 1 = insg_mxfp4_repack_umma   */
     int *error_flag;          /* set to 1 if a bounded wait inside the kernel ran out (device int), or NULL                 */
     int pdl;                  /* 1: launch with programmatic dependent launch          */
-    const float *prep_partials; /* INSG_PRO_PREPARED: the producer's prep_partials [296], or NULL for no RMS scaling      */
+    const float *prep_partials; /* INSG_PRO_PREPARED: the producer's prep_partials [296], or NULL                        */
+    int prep_rms;               /* INSG_PRO_PREPARED: 1 = scale by the RMS factor computed from prep_partials            */
 } insg_gemv_op;
 
 INSG_API size_t insg_gemv_argmax_scratch_bytes(void);

@@ -60,7 +60,7 @@ public:
     int *d_next{};       // device: arg-max of the last logits
     void *attn_scratch{};
     void *argmax_scratch{};
-    void *prep{};        // device: prepared GEMV inputs, fp16 [2][4096] + fp16 [2][12288] + fp32 [296] sums of squares
+    void *prep{};        // device: prepared GEMV inputs, fp16 [2][4096] + fp16 [2][12288] + fp32 [2][296] sums of squares
     void *trace{};       // optional profiling buffer: [GEMV launch of the step][296 CTAs][8] u64 timestamps (see insg_gemv_op.trace)
     int trace_index{};   // GEMV launches enqueued since the step began
     void reset(); // zero recurrent state and position, as a fresh workspace

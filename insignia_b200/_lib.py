@@ -25,7 +25,7 @@ class GemvOp(C.Structure):
     _fields_ = [("in_", vp), ("aux", vp), ("norm_w", vp), ("x_out", vp), ("cols", i32), ("prologue", i32),
                 ("n_segments", i32), ("seg", GemvSegment * 4), ("argmax_scratch", vp), ("token_out", vp),
                 ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("trace", vp), ("layout", i32), ("error_flag", vp), ("pdl", i32),
-                ("prep_partials", vp)]
+                ("prep_partials", vp), ("prep_rms", i32)]
 
 
 class AttnOp(C.Structure):

@@ -78,6 +78,7 @@ struct GemvParams {
     unsigned long long *trace; // optional [grid][8] phase timestamps (ns), or null
     int *error_flag;           // RING: raised when a bounded wait expires
     const float *prep_partials_in; // INSG_PRO_PREPARED: [kMaxGrid] per-CTA sums of squares of the producer, or null
+    int prep_rms;                  // INSG_PRO_PREPARED: scale by rsqrt(mean square + 1e-6) (the RMSNorm case)
     float *prep_partials_out;      // RESIDUAL with prep: [kMaxGrid], this launch's per-CTA sums of out^2
 };
 
@@ -240,13 +241,17 @@ __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, c
 
 // One output row of one token through the epilogue of its segment.
 // The two fp16 pieces of v * w / 16 (see kPrepScale) into a prepared image of `rows` elements.
-__device__ __forceinline__ void prep_store(const SegDev &s, int row, float v)
+// Returns false when the value does not fit (the consumer is then told, through an infinite sum of squares, to read the
+// fp32 vector instead).
+__device__ __forceinline__ bool prep_store(const SegDev &s, int row, float v)
 {
     const float w = s.prep_w ? bf16_bits_to_float(s.prep_w[row]) : 1.0f;
-    const float e = fminf(fmaxf(v * w * kPrepScale, -65504.0f), 65504.0f);
+    const float raw = v * w * kPrepScale;
+    const float e = fminf(fmaxf(raw, -65504.0f), 65504.0f);
     const __half hi = __float2half_rn(e);
     s.prep[row] = hi;
     s.prep[s.rows + row] = __float2half_rn((e - __half2float(hi)) * 2048.0f);
+    return fabsf(raw) <= 65504.0f; // false for NaN too
 }
 
 __device__ __forceinline__ void row_epilogue(const SegDev &s, int row, int m, float y0, float y1, float &best, int &best_idx, float &ss)
@@ -257,10 +262,7 @@ __device__ __forceinline__ void row_epilogue(const SegDev &s, int row, int m, fl
     case INSG_EPI_RESIDUAL: {
         const float h = __ldcg(out + row) + y0;
         out[row] = h;
-        if (s.prep) {
-            prep_store(s, row, h);
-            ss = fmaf(h, h, ss);
-        }
+        if (s.prep) ss = prep_store(s, row, h) ? fmaf(h, h, ss) : __int_as_float(0x7f800000);
         break;
     }
     case INSG_EPI_CONV_SILU: {
@@ -284,7 +286,7 @@ __device__ __forceinline__ void row_epilogue(const SegDev &s, int row, int m, fl
     case INSG_EPI_SWIGLU: {
         const float act = fast_silu(y0) * y1;
         out[row] = act;
-        if (s.prep) prep_store(s, row, act);
+        if (s.prep) ss = prep_store(s, row, act) ? fmaf(act, act, ss) : __int_as_float(0x7f800000);
         break;
     }
     case INSG_EPI_LOGITS:
@@ -383,21 +385,36 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         if (warp == 0) {
-            float f = 1.0f;
+            float f = 1.0f, ok = 1.0f;
             if (p.prep_partials_in) {
                 float a = 0.f;
 #pragma unroll
                 for (int j = 0; j < (kMaxGrid + 31) / 32; j++)
                     if (lane + 32 * j < kMaxGrid) a += __ldcg(p.prep_partials_in + lane + 32 * j);
                 a = warp_sum(a);
-                f = rsqrtf(a / float(p.cols) + 1e-6f);
+                const float ms = a / float(p.cols);
+                if (p.prep_rms) f = rsqrtf(ms + 1e-6f);
+                // The image has a fixed scale: it is exact enough for a root mean square between 1e-3 and 1e5 and
+                // when no element saturated (the producer then left an infinite sum).  Outside that, use the fp32 vector.
+                ok = (ms >= 1e-6f && ms <= 1e10f) ? 1.0f : 0.0f;
             }
-            if (lane == 0) scratch[0] = f * kPrepInv;
+            if (lane == 0) { scratch[0] = f * kPrepInv; scratch[1] = ok; }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
+        if (scratch[1] == 0.0f && p.aux) { // CTA-uniform and the same in every CTA: it depends on global sums only
+            GemvParams q = p;
+            q.in = p.aux;
+            q.aux = nullptr;
+            q.prologue = p.norm_w ? INSG_PRO_RMSNORM : INSG_PRO_PLAIN;
+            preload_norm_weights(ProIn{q.in, q.aux, q.norm_w, nullptr, q.cols, q.prologue, nullptr}, wpre);
+            __syncthreads(); // every thread has read scratch[1]
 #pragma unroll
-        for (int m = 0; m < M; m++) inv_alpha[m] = scratch[0];
+            for (int m = 0; m < M; m++) inv_alpha[m] = prologue(q, m, xs, xstride, wpre, scratch);
+        } else {
+#pragma unroll
+            for (int m = 0; m < M; m++) inv_alpha[m] = scratch[0];
+        }
     } else {
 #pragma unroll
         for (int m = 0; m < M; m++) inv_alpha[m] = prologue(p, m, xs, xstride, wpre, scratch);
@@ -699,8 +716,7 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
         if (s.prep) {
             if (s.epilogue != INSG_EPI_RESIDUAL && s.epilogue != INSG_EPI_SWIGLU) return fail(INSG_E_ARG, "gemv: prepared output needs the residual or SwiGLU epilogue");
             if (M != 1) return fail(INSG_E_SHAPE, "gemv: a prepared output carries one token");
-            if (s.prep_partials && (s.epilogue != INSG_EPI_RESIDUAL || op->n_segments != 1))
-                return fail(INSG_E_ARG, "gemv: sums of squares come from a single residual segment");
+            if (s.prep_partials && op->n_segments != 1) return fail(INSG_E_ARG, "gemv: sums of squares come from a single-segment launch");
             d.prep = static_cast<__half *>(s.prep);
             d.prep_w = s.prep_w;
             if (s.prep_partials) p.prep_partials_out = s.prep_partials;
@@ -734,6 +750,7 @@ int gemv_fused_launch(const insg_gemv_op *op, int M, cudaStream_t st)
     p.trace = static_cast<unsigned long long *>(op->trace);
     p.error_flag = op->error_flag;
     p.prep_partials_in = op->prologue == INSG_PRO_PREPARED ? op->prep_partials : nullptr;
+    p.prep_rms = op->prep_rms != 0;
     const size_t smem = size_t(M) * 2 * (op->cols + 8) * sizeof(__half) + size_t(kWarps) * p.slots * M * 16 * 4 + 64 * 4;
     if (smem > 220 * 1024) return fail(INSG_E_LIMIT, "gemv: shared memory beyond 220 KB");
     const bool pdl = op->pdl != 0;

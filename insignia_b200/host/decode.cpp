@@ -21,7 +21,7 @@ namespace {
 constexpr int kHidden = Qwen35Shape::hidden, kInter = Qwen35Shape::intermediate;
 // DecodeWorkspace::prep: fp16 image of the normalised-to-be hidden vector, fp16 image of the SwiGLU output, sums of squares
 constexpr size_t kPrepHidden = 0, kPrepAct = size_t(2) * kHidden * 2, kPrepSums = kPrepAct + size_t(2) * kInter * 2;
-constexpr size_t kPrepBytes = kPrepSums + 296 * sizeof(float);
+constexpr size_t kPrepBytes = kPrepSums + 2 * 296 * sizeof(float); // one row of sums per image
 const char *const kLM = "language_model";
 
 void cuda_check(cudaError_t e, const char *what)
@@ -234,6 +234,9 @@ void rmsnorm_input(const Ctx &c, insg_gemv_op &op, const uint16_t *norm_w)
         op.in = static_cast<const float *>(c.prep_hidden());
         op.prologue = INSG_PRO_PREPARED;
         op.prep_partials = c.prep_sums();
+        op.prep_rms = 1;
+        op.aux = c.x.hidden; // read instead of the image when the producer's sums put the image out of its range
+        op.norm_w = norm_w;
     } else {
         op.in = c.x.hidden;
         op.norm_w = norm_w;
@@ -315,13 +318,20 @@ static void enqueue_mlp_block(Ctx &c, const Qwen35Decode::Plan::Block &b)
     op.n_segments = 1;
     op.seg[0] = seg(b.gate, c.x.gate, INSG_EPI_SWIGLU);
     op.seg[0].packed2 = b.up.data;
-    if (c.prepared()) op.seg[0].prep = c.prep_act();
+    if (c.prepared()) {
+        op.seg[0].prep = c.prep_act();
+        op.seg[0].prep_partials = c.prep_sums() + 296; // second row: sums of squares of the SwiGLU output
+    }
     run_gemv(c, op);
 
     insg_gemv_op dn = {};
     dn.in = c.prepared() ? static_cast<const float *>(c.prep_act()) : c.x.gate;
     dn.cols = kInter;
     dn.prologue = c.prepared() ? INSG_PRO_PREPARED : INSG_PRO_PLAIN;
+    if (c.prepared()) {
+        dn.prep_partials = c.prep_sums() + 296;
+        dn.aux = c.x.gate;
+    }
     dn.n_segments = 1;
     dn.seg[0] = seg(b.down, c.x.hidden, INSG_EPI_RESIDUAL);
     residual_output(c, dn.seg[0], c.next_norm);

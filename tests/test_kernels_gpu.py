@@ -549,8 +549,9 @@ def test_int8_activation_path(cuda):
 def test_gemv_fused_prepared_chain_matches_in_kernel_prologues(cuda):
     """out_proj (residual, leaves the next RMSNorm's input ready) -> gate|up (prepared input, leaves its SwiGLU output
     ready) -> down (prepared input, residual): against the oracle chain and against the same three launches with the
-    in-kernel prologues."""
-    from insignia_b200 import ops
+    in-kernel prologues.  At scales the fixed-scale image cannot hold (tiny or huge residual stream) the consumer must
+    notice from the producer's sums and read the fp32 vector instead."""
+    from insignia_b200 import _lib, ops
 
     rng = np.random.default_rng(31)
     wo, so = rand_matrix(rng, 4096, 4096)
@@ -560,27 +561,21 @@ def test_gemv_fused_prepared_chain_matches_in_kernel_prologues(cuda):
     po, pg, pu, pd = (ops.repack(dev(w), dev(s)) for w, s in ((wo, so), (wg, sg), (wu, su), (wd, sd)))
     nw = bf16(rng, 4096)
     x0 = rng.standard_normal(4096).astype(np.float32)
-    h0 = (rng.standard_normal(4096) * 3).astype(np.float32)
-    h0[7] = 250.0  # an outlier in the residual stream
-    # oracle
-    h1 = h0 + orc.gemv_mlx_f64(wo, so, x0)
-    n = orc.rmsnorm_bf16(h1.astype(np.float32), nw)
-    g, u = orc.gemv_mlx_f64(wg, sg, n), orc.gemv_mlx_f64(wu, su, n)
-    act = g / (1 + np.exp(-g)) * u
-    h2 = h1 + orc.gemv_mlx_f64(wd, sd, act.astype(np.float32))
 
-    def run(prepared):
+    def run(h0, prepared):
         hidden = dev(h0.copy())
         act_d = torch.zeros(12288, device="cuda")
         img_h = torch.zeros(2 * 4096, dtype=torch.float16, device="cuda")
         img_a = torch.zeros(2 * 12288, dtype=torch.float16, device="cuda")
-        parts = torch.full((296,), 7.0, device="cuda")  # stale values must be overwritten
+        parts = torch.full((2, 296), 7.0, device="cuda")  # stale values must be overwritten
         if prepared:
             ops.gemv_fused(dev(x0), [dict(packed=po, out=hidden, rows=4096, epilogue="residual", prep=img_h, prep_w=dev(nw),
-                                          prep_partials=parts)])
-            ops.gemv_fused(img_h, [dict(packed=pg, packed2=pu, out=act_d, rows=12288, epilogue="swiglu", prep=img_a)],
-                           prologue="prepared", prep_partials=parts, cols=4096)
-            ops.gemv_fused(img_a, [dict(packed=pd, out=hidden, rows=4096, epilogue="residual")], prologue="prepared", cols=12288)
+                                          prep_partials=parts[0])])
+            ops.gemv_fused(img_h, [dict(packed=pg, packed2=pu, out=act_d, rows=12288, epilogue="swiglu", prep=img_a,
+                                        prep_partials=parts[1])],
+                           prologue="prepared", prep_partials=parts[0], prep_rms=True, aux=hidden, norm_w=dev(nw), cols=4096)
+            ops.gemv_fused(img_a, [dict(packed=pd, out=hidden, rows=4096, epilogue="residual")], prologue="prepared",
+                           prep_partials=parts[1], aux=act_d, cols=12288)
         else:
             ops.gemv_fused(dev(x0), [dict(packed=po, out=hidden, rows=4096, epilogue="residual")])
             ops.gemv_fused(hidden, [dict(packed=pg, packed2=pu, out=act_d, rows=12288, epilogue="swiglu")], prologue="rmsnorm",
@@ -588,15 +583,26 @@ def test_gemv_fused_prepared_chain_matches_in_kernel_prologues(cuda):
             ops.gemv_fused(act_d, [dict(packed=pd, out=hidden, rows=4096, epilogue="residual")])
         return host(hidden), host(act_d), host(parts)
 
-    hp, ap, parts = run(True)
-    hn, an, _ = run(False)
-    assert np.max(np.abs(ap - act)) <= 3e-5 * np.abs(act).max()
-    assert np.max(np.abs(hp - h2)) <= 2e-5 * np.abs(h2).max()
-    assert np.max(np.abs(ap - an)) <= 2e-5 * np.abs(an).max() and np.max(np.abs(hp - hn)) <= 1e-5 * np.abs(hn).max()
-    assert abs(parts.sum() - float((h1.astype(np.float64) ** 2).sum())) <= 1e-5 * float((h1 ** 2).sum())
-    assert np.count_nonzero(parts) <= 148
+    for scale, outlier in ((3.0, 250.0), (1e-6, 0.0), (3e6, 0.0), (3.0, 4e7)):
+        h0 = (rng.standard_normal(4096) * scale).astype(np.float32)
+        if outlier:
+            h0[7] = outlier  # an outlier in the residual stream (the second one is beyond what the image can hold)
+        h1 = h0 + orc.gemv_mlx_f64(wo, so, x0)
+        n = orc.rmsnorm_bf16(h1.astype(np.float32), nw)
+        g, u = orc.gemv_mlx_f64(wg, sg, n), orc.gemv_mlx_f64(wu, su, n)
+        act = g / (1 + np.exp(-g)) * u
+        h2 = h1 + orc.gemv_mlx_f64(wd, sd, act.astype(np.float32))
+        hp, ap, parts = run(h0, True)
+        hn, an, _ = run(h0, False)
+        assert np.max(np.abs(ap - act)) <= 3e-5 * np.abs(act).max(), (scale, outlier)
+        assert np.max(np.abs(hp - h2)) <= 2e-5 * np.abs(h2).max(), (scale, outlier)
+        assert np.max(np.abs(ap - an)) <= 2e-5 * np.abs(an).max() and np.max(np.abs(hp - hn)) <= 1e-5 * np.abs(hn).max()
+        if outlier > 1e7 or scale > 1e6:
+            assert np.isinf(parts[0].sum())  # the producer flagged values that did not fit the image
+        else:
+            assert abs(parts[0].sum() - float((h1.astype(np.float64) ** 2).sum())) <= 1e-5 * float((h1.astype(np.float64) ** 2).sum())
+        assert np.count_nonzero(parts[0]) <= 148
     # a prepared input is one token wide, and only residual / SwiGLU rows can be left prepared
-    from insignia_b200 import _lib
     with pytest.raises(_lib.InsigniaError):
         ops.gemv_fused(dev(x0), [dict(packed=po, out=torch.zeros(4096, device="cuda"), rows=4096, epilogue="store",
                                       prep=torch.zeros(8192, dtype=torch.float16, device="cuda"))])
