@@ -91,7 +91,7 @@ def test_gemv_mlx_ragged_rows(cuda):
         assert np.max(np.abs(y - y64)) <= 2e-6 * max(1.0, np.abs(y64).max()) * np.sqrt(cols)
 
 
-@pytest.mark.parametrize("unr,ring", [(2, 0), (4, 0), (4, 2), (4, 4)])
+@pytest.mark.parametrize("unr,ring", [(2, 0), (3, 0), (4, 0), (4, 2), (4, 4)])
 def test_gemv_packed_reference_fixture(cuda, unr, ring):
     from insignia_b200 import ops
 
