@@ -50,7 +50,7 @@ WEIGHT_BYTES_PER_TOKEN = 4_217_924_096  # 24 DeltaNet + 8 attention layers + lm_
 STATE_BYTES_PER_TOKEN = 24 * 2 * (32 * 128 * 128 * 4 + 8192 * 3 * 4)
 # dram__bytes_read+write of the GEMV kernel / its algorithmic bytes, from the ncu capture summarised in
 # profiles/gemv_fused_kernel_65536x4096.md (scaled per launch by the bytes processed)
-GEMV_TRAFFIC_RATIO = 1.034
+GEMV_TRAFFIC_RATIO = 1.03
 
 
 def parse_args():
