@@ -130,6 +130,7 @@ struct Qwen35Decode::Plan {
     cudaGraphExec_t exec{};
     uint64_t graph_nodes = 0;
     bool capturing = false;
+    int *host_result{}; // pinned: {next token, wait-expired flag}, so the per-token read-back is a true asynchronous copy
 };
 
 Qwen35Decode::Qwen35Decode(Qwen35Weights &weights, DecodeWorkspace &workspace) : w_(weights), x_(workspace) {}
@@ -143,6 +144,7 @@ Qwen35Decode::~Qwen35Decode()
     if (p.graph) cudaGraphDestroy(p.graph);
     for (const std::string &n : p.pinned) w_.storage().release(n);
     for (const std::string &n : p.pinned_mats) w_.release(n);
+    if (p.host_result) cudaFreeHost(p.host_result);
     if (p.own_stream) cudaStreamDestroy(p.stream);
 }
 
@@ -159,6 +161,7 @@ Qwen35Decode::Plan &Qwen35Decode::plan()
             cuda_check(cudaStreamCreateWithFlags(&plan_->stream, cudaStreamDefault), "cudaStreamCreate");
             plan_->own_stream = true;
         }
+        cuda_check(cudaMallocHost(&plan_->host_result, 2 * sizeof(int)), "cudaMallocHost");
     }
     return *plan_;
 }
@@ -642,7 +645,9 @@ int Qwen35Decode::logits_argmax()
         insg_check(insg_argmax_logits(x_.logits, x_.options.vocab, x_.d_next, p.stream));
         launches_++;
     }
-    int result[2] = {-1, 0}; // next token, kernel wait-expired flag
+    int *result = p.host_result; // next token, kernel wait-expired flag
+    result[0] = -1;
+    result[1] = 0;
     cuda_check(cudaMemcpyAsync(result, x_.d_next, 2 * sizeof(int), cudaMemcpyDeviceToHost, p.stream), "read token");
     cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
     if (result[1]) throw std::runtime_error("a bounded wait inside a GPU kernel expired");
