@@ -42,16 +42,6 @@ struct AttnParams {
     float *partials;       // [4][kSplits][kPartFloats]
 };
 
-#ifdef INSG_ATTN_TRACE // development build only: stage clocks of every CTA of the last launch
-__device__ unsigned long long g_attn_trace[4 * kSplits][8];
-#define ATTN_TRACE(i)                                                                                   \
-    do {                                                                                                \
-        if (threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g_attn_trace[blockIdx.x][i])); \
-    } while (0)
-#else
-#define ATTN_TRACE(i) do { } while (0)
-#endif
-
 // A lane's 8 dims of one cache row, as loaded (converted only when used, so that two token groups can be in flight).
 template <bool BF16> struct KvRow;
 template <> struct KvRow<false> {
@@ -168,7 +158,6 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     const int kvh = blockIdx.x / kSplits, split = blockIdx.x % kSplits;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    ATTN_TRACE(0);
     pdl_launch_dependents();
 
     // Geometry from the position as it is visible now.  Cache rows of earlier tokens never change
@@ -198,7 +187,6 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     }
 
     pdl_wait();
-    ATTN_TRACE(1);
 
     if constexpr (FUSED) {
         const int now = __ldcg(p.position) + p.position_offset;
@@ -254,7 +242,6 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         }
     }
     __syncthreads();
-    ATTN_TRACE(2);
 
     if (has_work) {
         float q[4][8];
@@ -364,7 +351,6 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         }
     }
     __syncthreads();
-    ATTN_TRACE(3);
     float *part = p.partials + size_t(kvh * kSplits + split) * kPartFloats;
     if (has_work) {
         const int d = tid;
@@ -385,16 +371,13 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         }
     }
     // ---- last CTA of this kv head folds the splits -----------------------------------
-    ATTN_TRACE(4);
     __threadfence();
     __syncthreads();
-    ATTN_TRACE(5);
     if (tid == 0) {
         const unsigned ticket = atomicAdd(p.counters + kvh, 1u);
         s_last = (ticket == kSplits - 1);
     }
     __syncthreads();
-    ATTN_TRACE(6);
     if (s_last) {
         __threadfence();
         const float *pp = p.partials + size_t(kvh * kSplits) * kPartFloats;
@@ -430,7 +413,6 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         reinterpret_cast<float4 *>(p.out + size_t(kvh * 4 + h) * 256)[c4] = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
         if (tid == 0) p.counters[kvh] = 0u;
     }
-    ATTN_TRACE(7);
 }
 
 template <bool BF16, bool FUSED> int launch_attn(const AttnParams &p, cudaStream_t st, bool pdl)
@@ -503,13 +485,6 @@ int insg_gqa_decode_noalloc(const float *q, const void *k_cache, const void *v_c
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(static attention scratch)");
     return attn_plain_launch(q, k_cache, v_cache, out, tokens, kv_dtype, scratch, stream);
 }
-
-#ifdef INSG_ATTN_TRACE
-__attribute__((visibility("default"))) int insg_debug_attn_trace(unsigned long long *host)
-{
-    return cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(g_attn_trace)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 size_t insg_gqa_scratch_bytes(int tokens)
 {

@@ -26,12 +26,6 @@
 //     prologues on the activation, residual / conv+SiLU / decay / beta / SwiGLU / logits+arg-max
 //     epilogues on the rows.
 #include "common.cuh"
-#ifdef INSG_PRO_TRACE // development build: slots 5 and 7 of the phase trace are taken inside the prologue instead
-#define PRO_TRACE(slot)                                                                                  \
-    do {                                                                                                 \
-        if (p.trace && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(p.trace[blockIdx.x * 8 + (slot)])); \
-    } while (0)
-#endif
 #include "gemv_prologue.cuh"
 #include "host_util.h"
 
@@ -211,7 +205,7 @@ __device__ __forceinline__ bool ring_wait(uint64_t *bar, uint32_t parity, int *a
 // Returns 1/alpha, which undoes the power-of-two pre-scale.
 __device__ float prologue(const GemvParams &p, int m, __half *xs, int xstride, const uint2 (&wpre)[kPreVec], float *scratch)
 {
-    const ProIn pin{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue, p.trace};
+    const ProIn pin{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue};
     float4 v[kMaxVec];
     load_activation(pin, m, v);
     const float tmax = transform_activation(pin, m, v, wpre, scratch);
@@ -354,19 +348,11 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
             }
         }
     } else {
-#ifdef INSG_SETUP_TRACE
-        INSG_TRACE(5);
-#endif
-#ifndef INSG_NO_PREFETCH
         load_chunk<UNR>(p, A, lit, ub, lane);
-#ifdef INSG_SETUP_TRACE
-        INSG_TRACE(7);
-#endif
         load_chunk<UNR>(p, B, lit, ub, lane);
-#endif
     }
     uint2 wpre[kPreVec];
-    preload_norm_weights(ProIn{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue, p.trace}, wpre);
+    preload_norm_weights(ProIn{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue}, wpre);
     INSG_TRACE(1);
 
     pdl_wait();
@@ -407,7 +393,7 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
             q.in = p.aux;
             q.aux = nullptr;
             q.prologue = p.norm_w ? INSG_PRO_RMSNORM : INSG_PRO_PLAIN;
-            preload_norm_weights(ProIn{q.in, q.aux, q.norm_w, nullptr, q.cols, q.prologue, nullptr}, wpre);
+            preload_norm_weights(ProIn{q.in, q.aux, q.norm_w, nullptr, q.cols, q.prologue}, wpre);
             __syncthreads(); // every thread has read scratch[1]
 #pragma unroll
             for (int m = 0; m < M; m++) inv_alpha[m] = prologue(q, m, xs, xstride, wpre, scratch);
@@ -421,12 +407,6 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
     }
     __syncthreads();
     INSG_TRACE(3);
-#ifdef INSG_NO_PREFETCH // development experiment: weights requested only after the prologue
-    if constexpr (!RING) {
-        load_chunk<UNR>(p, A, lit, ub, lane);
-        load_chunk<UNR>(p, B, lit, ub, lane);
-    }
-#endif
 
     const bool bactive = (t == (g >> 1));
     const int piece = g & 1;
@@ -520,9 +500,7 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
     }
     INSG_TRACE(4);
     __syncthreads();
-#if !defined(INSG_PRO_TRACE) && !defined(INSG_SETUP_TRACE)
     INSG_TRACE(5);
-#endif
 
     // ---- combine: every (tile) this CTA touched, its runs summed over the warps in warp order --------
     float best = -3.402823466e38f;
@@ -557,9 +535,7 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
                     for (int w = 0; w < kWarps; w++) z += part[w]; // warp order, whatever the schedule
                     y[mat] = z;
                 }
-#if !defined(INSG_PRO_TRACE) && !defined(INSG_SETUP_TRACE)
                 if (tmq == tm_lo) INSG_TRACE(7);
-#endif
                 row_epilogue(s, (tm0 - s.tm_begin) / s.nmat * 16 + row, m, y[0], y[1], best, best_idx, ss);
             }
         }

@@ -4,10 +4,6 @@
 #include "common.cuh"
 #include "insignia_b200.h"
 
-#ifndef PRO_TRACE
-#define PRO_TRACE(slot) do { } while (0)
-#endif
-
 namespace insg {
 
 constexpr int kProThreads = 512; // threads per CTA the prologue is written for
@@ -19,7 +15,6 @@ struct ProIn {
     const uint16_t *norm_w;
     float *x_out;
     int cols, prologue;
-    unsigned long long *trace; // development builds: per-CTA stage clocks (may be null)
 };
 
 __device__ __forceinline__ float block_max16(float v, float *scratch)
@@ -72,7 +67,6 @@ __device__ __forceinline__ float transform_activation(const ProIn &p, int m, flo
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < kMaxVec; j++) ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
-    PRO_TRACE(5); // inputs arrived
     float inv_rms = 1.f;
     float amax = 0.f;
     if (p.prologue == INSG_PRO_RMSNORM) {
@@ -98,7 +92,6 @@ __device__ __forceinline__ float transform_activation(const ProIn &p, int m, flo
         inv_rms = rsqrtf(tot / float(cols) + 1e-6f);
         amax = mx * inv_rms;
     }
-    PRO_TRACE(7); // reductions done
 #pragma unroll
     for (int j = 0; j < kMaxVec; j++) {
         const int i = tid + j * kProThreads;

@@ -490,7 +490,7 @@ int gemv_umma_launch(const insg_gemv_op *op, cudaStream_t st)
     if ((op->prologue == INSG_PRO_RMSNORM || op->prologue == INSG_PRO_GATED_RMSNORM) && !op->norm_w) return fail(INSG_E_ARG, "gemv: norm weight missing");
     if (op->prologue >= INSG_PRO_GATED_RMSNORM && !op->aux) return fail(INSG_E_ARG, "gemv: prologue operand missing");
     UParams p = {};
-    p.pro = ProIn{op->in, op->aux, op->norm_w, op->x_out, op->cols, op->prologue, nullptr};
+    p.pro = ProIn{op->in, op->aux, op->norm_w, op->x_out, op->cols, op->prologue};
     p.nkb = op->cols >> 7;
     p.nseg = op->n_segments;
     int tiles = 0, nmat_all = 0;
