@@ -21,6 +21,7 @@ namespace {
 constexpr int kHidden = Qwen35Shape::hidden, kInter = Qwen35Shape::intermediate;
 // DecodeWorkspace::prep: fp16 image of the normalised-to-be hidden vector, fp16 image of the SwiGLU output, sums of squares
 constexpr size_t kPrepHidden = 0, kPrepAct = size_t(2) * kHidden * 2, kPrepSums = kPrepAct + size_t(2) * kInter * 2;
+constexpr int kMultiSteps = 8; // token steps per graph in Qwen35Decode::generate
 constexpr size_t kPrepBytes = kPrepSums + 2 * 296 * sizeof(float); // one row of sums per image
 const char *const kLM = "language_model";
 
@@ -130,6 +131,7 @@ struct Qwen35Decode::Plan {
     cudaGraphExec_t exec{};
     uint64_t graph_nodes = 0;
     bool capturing = false;
+    cudaGraphExec_t exec_multi{}; // kMultiSteps token steps in one graph, for device-fed generation
     int *host_result{}; // pinned: {next token, wait-expired flag}, so the per-token read-back is a true asynchronous copy
 };
 
@@ -141,6 +143,7 @@ Qwen35Decode::~Qwen35Decode()
     Plan &p = *plan_;
     cudaStreamSynchronize(p.stream);
     if (p.exec) cudaGraphExecDestroy(p.exec);
+    if (p.exec_multi) cudaGraphExecDestroy(p.exec_multi);
     if (p.graph) cudaGraphDestroy(p.graph);
     for (const std::string &n : p.pinned) w_.storage().release(n);
     for (const std::string &n : p.pinned_mats) w_.release(n);
@@ -669,9 +672,37 @@ std::vector<int> Qwen35Decode::generate(int first_token, int count)
     Plan &p = plan();
     const int start = x_.position;
     sync_scalars(first_token);
-    for (int i = 0; i < count; i++) {
-        replay_token_step(); // the head feeds its arg-max back into d_token and advances d_position
-        x_.position++;
+    for (int i = 0; i < count;) {
+        // The head feeds its arg-max back into d_token and advances d_position, so consecutive steps need nothing from
+        // the host.  Once the single-step graph exists, runs of kMultiSteps steps go out as one graph: the dependent-launch
+        // edges then also span the token boundaries, and there is one graph launch per kMultiSteps tokens.
+        if (x_.options.use_graph && p.exec && count - i >= kMultiSteps) {
+            if (!p.exec_multi) {
+                const uint64_t before = launches_;
+                cudaGraph_t g = nullptr;
+                cuda_check(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal), "begin graph capture");
+                try {
+                    for (int k = 0; k < kMultiSteps; k++) enqueue_token_step();
+                } catch (...) {
+                    cudaStreamEndCapture(p.stream, &g);
+                    if (g) cudaGraphDestroy(g);
+                    throw;
+                }
+                launches_ = before;
+                cuda_check(cudaStreamEndCapture(p.stream, &g), "end graph capture");
+                const cudaError_t e = cudaGraphInstantiate(&p.exec_multi, g, 0);
+                cudaGraphDestroy(g);
+                cuda_check(e, "instantiate graph");
+            }
+            cuda_check(cudaGraphLaunch(p.exec_multi, p.stream), "launch graph");
+            launches_ += p.graph_nodes * kMultiSteps;
+            x_.position += kMultiSteps;
+            i += kMultiSteps;
+        } else {
+            replay_token_step();
+            x_.position++;
+            i++;
+        }
     }
     fused_token_valid_ = true;
     cuda_check(cudaMemcpyAsync(out.data(), x_.d_token + 4 + start, size_t(count) * sizeof(int), cudaMemcpyDeviceToHost, p.stream),
