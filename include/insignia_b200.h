@@ -197,6 +197,10 @@ typedef struct insg_gemv_op {
     int pdl;                  /* 1: launch with programmatic dependent launch          */
     const float *prep_partials; /* INSG_PRO_PREPARED: the producer's prep_partials [296], or NULL                        */
     int prep_rms;               /* INSG_PRO_PREPARED: 1 = scale by the RMS factor computed from prep_partials            */
+    int tokens;                 /* 0 or 1: one token.  2 or 4: consecutive tokens of one sequence in one launch (the
+                                   weights are streamed once): in, aux and x_out are [tokens][cols], every out is
+                                   [tokens][rows]; the convolution history is advanced token by token.  Not with
+                                   INSG_PRO_PREPARED, prepared outputs or INSG_EPI_LOGITS. */
 } insg_gemv_op;
 
 INSG_API size_t insg_gemv_argmax_scratch_bytes(void);
@@ -342,6 +346,10 @@ INSG_API int insg_engine_layer(insg_engine *e, int layer);
 /* Qwen35Decode::forward_token (src/decode.cu:21): asynchronous */
 INSG_API int insg_engine_forward_token(insg_engine *e, int token);
 /* Qwen35Decode::logits_argmax (src/decode.cu:22): synchronises, returns the token id (>=0) */
+/* Additive: insg_engine_forward_token for `count` consecutive tokens (host array), four tokens per pass over the
+ * weights; same resulting state, logits and arg-max of the last token.  No reference counterpart (its prompt loop is
+ * src/generate_ids.cu:4). */
+INSG_API int insg_engine_forward_tokens(insg_engine *e, const int *tokens /* host */, int count);
 INSG_API int insg_engine_logits_argmax(insg_engine *e);
 /* Qwen35Decode::decode_token (src/decode.cu:23): synchronises, returns the token id (>=0) */
 INSG_API int insg_engine_decode_token(insg_engine *e, int token);

@@ -60,6 +60,7 @@ public:
     int *d_next{};       // device: arg-max of the last logits
     void *attn_scratch{};
     void *argmax_scratch{};
+    float *multi{};      // device: activations of up to four consecutive tokens (forward_tokens)
     void *prep{};        // device: prepared GEMV inputs, fp16 [2][4096] + fp16 [2][12288] + fp32 [2][296] sums of squares
     void *trace{};       // optional profiling buffer: [GEMV launch of the step][296 CTAs][8] u64 timestamps (see insg_gemv_op.trace)
     int trace_index{};   // GEMV launches enqueued since the step began
@@ -78,6 +79,9 @@ public:
     void layer(int layer);
     int decode_token(int token);
     void forward_token(int token);
+    // Additive: forward_token for `count` consecutive tokens (a prompt), the GEMVs taking four tokens per pass over the
+    // weights; leaves the same state as the loop would, and the logits and arg-max of the last token.
+    void forward_tokens(const int *tokens, int count);
     int logits_argmax();
     int mtp_draft(int input_token);
 
@@ -101,6 +105,7 @@ private:
     void enqueue_embed();
     // hidden_prepared: the launch before left this block's input prepared; next_norm: weight of the RMSNorm that reads
     // this block's output next (the block then leaves that input prepared), or null when the caller may touch hidden
+    void load_embed();
     void load_block(int layer);
     void load_head();
     void enqueue_delta(int layer, bool hidden_prepared = false, const uint16_t *next_norm = nullptr);

@@ -25,7 +25,7 @@ class GemvOp(C.Structure):
     _fields_ = [("in_", vp), ("aux", vp), ("norm_w", vp), ("x_out", vp), ("cols", i32), ("prologue", i32),
                 ("n_segments", i32), ("seg", GemvSegment * 4), ("argmax_scratch", vp), ("token_out", vp),
                 ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("trace", vp), ("layout", i32), ("error_flag", vp), ("pdl", i32),
-                ("prep_partials", vp), ("prep_rms", i32)]
+                ("prep_partials", vp), ("prep_rms", i32), ("tokens", i32)]
 
 
 class AttnOp(C.Structure):
@@ -85,6 +85,7 @@ SIGNATURES = {
     "insg_engine_embed": (i32, [vp, i32]),
     "insg_engine_layer": (i32, [vp, i32]),
     "insg_engine_forward_token": (i32, [vp, i32]),
+    "insg_engine_forward_tokens": (i32, [vp, vp, i32]),
     "insg_engine_logits_argmax": (i32, [vp]),
     "insg_engine_decode_token": (i32, [vp, i32]),
     "insg_engine_mtp_draft": (i32, [vp, i32]),

@@ -520,7 +520,10 @@ __global__ void __launch_bounds__(kThreads, RING ? 2 : 1) gemv_fused_kernel(cons
             const int local = tmq - s.tm_begin;
             if (s.nmat == 2 && (local & 1)) continue; // the pair is handled from its gate run
             const int tm0 = tmq - (s.nmat == 2 ? (local & 1) : 0);
-            for (int m = lane >> 4; m < M; m += 2) {
+            // Tokens are independent except for the convolution, whose history is carried from one token to the next:
+            // there the 16 row lanes walk the tokens in order, elsewhere the two half-warps take alternate tokens.
+            const bool serial = M > 1 && s.epilogue == INSG_EPI_CONV_SILU;
+            for (int m = serial ? (lane < 16 ? 0 : M) : lane >> 4; m < M; m += serial ? 1 : 2) {
                 float y[2] = {0.f, 0.f};
                 for (int mat = 0; mat < s.nmat; mat++) {
                     const int tm = tm0 + mat, lo = max(tm * nkb, a), hi = min((tm + 1) * nkb, b);
@@ -642,7 +645,7 @@ template <int M> int dispatch(const GemvParams &p, int grid, size_t smem, cudaSt
         if (smem + size_t(kWarps) * 3 * kRec <= 112 * 1024 && g_tune.ring >= 3) return launch_variant<3, M, true>(p, grid, smem, st, pdl);
         return launch_variant<2, M, true>(p, grid, smem, st, pdl);
     }
-    if (g_tune.unr == 2) return launch_variant<2, M, false>(p, grid, smem, st, pdl);
+    if (g_tune.unr == 2 || M == 4) return launch_variant<2, M, false>(p, grid, smem, st, pdl); // four tokens: registers for accumulators
     if (g_tune.unr == 3) return launch_variant<3, M, false>(p, grid, smem, st, pdl);
     return launch_variant<4, M, false>(p, grid, smem, st, pdl);
 }
@@ -748,8 +751,11 @@ size_t insg_gemv_argmax_scratch_bytes(void) { return 64 + size_t(8) * 512; }
 
 int insg_gemv_fused(const insg_gemv_op *op, insg_stream_t stream)
 {
-    if (op && op->layout == 1) return gemv_umma_launch(op, stream);
-    return gemv_fused_launch(op, 1, stream);
+    if (op && op->layout == 1) {
+        if (op->tokens > 1) return fail(INSG_E_SHAPE, "gemv: the tcgen05 layout takes one token per launch");
+        return gemv_umma_launch(op, stream);
+    }
+    return gemv_fused_launch(op, op && op->tokens > 1 ? op->tokens : 1, stream);
 }
 
 int insg_mxfp4_gemv_packed(const void *packed, const float *x, float *y, int rows, int cols, int M, insg_stream_t stream)

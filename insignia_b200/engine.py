@@ -55,6 +55,11 @@ class Engine:
     def forward_token(self, token: int):
         check(_lib.lib().insg_engine_forward_token(self._h, token))
 
+    def forward_tokens(self, tokens):
+        """``forward_token`` over a list of consecutive tokens, four per pass over the weights (prompt processing)."""
+        arr = (C.c_int * len(tokens))(*[int(t) for t in tokens])
+        check(_lib.lib().insg_engine_forward_tokens(self._h, arr, len(tokens)))
+
     def logits_argmax(self) -> int:
         return check(_lib.lib().insg_engine_logits_argmax(self._h))
 

@@ -22,6 +22,13 @@ constexpr int kHidden = Qwen35Shape::hidden, kInter = Qwen35Shape::intermediate;
 // DecodeWorkspace::prep: fp16 image of the normalised-to-be hidden vector, fp16 image of the SwiGLU output, sums of squares
 constexpr size_t kPrepHidden = 0, kPrepAct = size_t(2) * kHidden * 2, kPrepSums = kPrepAct + size_t(2) * kInter * 2;
 constexpr int kMultiSteps = 8; // token steps per graph in Qwen35Decode::generate
+// DecodeWorkspace::multi: activations of up to kChunk consecutive tokens for Qwen35Decode::forward_tokens, [token][width] each
+constexpr int kChunk = 4;
+constexpr size_t kMultiHidden = 0, kMultiQkv = kMultiHidden + size_t(kChunk) * 4096, kMultiZ = kMultiQkv + size_t(kChunk) * 8192,
+                 kMultiA = kMultiZ + size_t(kChunk) * 4096, kMultiB = kMultiA + size_t(kChunk) * 32, kMultiCore = kMultiB + size_t(kChunk) * 32,
+                 kMultiQg = kMultiCore + size_t(kChunk) * 4096, kMultiKey = kMultiQg + size_t(kChunk) * 8192,
+                 kMultiValue = kMultiKey + size_t(kChunk) * 1024, kMultiAct = kMultiValue + size_t(kChunk) * 1024,
+                 kMultiTokens = kMultiAct + size_t(kChunk) * 12288, kMultiFloats = kMultiTokens + kChunk;
 constexpr size_t kPrepBytes = kPrepSums + 2 * 296 * sizeof(float); // one row of sums per image
 const char *const kLM = "language_model";
 
@@ -80,6 +87,7 @@ void DecodeWorkspace::allocate()
     cuda_check(cudaMalloc(&attn_scratch, insg_gqa_scratch_bytes(max_context)), "cudaMalloc attention scratch");
     cuda_check(cudaMalloc(&argmax_scratch, insg_gemv_argmax_scratch_bytes()), "cudaMalloc arg-max scratch");
     cuda_check(cudaMalloc(&prep, kPrepBytes), "cudaMalloc prepared inputs");
+    cuda_check(cudaMalloc(&multi, kMultiFloats * sizeof(float)), "cudaMalloc multi-token buffers");
     cuda_check(cudaMemsetAsync(prep, 0, kPrepBytes, stream), "memset");
     cuda_check(cudaMemsetAsync(attn_scratch, 0, 64, stream), "memset");
     cuda_check(cudaMemsetAsync(argmax_scratch, 0, 64, stream), "memset");
@@ -100,7 +108,7 @@ DecodeWorkspace::~DecodeWorkspace()
     for (void *p : {(void *)hidden, (void *)norm, (void *)qkv, (void *)attn_gate, (void *)key, (void *)value, (void *)z, (void *)a,
                     (void *)b, (void *)core, (void *)gate, (void *)up, (void *)down, (void *)logits, (void *)delta_state,
                     (void *)conv_state, (void *)kv_keys, (void *)kv_values, (void *)mtp_keys, (void *)mtp_values, (void *)d_token,
-                    attn_scratch, argmax_scratch, prep})
+                    attn_scratch, argmax_scratch, prep, (void *)multi})
         cudaFree(p);
 }
 
@@ -129,9 +137,10 @@ struct Qwen35Decode::Plan {
     bool own_stream = false;
     cudaGraph_t graph{};
     cudaGraphExec_t exec{};
-    uint64_t graph_nodes = 0;
-    bool capturing = false;
+    uint64_t graph_nodes = 0, chunk_nodes = 0;
+    bool capturing = false, chunk_warm = false;
     cudaGraphExec_t exec_multi{}; // kMultiSteps token steps in one graph, for device-fed generation
+    cudaGraphExec_t exec_chunk{}; // one pass of forward_tokens over kChunk prompt tokens
     int *host_result{}; // pinned: {next token, wait-expired flag}, so the per-token read-back is a true asynchronous copy
 };
 
@@ -144,6 +153,7 @@ Qwen35Decode::~Qwen35Decode()
     cudaStreamSynchronize(p.stream);
     if (p.exec) cudaGraphExecDestroy(p.exec);
     if (p.exec_multi) cudaGraphExecDestroy(p.exec_multi);
+    if (p.exec_chunk) cudaGraphExecDestroy(p.exec_chunk);
     if (p.graph) cudaGraphDestroy(p.graph);
     for (const std::string &n : p.pinned) w_.storage().release(n);
     for (const std::string &n : p.pinned_mats) w_.release(n);
@@ -428,6 +438,138 @@ static void enqueue_attention_block(Ctx &c, const Qwen35Decode::Plan::Block &b, 
     enqueue_mlp_block(c, b);
 }
 
+// ---- the same blocks over T = 2 or 4 consecutive tokens of the sequence (prompt processing): every GEMV streams its
+// weights once for the T tokens; the DeltaNet and attention steps, which are recurrences, run token by token.
+namespace {
+struct Multi {
+    float *hidden, *qkv, *z, *a, *b, *core, *qg, *key, *value, *act;
+    int *tokens;
+    int T;
+    explicit Multi(DecodeWorkspace &x, int t)
+        : hidden(x.multi + kMultiHidden), qkv(x.multi + kMultiQkv), z(x.multi + kMultiZ), a(x.multi + kMultiA), b(x.multi + kMultiB),
+          core(x.multi + kMultiCore), qg(x.multi + kMultiQg), key(x.multi + kMultiKey), value(x.multi + kMultiValue),
+          act(x.multi + kMultiAct), tokens(reinterpret_cast<int *>(x.multi + kMultiTokens)), T(t)
+    {
+    }
+};
+
+void mlp_block_multi(Ctx &c, const Qwen35Decode::Plan::Block &b, const Multi &u)
+{
+    insg_gemv_op op = {};
+    op.in = u.hidden;
+    op.norm_w = b.post_norm;
+    op.cols = kHidden;
+    op.prologue = INSG_PRO_RMSNORM;
+    op.tokens = u.T;
+    op.n_segments = 1;
+    op.seg[0] = seg(b.gate, u.act, INSG_EPI_SWIGLU);
+    op.seg[0].packed2 = b.up.data;
+    run_gemv(c, op);
+
+    insg_gemv_op dn = {};
+    dn.in = u.act;
+    dn.cols = kInter;
+    dn.prologue = INSG_PRO_PLAIN;
+    dn.tokens = u.T;
+    dn.n_segments = 1;
+    dn.seg[0] = seg(b.down, u.hidden, INSG_EPI_RESIDUAL);
+    run_gemv(c, dn);
+}
+
+void delta_block_multi(Ctx &c, const Qwen35Decode::Plan::Block &b, int di, const Multi &u)
+{
+    DecodeWorkspace &x = c.x;
+    insg_gemv_op in = {};
+    in.in = u.hidden;
+    in.norm_w = b.in_norm;
+    in.cols = kHidden;
+    in.prologue = INSG_PRO_RMSNORM;
+    in.tokens = u.T;
+    in.n_segments = 4;
+    in.seg[0] = seg(b.qkv, u.qkv, INSG_EPI_CONV_SILU);
+    in.seg[0].conv_state = x.conv_state + size_t(di) * 8192 * 3;
+    in.seg[0].conv_w = b.conv_w;
+    in.seg[1] = seg(b.z, u.z, INSG_EPI_STORE);
+    in.seg[2] = seg(b.a, u.a, INSG_EPI_DECAY);
+    in.seg[2].A_log = b.A_log;
+    in.seg[2].dt_bias = b.dt_bias;
+    in.seg[3] = seg(b.b, u.b, INSG_EPI_BETA);
+    run_gemv(c, in);
+
+    for (int m = 0; m < u.T; m++) {
+        const float *q = u.qkv + size_t(m) * 8192;
+        // no dependent-launch overlap here: the kernel fetches its state before the dependency wait, which is only safe
+        // when the state was not written by the launch right before it (in decoding it was written a token ago)
+        insg_check(insg_deltanet_decode(x.delta_state + size_t(di) * 32 * 128 * 128, q, q + 2048, q + 4096, u.a + m * 32, u.b + m * 32,
+                                        u.core + size_t(m) * 4096, /*pdl*/ 0, c.st));
+        c.launches++;
+    }
+
+    insg_gemv_op out = {};
+    out.in = u.core;
+    out.aux = u.z;
+    out.norm_w = b.dn_norm;
+    out.cols = 4096;
+    out.prologue = INSG_PRO_GATED_RMSNORM;
+    out.tokens = u.T;
+    out.n_segments = 1;
+    out.seg[0] = seg(b.out, u.hidden, INSG_EPI_RESIDUAL);
+    run_gemv(c, out);
+
+    mlp_block_multi(c, b, u);
+}
+
+void attention_block_multi(Ctx &c, const Qwen35Decode::Plan::Block &b, void *kc, void *vc, const Multi &u)
+{
+    DecodeWorkspace &x = c.x;
+    insg_gemv_op in = {};
+    in.in = u.hidden;
+    in.norm_w = b.in_norm;
+    in.cols = kHidden;
+    in.prologue = INSG_PRO_RMSNORM;
+    in.tokens = u.T;
+    in.n_segments = 3;
+    in.seg[0] = seg(b.q, u.qg, INSG_EPI_STORE);
+    in.seg[1] = seg(b.k, u.key, INSG_EPI_STORE);
+    in.seg[2] = seg(b.v, u.value, INSG_EPI_STORE);
+    run_gemv(c, in);
+
+    for (int m = 0; m < u.T; m++) { // token m sits at the device position + m and sees the rows of the tokens before it
+        insg_attn_op at = {};
+        at.qraw = u.qg + size_t(m) * 8192;
+        at.k_raw = u.key + size_t(m) * 1024;
+        at.v = u.value + size_t(m) * 1024;
+        at.q_norm_w = b.q_norm;
+        at.k_norm_w = b.k_norm;
+        at.k_cache = kc;
+        at.v_cache = vc;
+        at.out = u.core + size_t(m) * 4096;
+        at.position = x.d_position;
+        at.position_offset = m;
+        at.max_context = x.max_context;
+        at.kv_dtype = x.options.kv_bf16 ? INSG_KV_BF16 : INSG_KV_F32;
+        at.fast_trig = x.options.accurate_trig ? 0 : 1;
+        at.scratch = x.attn_scratch;
+        at.scratch_bytes = insg_gqa_scratch_bytes(x.max_context);
+        at.pdl = 0; // it fetches cache rows before the dependency wait; the row of token m - 1 was written by the launch before
+        insg_check(insg_attention_step(&at, c.st));
+        c.launches++;
+    }
+
+    insg_gemv_op o = {};
+    o.in = u.core;
+    o.aux = u.qg;
+    o.cols = 4096;
+    o.prologue = x.options.gate_elementwise ? INSG_PRO_SIGMOID_GATE_QPROJ : INSG_PRO_SIGMOID_GATE_HEAD0;
+    o.tokens = u.T;
+    o.n_segments = 1;
+    o.seg[0] = seg(b.o, u.hidden, INSG_EPI_RESIDUAL);
+    run_gemv(c, o);
+
+    mlp_block_multi(c, b, u);
+}
+} // namespace
+
 static void load_mlp(Loader &L, const std::string &p, Qwen35Decode::Plan::Block &b)
 {
     b.post_norm = L.bf16(p + ".post_attention_layernorm.weight", kHidden);
@@ -477,16 +619,21 @@ void Qwen35Decode::sync_scalars(int token)
     launches_++;
 }
 
+void Qwen35Decode::load_embed()
+{
+    Plan &p = plan();
+    if (p.embed_ready) return;
+    const std::string base = std::string(kLM) + ".model.embed_tokens";
+    p.embed = w_.matrix(base);
+    p.pinned_mats.push_back(base);
+    if (p.embed.cols != kHidden) throw std::runtime_error("unexpected matrix shape: " + base);
+    p.embed_ready = true;
+}
+
 void Qwen35Decode::enqueue_embed()
 {
     Plan &p = plan();
-    if (!p.embed_ready) {
-        const std::string base = std::string(kLM) + ".model.embed_tokens";
-        p.embed = w_.matrix(base);
-        p.pinned_mats.push_back(base);
-        if (p.embed.cols != kHidden) throw std::runtime_error("unexpected matrix shape: " + base);
-        p.embed_ready = true;
-    }
+    load_embed();
     Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_};
     if (prof_ && prof_->gemv_only) return;
     Timed t(c, 3, uint64_t(kHidden) * 17 / 32);
@@ -626,6 +773,24 @@ void Qwen35Decode::replay_token_step()
         p.graph_nodes = launches_ - before;
         launches_ = before;
         cuda_check(cudaGraphInstantiate(&p.exec, p.graph, 0), "instantiate graph");
+        // and kMultiSteps steps as one graph for device-fed generation (built here, once, so that no later call pays for it)
+        cudaGraph_t g = nullptr;
+        cuda_check(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal), "begin graph capture");
+        try {
+            for (int k = 0; k < kMultiSteps; k++) enqueue_token_step();
+        } catch (...) {
+            cudaStreamEndCapture(p.stream, &g);
+            if (g) cudaGraphDestroy(g);
+            throw;
+        }
+        launches_ = before;
+        cuda_check(cudaStreamEndCapture(p.stream, &g), "end graph capture");
+        const cudaError_t e = cudaGraphInstantiate(&p.exec_multi, g, 0);
+        cudaGraphDestroy(g);
+        cuda_check(e, "instantiate graph");
+        // upload now: otherwise the first launch of each graph pays for it
+        cuda_check(cudaGraphUpload(p.exec, p.stream), "upload graph");
+        cuda_check(cudaGraphUpload(p.exec_multi, p.stream), "upload graph");
     }
     cuda_check(cudaGraphLaunch(p.exec, p.stream), "launch graph");
     launches_ += p.graph_nodes;
@@ -639,6 +804,87 @@ void Qwen35Decode::forward_token(int token)
     replay_token_step();
     x_.position++;
     fused_token_valid_ = true;
+}
+
+void Qwen35Decode::forward_tokens(const int *tokens, int count)
+{
+    if (count <= 0) return;
+    if (!tokens) throw std::runtime_error("forward_tokens: null token list");
+    for (int i = 0; i < count; i++)
+        if (tokens[i] < 0 || tokens[i] >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
+    if (x_.options.n_layers > 3 && x_.position + count > x_.max_context) throw std::runtime_error("KV cache full");
+    if (x_.options.gemv_tcgen05) { // that layout takes one token per launch
+        for (int i = 0; i < count; i++) forward_token(tokens[i]);
+        return;
+    }
+    Plan &p = plan();
+    const int n = x_.options.n_layers;
+    for (int l = 0; l < n; l++) load_block(l);
+    load_head();
+    load_embed();
+    Ctx c{x_, p.stream, x_.options.use_pdl, launches_, nullptr};
+    for (int done = 0; done < count;) {
+        const int left = count - done, T = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
+        Multi u(x_, T);
+        sync_scalars(-1); // the chunk's first position; token m of the chunk sits at position + m
+        cuda_check(cudaMemcpyAsync(u.tokens, tokens + done, size_t(T) * sizeof(int), cudaMemcpyHostToDevice, p.stream), "copy tokens");
+        auto enqueue_chunk = [&] {
+            for (int m = 0; m < T; m++) {
+                insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
+                                            u.hidden + size_t(m) * kHidden, u.tokens + m, p.embed.rows, kHidden, c.pdl ? 1 : 0, p.stream));
+                launches_++;
+            }
+            for (int l = 0; l < n; l++) {
+                if (Qwen35Shape::full_attention(l)) {
+                    const size_t esz = x_.options.kv_bf16 ? 2 : 4;
+                    const size_t off = size_t(l / 4) * x_.max_context * 1024 * esz;
+                    attention_block_multi(c, p.layers[l], reinterpret_cast<uint8_t *>(x_.kv_keys) + off,
+                                          reinterpret_cast<uint8_t *>(x_.kv_values) + off, u);
+                } else {
+                    delta_block_multi(c, p.layers[l], l - l / 4, u);
+                }
+            }
+        };
+        if (T == kChunk && x_.options.use_graph && p.chunk_warm) {
+            // full chunks replay one graph (tokens and position are read from device memory); the first full chunk ran
+            // eagerly (first launches of a kernel variant set function attributes)
+            const uint64_t before = launches_;
+            if (!p.exec_chunk) {
+                cudaGraph_t g = nullptr;
+                cuda_check(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal), "begin graph capture");
+                try {
+                    enqueue_chunk();
+                } catch (...) {
+                    cudaStreamEndCapture(p.stream, &g);
+                    if (g) cudaGraphDestroy(g);
+                    throw;
+                }
+                cuda_check(cudaStreamEndCapture(p.stream, &g), "end graph capture");
+                const cudaError_t e = cudaGraphInstantiate(&p.exec_chunk, g, 0);
+                cudaGraphDestroy(g);
+                cuda_check(e, "instantiate graph");
+                p.chunk_nodes = launches_ - before;
+            }
+            launches_ = before + p.chunk_nodes;
+            cuda_check(cudaGraphLaunch(p.exec_chunk, p.stream), "launch graph");
+        } else {
+            enqueue_chunk();
+            p.chunk_warm |= T == kChunk;
+        }
+        x_.position += T;
+        done += T;
+        if (done == count) // the sequence's hidden state is the last token's
+            cuda_check(cudaMemcpyAsync(x_.hidden, u.hidden + size_t(T - 1) * kHidden, kHidden * sizeof(float), cudaMemcpyDeviceToDevice, p.stream),
+                       "copy hidden");
+    }
+    // logits of the last token (from the fp32 hidden vector; nothing was left prepared); the head also writes the
+    // arg-max, so logits_argmax() needs no further launch
+    x_.position--;
+    sync_scalars(tokens[count - 1]);
+    enqueue_head(false);
+    x_.position++;
+    fused_token_valid_ = true;
+    p.capturing = true; // every weight is resident now: the next forward_token may capture its graph
 }
 
 int Qwen35Decode::logits_argmax()
@@ -674,26 +920,9 @@ std::vector<int> Qwen35Decode::generate(int first_token, int count)
     sync_scalars(first_token);
     for (int i = 0; i < count;) {
         // The head feeds its arg-max back into d_token and advances d_position, so consecutive steps need nothing from
-        // the host.  Once the single-step graph exists, runs of kMultiSteps steps go out as one graph: the dependent-launch
-        // edges then also span the token boundaries, and there is one graph launch per kMultiSteps tokens.
-        if (x_.options.use_graph && p.exec && count - i >= kMultiSteps) {
-            if (!p.exec_multi) {
-                const uint64_t before = launches_;
-                cudaGraph_t g = nullptr;
-                cuda_check(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal), "begin graph capture");
-                try {
-                    for (int k = 0; k < kMultiSteps; k++) enqueue_token_step();
-                } catch (...) {
-                    cudaStreamEndCapture(p.stream, &g);
-                    if (g) cudaGraphDestroy(g);
-                    throw;
-                }
-                launches_ = before;
-                cuda_check(cudaStreamEndCapture(p.stream, &g), "end graph capture");
-                const cudaError_t e = cudaGraphInstantiate(&p.exec_multi, g, 0);
-                cudaGraphDestroy(g);
-                cuda_check(e, "instantiate graph");
-            }
+        // the host.  Once the graphs exist, runs of kMultiSteps steps go out as one graph: the dependent-launch edges
+        // then also span the token boundaries, and there is one graph launch per kMultiSteps tokens.
+        if (x_.options.use_graph && p.exec_multi && count - i >= kMultiSteps) {
             cuda_check(cudaGraphLaunch(p.exec_multi, p.stream), "launch graph");
             launches_ += p.graph_nodes * kMultiSteps;
             x_.position += kMultiSteps;

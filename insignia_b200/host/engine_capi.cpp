@@ -126,6 +126,13 @@ int insg_engine_forward_token(insg_engine *e, int token)
         return INSG_OK;
     });
 }
+int insg_engine_forward_tokens(insg_engine *e, const int *tokens, int count)
+{
+    return guarded(e, [&] {
+        e->dec->forward_tokens(tokens, count);
+        return int(INSG_OK);
+    });
+}
 int insg_engine_logits_argmax(insg_engine *e)
 {
     return guarded(e, [&] { return e->dec->logits_argmax(); });

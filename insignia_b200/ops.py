@@ -88,14 +88,14 @@ def gemv_packed(packed, x, rows=None, cols=None):
 
 
 def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, trace=None, layout=0, error_flag=None,
-               prep_partials=None, prep_rms=False, cols=None):
+               prep_partials=None, prep_rms=False, cols=None, tokens=1):
     """``segments``: list of dicts with packed, out, rows, epilogue (+ packed2 / conv_state, conv_w / A_log, dt_bias /
     prep, prep_w, prep_partials).  ``argmax``: dict(scratch, token_out[, token_feedback, token_log, position]) for the
     logits epilogue.  With ``prologue="prepared"`` ``inp`` is the fp16 image [2][cols] a producer left through ``prep``."""
     op = GemvOp()
     op.in_, op.aux, op.norm_w, op.x_out = _p(inp), _p(aux), _p(norm_w), _p(x_out)
     op.cols, op.prologue, op.n_segments = cols or inp.shape[-1], PRO[prologue], len(segments)
-    op.prep_partials, op.prep_rms = _p(prep_partials), int(prep_rms)
+    op.prep_partials, op.prep_rms, op.tokens = _p(prep_partials), int(prep_rms), tokens
     for i, s in enumerate(segments):
         g = op.seg[i]
         g.packed, g.packed2, g.out = _p(s["packed"]), _p(s.get("packed2")), _p(s["out"])

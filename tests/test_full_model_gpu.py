@@ -93,6 +93,33 @@ def test_greedy_tokens_identical_to_reference(cuda, full_ckpt):
         ref.close()
 
 
+def test_prompt_in_passes_of_four_then_greedy_tokens_identical_to_reference(cuda, full_ckpt):
+    """The prompt through forward_tokens (four tokens per pass over the weights), then greedy decode: same ids as the
+    reference fed token by token."""
+    from insignia_b200.engine import Engine
+
+    n_prompt, n_gen = 61, 48
+    rng = np.random.default_rng(77)
+    prompt = [int(t) for t in rng.integers(0, 248320, n_prompt)]
+    ref = ref_engine.RefEngine(full_ckpt[1], max_context=n_prompt + n_gen + 4)
+    try:
+        with Engine(full_ckpt[1], max_context=n_prompt + n_gen + 4) as e:
+            for t in prompt:
+                ref.forward_token(t)
+            e.forward_tokens(prompt)
+            tr, te = ref.logits_argmax(), e.logits_argmax()
+            assert tr == te
+            assert cos(e.read("hidden"), ref.read("hidden", 4096)) >= 0.9999
+            want, t = [], tr
+            for _ in range(n_gen):
+                t = ref.decode_token(t)
+                want.append(t)
+            assert e.generate(te, n_gen) == want
+            assert e.position == ref.position == n_prompt + n_gen
+    finally:
+        ref.close()
+
+
 def test_mtp_draft_matches_reference(cuda, full_ckpt):
     """src/test_mtp.cu:3: forward a token, take the arg-max, draft twice."""
     from insignia_b200.engine import Engine

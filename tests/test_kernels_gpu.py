@@ -606,3 +606,59 @@ def test_gemv_fused_prepared_chain_matches_in_kernel_prologues(cuda):
     with pytest.raises(_lib.InsigniaError):
         ops.gemv_fused(dev(x0), [dict(packed=po, out=torch.zeros(4096, device="cuda"), rows=4096, epilogue="store",
                                       prep=torch.zeros(8192, dtype=torch.float16, device="cuda"))])
+
+
+@pytest.mark.parametrize("tokens", [2, 4])
+def test_gemv_fused_consecutive_tokens_equal_single_token_launches(cuda, tokens):
+    """A launch over 2 or 4 consecutive tokens of one sequence (weights streamed once) gives, bit for bit, what one
+    launch per token gives, including the convolution history that is carried from token to token."""
+    from insignia_b200 import mxfp4, ops
+
+    rng = np.random.default_rng(41)
+    nq = 256
+    wq, sq = rand_matrix(rng, nq, 4096)
+    wz, sz = rand_matrix(rng, 64, 4096)
+    wa, sa = rand_matrix(rng, 32, 4096, std=0.05)
+    wb, sb = rand_matrix(rng, 32, 4096, std=0.05)
+    P = [ops.repack(dev(w), dev(s)) for w, s in ((wq, sq), (wz, sz), (wa, sa), (wb, sb))]
+    d_cw = dev(mxfp4.f32_to_bf16_bits((0.5 * rng.standard_normal((nq, 4))).astype(np.float32)))
+    d_A = dev(rng.uniform(-1, 1, 32).astype(np.float32))
+    d_dt = dev(mxfp4.f32_to_bf16_bits((0.5 * rng.standard_normal(32)).astype(np.float32)))
+    d_nw = dev(bf16(rng, 4096))
+    hidden = dev(np.stack([_fused_setup(rng) for _ in range(tokens)]))
+    state0 = (rng.standard_normal(nq * 3)).astype(np.float32)
+
+    def segs(o, conv):
+        return [dict(packed=P[0], out=o[0], rows=nq, epilogue="conv_silu", conv_state=conv, conv_w=d_cw),
+                dict(packed=P[1], out=o[1], rows=64, epilogue="store"),
+                dict(packed=P[2], out=o[2], rows=32, epilogue="decay", A_log=d_A, dt_bias=d_dt),
+                dict(packed=P[3], out=o[3], rows=32, epilogue="beta")]
+
+    rows = (nq, 64, 32, 32)
+    together = [torch.zeros(tokens, r, device="cuda") for r in rows]
+    conv_a = dev(state0.copy())
+    ops.gemv_fused(hidden, segs(together, conv_a), prologue="rmsnorm", norm_w=d_nw, cols=4096, tokens=tokens)
+    conv_b = dev(state0.copy())
+    for m in range(tokens):
+        single = [torch.zeros(r, device="cuda") for r in rows]
+        ops.gemv_fused(hidden[m], segs(single, conv_b), prologue="rmsnorm", norm_w=d_nw)
+        for o, t in zip(single, together):
+            assert np.array_equal(host(o), host(t[m])), m
+    assert np.array_equal(host(conv_a), host(conv_b))
+    # residual and SwiGLU rows, gated prologue with a per-token operand
+    wg, sg = rand_matrix(rng, 256, 4096)
+    wu, su = rand_matrix(rng, 256, 4096)
+    pg, pu = ops.repack(dev(wg), dev(sg)), ops.repack(dev(wu), dev(su))
+    z = dev(rng.standard_normal((tokens, 4096)).astype(np.float32))
+    gw = dev(bf16(rng, 128))
+    res0 = rng.standard_normal((tokens, 256)).astype(np.float32)
+    act_t, res_t = torch.zeros(tokens, 256, device="cuda"), dev(res0.copy())
+    ops.gemv_fused(hidden, [dict(packed=pg, packed2=pu, out=act_t, rows=256, epilogue="swiglu")], prologue="gated_rmsnorm", aux=z,
+                   norm_w=gw, cols=4096, tokens=tokens)
+    ops.gemv_fused(hidden, [dict(packed=pg, out=res_t, rows=256, epilogue="residual")], cols=4096, tokens=tokens)
+    for m in range(tokens):
+        act_1, res_1 = torch.zeros(256, device="cuda"), dev(res0[m].copy())
+        ops.gemv_fused(hidden[m], [dict(packed=pg, packed2=pu, out=act_1, rows=256, epilogue="swiglu")], prologue="gated_rmsnorm",
+                       aux=z[m], norm_w=gw)
+        ops.gemv_fused(hidden[m], [dict(packed=pg, out=res_1, rows=256, epilogue="residual")])
+        assert np.array_equal(host(act_1), host(act_t[m])) and np.array_equal(host(res_1), host(res_t[m])), m

@@ -130,6 +130,37 @@ def test_prepared_inputs_on_and_off_agree(cuda, golden_ckpt):
         assert np.max(np.abs(a.read("hidden") - b.read("hidden"))) <= 1e-4 * np.abs(b.read("hidden")).max()
 
 
+@pytest.mark.parametrize("count", [1, 2, 7, 13])
+def test_forward_tokens_equals_token_loop(cuda, golden_ckpt, count):
+    """Prompt processing four tokens per pass over the weights: the same state as forward_token in a loop (bit for bit
+    without prepared inputs, which only the one-token path uses; within rounding of the default path), the same
+    arg-max, and decoding continues identically afterwards."""
+    prompt = [42, 7, 63, 0, 21, 5, 33, 60, 11, 12, 1, 2, 3][:count]
+    with small_engine(golden_ckpt[1], prepared_inputs=False) as a, small_engine(golden_ckpt[1], prepared_inputs=False) as b, \
+            small_engine(golden_ckpt[1]) as c:
+        a.forward_tokens(prompt)
+        for t in prompt:
+            b.forward_token(t)
+            c.forward_token(t)
+        assert a.position == b.position == count
+        for field, n in (("hidden", 4096), ("delta_state", 3 * 32 * 128 * 128), ("conv_state", 3 * 8192 * 3), ("kv_keys", count * 1024),
+                         ("kv_values", count * 1024)):
+            assert np.array_equal(a.read(field, n), b.read(field, n)), field
+        assert np.max(np.abs(a.read("hidden") - c.read("hidden"))) <= 1e-4 * np.abs(c.read("hidden")).max()
+        ta, tb = a.logits_argmax(), b.logits_argmax()
+        assert ta == tb == c.logits_argmax()
+        assert np.array_equal(a.read("logits", 64), b.read("logits", 64))
+        for _ in range(5):  # decoding goes on from the prompt's state
+            ta, tb = a.decode_token(ta), b.decode_token(tb)
+            assert ta == tb
+        assert np.array_equal(a.read("hidden"), b.read("hidden"))
+    with small_engine(golden_ckpt[1], max_context=8) as e:
+        with pytest.raises(Exception, match="KV cache full"):
+            e.forward_tokens(list(range(9)))
+        with pytest.raises(Exception, match="token out of range"):
+            e.forward_tokens([1, 248320])
+
+
 def test_kv_bf16_and_accurate_trig_modes(cuda, golden_ckpt):
     from insignia_b200.checkpoint_io import SafetensorsReader
 
