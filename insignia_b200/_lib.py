@@ -61,6 +61,7 @@ SIGNATURES = {
     "insg_gemv_argmax_scratch_bytes": (sz, []),
     "insg_gemv_fused": (i32, [C.POINTER(GemvOp), vp]),
     "insg_deltanet_decode": (i32, [vp] * 7 + [i32, vp]),
+    "insg_deltanet_decode_tokens": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "insg_gqa_scratch_bytes": (sz, [i32]),
     "insg_gqa_decode": (i32, [vp, vp, vp, vp, i32, i32, vp, sz, vp]),
     "insg_gqa_decode_noalloc": (i32, [vp, vp, vp, vp, i32, i32, vp]),

@@ -25,10 +25,12 @@ namespace insg {
 constexpr int kDnThreads = 256;
 constexpr int kSlices = 4; // 32 columns each
 
+// `tokens` consecutive steps of the sequence in one launch: the slice stays in registers from step to step and is
+// written back once; q/k/v of step m are at + m * qkv_stride, g/beta at + m * 32, the output at + m * 4096.
 __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__restrict__ state, const float *__restrict__ q16,
                                                                    const float *__restrict__ k16, const float *__restrict__ v32,
                                                                    const float *__restrict__ g32, const float *__restrict__ beta32,
-                                                                   float *__restrict__ out32)
+                                                                   float *__restrict__ out32, int tokens, int qkv_stride)
 {
     __shared__ __align__(16) float s_qk[8][2][128]; // per warp: its own copy of the normalised q and k (no block barrier)
     __shared__ __align__(16) float s_part[2][8][32]; // per-warp partial sums over k: [0] memory read-out, [1] output
@@ -47,81 +49,84 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
 
     pdl_wait();
 
-    // Every dependent input is requested at once.  Each warp reads the whole q and k of the key head (four values per
-    // lane) and normalises them itself: L2 norms over 128 with eps added to the sum, as the reference.
-    const float4 q4 = __ldcg(reinterpret_cast<const float4 *>(q16 + kh * 128) + lane);
-    const float4 k4 = __ldcg(reinterpret_cast<const float4 *>(k16 + kh * 128) + lane);
-    const float4 v4 = __ldcg(reinterpret_cast<const float4 *>(v32 + head * 128 + slice * 32) + vq); // this thread's columns
-    const float g_in = __ldcg(g32 + head), beta = __ldcg(beta32 + head);
-    const float qn = warp_sum(fmaf(q4.x, q4.x, fmaf(q4.y, q4.y, fmaf(q4.z, q4.z, q4.w * q4.w))));
-    const float kn = warp_sum(fmaf(k4.x, k4.x, fmaf(k4.y, k4.y, fmaf(k4.z, k4.z, k4.w * k4.w))));
-    const float qs = rsqrtf(qn + 1e-6f) * 0.08838834764831845f, ks = rsqrtf(kn + 1e-6f);
-    reinterpret_cast<float4 *>(s_qk[warp][0])[lane] = make_float4(q4.x * qs, q4.y * qs, q4.z * qs, q4.w * qs);
-    reinterpret_cast<float4 *>(s_qk[warp][1])[lane] = make_float4(k4.x * ks, k4.y * ks, k4.z * ks, k4.w * ks);
-    __syncwarp();
-    float qq[4], kk[4];
+    for (int step = 0; step < tokens; step++, q16 += qkv_stride, k16 += qkv_stride, v32 += qkv_stride, g32 += 32, beta32 += 32, out32 += 4096) {
+        __syncwarp(); // the previous step's reads of this warp's q/k copy are done
+        // Every dependent input is requested at once.  Each warp reads the whole q and k of the key head (four values per
+        // lane) and normalises them itself: L2 norms over 128 with eps added to the sum, as the reference.
+        const float4 q4 = __ldcg(reinterpret_cast<const float4 *>(q16 + kh * 128) + lane);
+        const float4 k4 = __ldcg(reinterpret_cast<const float4 *>(k16 + kh * 128) + lane);
+        const float4 v4 = __ldcg(reinterpret_cast<const float4 *>(v32 + head * 128 + slice * 32) + vq); // this thread's columns
+        const float g_in = __ldcg(g32 + head), beta = __ldcg(beta32 + head);
+        const float qn = warp_sum(fmaf(q4.x, q4.x, fmaf(q4.y, q4.y, fmaf(q4.z, q4.z, q4.w * q4.w))));
+        const float kn = warp_sum(fmaf(k4.x, k4.x, fmaf(k4.y, k4.y, fmaf(k4.z, k4.z, k4.w * k4.w))));
+        const float qs = rsqrtf(qn + 1e-6f) * 0.08838834764831845f, ks = rsqrtf(kn + 1e-6f);
+        reinterpret_cast<float4 *>(s_qk[warp][0])[lane] = make_float4(q4.x * qs, q4.y * qs, q4.z * qs, q4.w * qs);
+        reinterpret_cast<float4 *>(s_qk[warp][1])[lane] = make_float4(k4.x * ks, k4.y * ks, k4.z * ks, k4.w * ks);
+        __syncwarp();
+        float qq[4], kk[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        qq[j] = s_qk[warp][0][kr + 32 * j];
-        kk[j] = s_qk[warp][1][kr + 32 * j];
-    }
-    const float decay = expf(g_in);
+        for (int j = 0; j < 4; j++) {
+            qq[j] = s_qk[warp][0][kr + 32 * j];
+            kk[j] = s_qk[warp][1][kr + 32 * j];
+        }
+        const float decay = expf(g_in);
 
-    // mem_v = sum_i (S*d) * k
-    float4 pm = make_float4(0.f, 0.f, 0.f, 0.f);
+        // mem_v = sum_i (S*d) * k
+        float4 pm = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        pm.x = fmaf(cell[j].x * decay, kk[j], pm.x);
-        pm.y = fmaf(cell[j].y * decay, kk[j], pm.y);
-        pm.z = fmaf(cell[j].z * decay, kk[j], pm.z);
-        pm.w = fmaf(cell[j].w * decay, kk[j], pm.w);
-    }
-    // a warp holds 4 k-rows (lane>>3) x 8 column groups: fold the rows, then every thread folds the 8 warps itself
+        for (int j = 0; j < 4; j++) {
+            pm.x = fmaf(cell[j].x * decay, kk[j], pm.x);
+            pm.y = fmaf(cell[j].y * decay, kk[j], pm.y);
+            pm.z = fmaf(cell[j].z * decay, kk[j], pm.z);
+            pm.w = fmaf(cell[j].w * decay, kk[j], pm.w);
+        }
+        // a warp holds 4 k-rows (lane>>3) x 8 column groups: fold the rows, then every thread folds the 8 warps itself
 #pragma unroll
-    for (int m = 8; m <= 16; m <<= 1) {
-        pm.x += __shfl_xor_sync(0xffffffffu, pm.x, m);
-        pm.y += __shfl_xor_sync(0xffffffffu, pm.y, m);
-        pm.z += __shfl_xor_sync(0xffffffffu, pm.z, m);
-        pm.w += __shfl_xor_sync(0xffffffffu, pm.w, m);
-    }
-    if (lane < 8) *reinterpret_cast<float4 *>(&s_part[0][warp][lane * 4]) = pm;
-    __syncthreads();
-    float4 mem = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int m = 8; m <= 16; m <<= 1) {
+            pm.x += __shfl_xor_sync(0xffffffffu, pm.x, m);
+            pm.y += __shfl_xor_sync(0xffffffffu, pm.y, m);
+            pm.z += __shfl_xor_sync(0xffffffffu, pm.z, m);
+            pm.w += __shfl_xor_sync(0xffffffffu, pm.w, m);
+        }
+        if (lane < 8) *reinterpret_cast<float4 *>(&s_part[0][warp][lane * 4]) = pm;
+        __syncthreads();
+        float4 mem = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int w = 0; w < 8; w++) {
-        const float4 t = *reinterpret_cast<const float4 *>(&s_part[0][w][vq * 4]);
-        mem.x += t.x; mem.y += t.y; mem.z += t.z; mem.w += t.w;
-    }
-    const float4 dl = make_float4((v4.x - mem.x) * beta, (v4.y - mem.y) * beta, (v4.z - mem.z) * beta, (v4.w - mem.w) * beta);
+        for (int w = 0; w < 8; w++) {
+            const float4 t = *reinterpret_cast<const float4 *>(&s_part[0][w][vq * 4]);
+            mem.x += t.x; mem.y += t.y; mem.z += t.z; mem.w += t.w;
+        }
+        const float4 dl = make_float4((v4.x - mem.x) * beta, (v4.y - mem.y) * beta, (v4.z - mem.z) * beta, (v4.w - mem.w) * beta);
 
-    // S = S*d + k*delta ; out_v = sum_i S * q
-    float4 po = make_float4(0.f, 0.f, 0.f, 0.f);
+        // S = S*d + k*delta ; out_v = sum_i S * q
+        float4 po = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        cell[j].x = fmaf(cell[j].x, decay, kk[j] * dl.x);
-        cell[j].y = fmaf(cell[j].y, decay, kk[j] * dl.y);
-        cell[j].z = fmaf(cell[j].z, decay, kk[j] * dl.z);
-        cell[j].w = fmaf(cell[j].w, decay, kk[j] * dl.w);
-        po.x = fmaf(cell[j].x, qq[j], po.x);
-        po.y = fmaf(cell[j].y, qq[j], po.y);
-        po.z = fmaf(cell[j].z, qq[j], po.z);
-        po.w = fmaf(cell[j].w, qq[j], po.w);
-        *reinterpret_cast<float4 *>(S + size_t(kr + 32 * j) * 128 + v0) = cell[j];
-    }
+        for (int j = 0; j < 4; j++) {
+            cell[j].x = fmaf(cell[j].x, decay, kk[j] * dl.x);
+            cell[j].y = fmaf(cell[j].y, decay, kk[j] * dl.y);
+            cell[j].z = fmaf(cell[j].z, decay, kk[j] * dl.z);
+            cell[j].w = fmaf(cell[j].w, decay, kk[j] * dl.w);
+            po.x = fmaf(cell[j].x, qq[j], po.x);
+            po.y = fmaf(cell[j].y, qq[j], po.y);
+            po.z = fmaf(cell[j].z, qq[j], po.z);
+            po.w = fmaf(cell[j].w, qq[j], po.w);
+            if (step == tokens - 1) *reinterpret_cast<float4 *>(S + size_t(kr + 32 * j) * 128 + v0) = cell[j];
+        }
 #pragma unroll
-    for (int m = 8; m <= 16; m <<= 1) {
-        po.x += __shfl_xor_sync(0xffffffffu, po.x, m);
-        po.y += __shfl_xor_sync(0xffffffffu, po.y, m);
-        po.z += __shfl_xor_sync(0xffffffffu, po.z, m);
-        po.w += __shfl_xor_sync(0xffffffffu, po.w, m);
-    }
-    if (lane < 8) *reinterpret_cast<float4 *>(&s_part[1][warp][lane * 4]) = po;
-    __syncthreads();
-    if (tid < 32) {
-        float o = 0.f;
+        for (int m = 8; m <= 16; m <<= 1) {
+            po.x += __shfl_xor_sync(0xffffffffu, po.x, m);
+            po.y += __shfl_xor_sync(0xffffffffu, po.y, m);
+            po.z += __shfl_xor_sync(0xffffffffu, po.z, m);
+            po.w += __shfl_xor_sync(0xffffffffu, po.w, m);
+        }
+        if (lane < 8) *reinterpret_cast<float4 *>(&s_part[1][warp][lane * 4]) = po;
+        __syncthreads();
+        if (tid < 32) {
+            float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; w++) o += s_part[1][w][tid];
-        out32[head * 128 + slice * 32 + tid] = o;
+            for (int w = 0; w < 8; w++) o += s_part[1][w][tid];
+            out32[head * 128 + slice * 32 + tid] = o;
+        }
     }
 }
 
@@ -134,5 +139,15 @@ extern "C" int insg_deltanet_decode(float *state, const float *q16, const float 
 {
     if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
     return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
-                  beta32, out32);
+                  beta32, out32, 1, 0);
+}
+
+extern "C" int insg_deltanet_decode_tokens(float *state, const float *q16, const float *k16, const float *v32, const float *g32,
+                                           const float *beta32, float *out32, int tokens, int qkv_stride, int pdl,
+                                           insg_stream_t stream)
+{
+    if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
+    if (tokens < 1 || tokens > 64 || qkv_stride < 0) return fail(INSG_E_SHAPE, "deltanet: 1..64 tokens per launch");
+    return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
+                  beta32, out32, tokens, qkv_stride);
 }

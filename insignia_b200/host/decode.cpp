@@ -496,14 +496,11 @@ void delta_block_multi(Ctx &c, const Qwen35Decode::Plan::Block &b, int di, const
     in.seg[3] = seg(b.b, u.b, INSG_EPI_BETA);
     run_gemv(c, in);
 
-    for (int m = 0; m < u.T; m++) {
-        const float *q = u.qkv + size_t(m) * 8192;
-        // no dependent-launch overlap here: the kernel fetches its state before the dependency wait, which is only safe
-        // when the state was not written by the launch right before it (in decoding it was written a token ago)
-        insg_check(insg_deltanet_decode(x.delta_state + size_t(di) * 32 * 128 * 128, q, q + 2048, q + 4096, u.a + m * 32, u.b + m * 32,
-                                        u.core + size_t(m) * 4096, /*pdl*/ 0, c.st));
-        c.launches++;
-    }
+    // all T steps in one launch: the state stays on chip between them.  No dependent-launch overlap: the kernel fetches
+    // its state before the dependency wait, which is safe because the launch before it (the GEMV) does not write state.
+    insg_check(insg_deltanet_decode_tokens(x.delta_state + size_t(di) * 32 * 128 * 128, u.qkv, u.qkv + 2048, u.qkv + 4096, u.a, u.b, u.core,
+                                           u.T, 8192, c.pdl ? 1 : 0, c.st));
+    c.launches++;
 
     insg_gemv_op out = {};
     out.in = u.core;

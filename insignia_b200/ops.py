@@ -125,6 +125,14 @@ def deltanet_decode(state, q16, k16, v32, g32, beta32, pdl=False):
     return out
 
 
+def deltanet_decode_tokens(state, q16, k16, v32, g32, beta32, tokens, qkv_stride, pdl=False):
+    """``tokens`` consecutive DeltaNet steps in one launch; inputs of step m at + m * qkv_stride (q, k, v) and + m * 32 (g, beta)."""
+    out = torch.empty(tokens * 32 * 128, dtype=torch.float32, device=state.device)
+    check(_lib.lib().insg_deltanet_decode_tokens(_p(state), _p(q16), _p(k16), _p(v32), _p(g32), _p(beta32), _p(out), tokens,
+                                                 qkv_stride, int(pdl), _stream()))
+    return out.reshape(tokens, 32 * 128)
+
+
 def gqa_scratch(device, tokens=0):
     return torch.zeros(_lib.lib().insg_gqa_scratch_bytes(tokens), dtype=torch.uint8, device=device)
 

@@ -662,3 +662,24 @@ def test_gemv_fused_consecutive_tokens_equal_single_token_launches(cuda, tokens)
                        aux=z[m], norm_w=gw)
         ops.gemv_fused(hidden[m], [dict(packed=pg, out=res_1, rows=256, epilogue="residual")])
         assert np.array_equal(host(act_1), host(act_t[m])) and np.array_equal(host(res_1), host(res_t[m])), m
+
+
+def test_deltanet_several_steps_in_one_launch(cuda):
+    """Four consecutive steps in one launch (state kept on chip) equal four launches, bit for bit."""
+    from insignia_b200 import ops
+
+    rng = np.random.default_rng(51)
+    T = 4
+    state0 = (rng.standard_normal(32 * 128 * 128) * 0.05).astype(np.float32)
+    qkv = rng.standard_normal((T, 8192)).astype(np.float32)
+    g = -rng.uniform(0.01, 1, (T, 32)).astype(np.float32)
+    b = rng.uniform(0, 1, (T, 32)).astype(np.float32)
+    d_qkv, d_g, d_b = dev(qkv), dev(g), dev(b)
+    sa = dev(state0.copy())
+    flat = d_qkv.reshape(-1)  # step m's q, k, v start at m * 8192 + {0, 2048, 4096}
+    together = host(ops.deltanet_decode_tokens(sa, flat, flat[2048:], flat[4096:], d_g, d_b, T, 8192))
+    sb = dev(state0.copy())
+    for m in range(T):
+        one = host(ops.deltanet_decode(sb, d_qkv[m, :2048], d_qkv[m, 2048:4096], d_qkv[m, 4096:], d_g[m], d_b[m]))
+        assert np.array_equal(one, together[m]), m
+    assert np.array_equal(host(sa), host(sb))
