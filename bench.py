@@ -65,6 +65,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gemv", default="mma", choices=["mma", "tcgen05"], help="GEMV kernel family of the engine")
     ap.add_argument("--tune", action="append", default=[], help="kernel tuning knob key=value (insg_tune_set)")
+    ap.add_argument("--launch-per-op", action="store_true", help="one launch per fused operation (CUDA graph) instead of the persistent token kernel")
+    ap.add_argument("--prefetch", type=int, default=-1, help="persistent kernel: weight records per warp kept prefetched into L2 (-1 = default)")
     return ap.parse_args()
 
 
@@ -176,13 +178,16 @@ def run_native(args, rank, world, local_rank):
     st, idx = ensure_checkpoint(args.seed, True)
 
     K, W = args.steps, args.warmup
-    ctx = args.prompt + W + 2 * K + 8
+    ctx = args.prompt + W + 2 * K + 32
     from insignia_b200 import ops
 
     for kv in args.tune:
         k, v = kv.split("=")
         ops.tune(k, int(v))
-    eng = Engine(idx, max_context=ctx, budget_bytes=16 << 30, kv_bf16=args.kv_bf16, device=local_rank, gemv_tcgen05=args.gemv == "tcgen05")
+    eng = Engine(idx, max_context=ctx, budget_bytes=16 << 30, kv_bf16=args.kv_bf16, device=local_rank, gemv_tcgen05=args.gemv == "tcgen05",
+                 launch_per_op=args.launch_per_op)
+    if args.prefetch >= 0:
+        eng.set_prefetch_records(args.prefetch)
     rng = np.random.default_rng(args.seed + 1000 * rank)
     prompt = rng.integers(0, VOCAB, args.prompt)
     stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
@@ -228,7 +233,6 @@ def run_native(args, rank, world, local_rank):
 
         ms_e2e, tok = timed(e2e_loop)
     final_ctx = eng.position
-    prof = eng.profile_token(tok)
     # the dominant kernel in its own flow: the token's fused-GEMV launches alone, replayed as a graph between two events
     chain = eng.profile_gemv_chain(replays=8)
     gemv = {"bytes": chain["bytes"], "ms": chain["ms_per_token"], "launches": chain["launches"]}
@@ -257,8 +261,7 @@ def run_native(args, rank, world, local_rank):
                      "bytes_per_launch": gemv["bytes"] / gemv["launches"], "us_per_launch": gemv["ms"] * 1e3 / gemv["launches"],
                      "launches_per_token": gemv["launches"],
                      "timing": "CUDA events around 8 replays of a graph holding only this kernel's launches of one token "
-                               "(dependent-launch overlap on, weights exceed L2)",
-                     "eager_event_pairs_us_per_token": {k: v["ms"] * 1e3 for k, v in prof.items()}},
+                               "(dependent-launch overlap on, weights exceed L2)"},
         "clocks": clocks.summary(),
         "prefill": {"value": world * max(0, args.prompt - 8) / (prefill_ms * 1e-3) if args.prompt > 8 else None, "unit": "tok/s",
                     "tokens": max(0, args.prompt - 8), "how": "forward_tokens: four prompt tokens per pass over the weights, "

@@ -38,9 +38,8 @@ enum {
 
 INSG_API const char *insg_last_error(void);  /* host string, thread-local */
 INSG_API int insg_version(void);
-/* Kernel tuning knobs, process-wide, for benchmarking: "gemv_unr" (2|4 records per register prefetch chunk), "gemv_ring"
- * (0 = register prefetch, 2..4 = shared-memory ring of that many stages per warp), "gemv_ctas_per_sm" (1|2, ring only),
- * "umma_stages" / "umma_nacc" / "umma_prefetch" (tcgen05 kernel). */
+/* Tuning knobs of the optional tcgen05 GEMV kernel, process-wide, for benchmarking only: "umma_stages",
+ * "umma_nacc", "umma_prefetch".  The default path has no process-wide knobs. */
 INSG_API int insg_tune_set(const char *key /* host */, int value);
 
 /* ------------------------------------------------------------------ MXFP4 */
@@ -183,15 +182,14 @@ typedef struct insg_gemv_op {
     /* INSG_EPI_LOGITS only: partial arg-max scratch (>= insg_gemv_argmax_scratch_bytes(), its
      * first 64 bytes zero before the first call and left zero by every call).  The winning row
      * is written to *token_out and, when non-NULL, to *token_feedback and to
-     * token_log[*position_inout]; then *position_inout is incremented (when non-NULL). */
+     * token_log[*position_inout] (only while 0 <= *position_inout < token_log_capacity); then
+     * *position_inout is incremented (when non-NULL). */
     void *argmax_scratch;
     int *token_out;
     int *token_feedback;
     int *token_log;
+    int token_log_capacity;   /* entries of token_log; required (> 0) when token_log is given */
     int *position_inout;
-    /* Optional profiling aid: [grid][8] u64 nanosecond timestamps written by each CTA at its phase boundaries
-     * (start, loads issued, dependency met, prologue done, streaming done, CTA barrier, combine done), or NULL. */
-    void *trace;
     int layout;               /* weight layout of every segment: 0 = insg_mxfp4_repack records, 1 = insg_mxfp4_repack_umma   */
     int *error_flag;          /* set to 1 if a bounded wait inside the kernel ran out (device int), or NULL                 */
     int pdl;                  /* 1: launch with programmatic dependent launch          */
@@ -205,6 +203,49 @@ typedef struct insg_gemv_op {
 
 INSG_API size_t insg_gemv_argmax_scratch_bytes(void);
 INSG_API int insg_gemv_fused(const insg_gemv_op *op /* host */, insg_stream_t stream);
+
+/* ------------------------------------------------- persistent token program */
+/* A program is a recorded sequence of the fused operations above (GEMV, DeltaNet step, attention step, embedding
+ * lookup) that ONE cooperative launch of one CTA per SM executes back to back, with a grid-wide barrier between
+ * operations instead of a kernel boundary: the 162 dependent launches of a token step become one.  The GEMV phases
+ * split and sum exactly as insg_gemv_fused does (bit-identical results).  While the SMs sit in barriers and in the
+ * small recurrent phases, every warp keeps prefetching the weight records it will need next into L2.
+ * No reference counterpart: the reference launches every kernel separately (src/decode.cu:14-23).
+ *
+ * insg_program_create / _finalize allocate (host memory, then two small device buffers); _run allocates nothing and
+ * does not synchronise.  A program is bound to the device that was current at create.  The operations' pointers are
+ * baked in, as in a captured graph.  One run at a time per program (runs share the barrier state). */
+struct insg_attn_op;
+typedef struct insg_program insg_program;
+INSG_API insg_program *insg_program_create(void);
+INSG_API void insg_program_destroy(insg_program *prog);
+/* Append one operation.  The op structs have the meaning they have for insg_gemv_fused / insg_attention_step
+ * (pdl, layout and error_flag are ignored; one token per GEMV). */
+INSG_API int insg_program_add_gemv(insg_program *prog, const insg_gemv_op *op /* host */);
+INSG_API int insg_program_add_deltanet(insg_program *prog, float *state, const float *q16, const float *k16, const float *v32,
+                                       const float *g32, const float *beta32, float *out32);
+INSG_API int insg_program_add_attention(insg_program *prog, const struct insg_attn_op *op /* host */);
+INSG_API int insg_program_add_embed(insg_program *prog, const uint32_t *weight, const uint8_t *scales, float *out,
+                                    const int *device_row, int rows, int cols);
+/* Uploads the program; no operation can be added afterwards. */
+INSG_API int insg_program_finalize(insg_program *prog);
+/* Options: "prefetch_records" = how many 1088-byte weight records each warp keeps prefetched into L2 ahead of its own
+ * consumption (0 = off, default 24); "timeout_ns" = how long a barrier waits before it gives up (default 2 s). */
+INSG_API int insg_program_set_option(insg_program *prog, const char *key /* host */, long long value);
+/* Runs the program n_tokens times in one launch (the arg-max feedback of a LOGITS epilogue links consecutive tokens).
+ * token / position >= 0 are first stored to *device_token / *device_position by the kernel itself (pass -1 to leave
+ * them).  If a barrier wait runs out, *error_flag (device int, may be NULL) is set to 1, every CTA leaves the kernel and
+ * the results are undefined; call insg_program_recover before the next run. */
+INSG_API int insg_program_run(insg_program *prog, int n_tokens, int token, int position, int *device_token,
+                              int *device_position, int *error_flag, insg_stream_t stream);
+INSG_API int insg_program_recover(insg_program *prog, insg_stream_t stream);
+/* Failure-detection self-test: runs the program once with every barrier waiting for one CTA more than exists and the
+ * given (short, <= 100 ms) timeout, so the first wait runs out: *error_flag becomes 1 and the kernel returns.  Needs a
+ * program of at least two operations.  Call insg_program_recover afterwards. */
+INSG_API int insg_program_selftest_barrier_timeout(insg_program *prog, unsigned long long timeout_ns, int *error_flag,
+                                                   insg_stream_t stream);
+INSG_API int insg_program_phase_count(const insg_program *prog);
+INSG_API uint64_t insg_program_weight_bytes(const insg_program *prog);
 
 /* ------------------------------------------------------------ DeltaNet */
 
@@ -248,8 +289,9 @@ INSG_API int insg_gqa_decode(const float *q, const void *k_cache, const void *v_
  * (about 600 KB per GPU that loads the library, kept until the process exits), so there is no
  * scratch argument.  Limits and rules: at most 262144 cached tokens (INSG_E_LIMIT beyond);
  * every call on a device shares that one array, so two calls that overlap on the GPU (different
- * streams, or different threads) race -- serialise them; the first call on each device looks the
- * array's address up and should therefore be made before any stream capture begins.  Calls no
+ * streams, or different threads) race -- serialise them; every call looks the array's address up
+ * (cudaGetSymbolAddress, which allocates nothing), and the first such lookup on a device may load
+ * the library's code there, so make the first call before any stream capture begins.  Calls no
  * cudaMalloc / cudaFree or other allocating routine.  No counterpart in the reference, whose
  * gqa_decode keeps its scores in dynamic shared memory (src/attention.cu:4-5). */
 INSG_API int insg_gqa_decode_noalloc(const float *q, const void *k_cache, const void *v_cache, float *out, int tokens,
@@ -318,6 +360,31 @@ INSG_API int insg_argmax_logits(const float *logits, int n, int *device_token, i
 INSG_API int insg_bf16_gemv(const uint16_t *w, const float *x, float *y, int rows, int cols, int pdl,
                             insg_stream_t stream);
 
+/* -------------------------------------------------------------- storage */
+/* Handle-based face of ModelFile + TieredStorage (include/insignia_model.hpp:20-40, include/insignia_storage.hpp:15-31 of
+ * the reference; behaviour src/storage.cu:5-11): a byte budget of device memory, acquire = make resident + pin,
+ * release = unpin, least-recently-used eviction of unpinned tensors, and the reference's error texts ("tensor not
+ * found: ...", "tensor exceeds device budget", "device budget exhausted by pinned tensors") through insg_last_error().
+ * Additive: background prefetch, the tier a tensor is in (0 mapped file, 1 pinned host memory, 2 device), a pinned-host
+ * cache tier, and reservations that charge other weight memory to the same budget.  host_backend = 1 replaces device
+ * memory by host memory so that the residency logic can run on a machine without a GPU (testing only).
+ * These allocate and may synchronise. */
+typedef struct insg_storage insg_storage;
+INSG_API insg_storage *insg_storage_open(const char *index_path /* host, UTF-8 */, uint64_t device_budget_bytes, int host_backend);
+INSG_API void insg_storage_close(insg_storage *s);
+INSG_API int insg_storage_acquire(insg_storage *s, const char *name, void **data /* out, may be NULL */, uint64_t *bytes /* out */);
+INSG_API int insg_storage_release(insg_storage *s, const char *name);
+INSG_API int insg_storage_prefetch(insg_storage *s, const char *name); /* 1 queued or already there, 0 absent from the file */
+INSG_API int insg_storage_tier(insg_storage *s, const char *name);
+INSG_API int insg_storage_reserve(insg_storage *s, uint64_t bytes);
+INSG_API int insg_storage_unreserve(insg_storage *s, uint64_t bytes);
+INSG_API int insg_storage_set_host_cache(insg_storage *s, uint64_t bytes);
+INSG_API int insg_storage_clear(insg_storage *s);
+INSG_API uint64_t insg_storage_device_bytes(insg_storage *s);
+INSG_API uint64_t insg_storage_reserved_bytes(insg_storage *s);
+/* out6 (host): uploads, uploaded bytes, evictions, hits, pinned-cache hits, prefetch requests */
+INSG_API int insg_storage_stats(insg_storage *s, uint64_t *out6);
+
 /* --------------------------------------------------------------- engine */
 /* Handle-based face of the C++ host classes (ModelFile, Qwen35Weights,
  * DecodeWorkspace, Qwen35Decode: include/insignia_model.hpp, insignia_qwen35.hpp,
@@ -333,12 +400,14 @@ typedef struct insg_engine_options {
                                      (src/qwen_kernels.cu:36); 1: element-wise gate as its NumPy
                                      tools (tools/reference_all_layers.py:13)                   */
     int accurate_trig;            /* 0: fast intrinsics for RoPE as the reference; 1: sincosf   */
-    int use_graph;                /* 1: capture the token step in a CUDA graph                  */
-    int use_pdl;                  /* 1: programmatic dependent launch between kernels           */
+    int use_graph;                /* launch_per_op: 1 = capture the token step in a CUDA graph  */
+    int use_pdl;                  /* launch_per_op: 1 = programmatic dependent launch between kernels */
     int gemv_tcgen05;             /* 1: tcgen05 kind::mxf4 GEMV; 0: mma.sync register-streaming GEMV */
     int n_layers;                 /* 0 = 32                                                     */
     int vocab;                    /* 0 = 248320 (rows of lm_head used for logits)               */
     int device;                   /* CUDA device ordinal                                        */
+    int launch_per_op;            /* 0: a token step is ONE persistent cooperative launch (insg_program_*); 1: one launch per
+                                     fused operation (162 per token), replayed from a CUDA graph when use_graph is set */
     int gemv_unprepared;          /* 0: a GEMV that writes the residual stream or the SwiGLU output leaves the next
                                      GEMV's input prepared (insg_gemv_segment.prep); 1: every GEMV converts its own */
 } insg_engine_options;
@@ -365,20 +434,19 @@ INSG_API int insg_engine_mtp_draft(insg_engine *e, int token);
  * arg-max back in, `count` times; writes the `count` produced ids to out_tokens (host).
  * Synchronises once at the end.  No reference counterpart (its loop is src/generate_ids.cu:4). */
 INSG_API int insg_engine_generate(insg_engine *e, int first_token, int count, int *out_tokens /* host */);
-/* One token step run eagerly with a CUDA-event pair around every launch (no dependent-launch overlap):
- * ms[4], bytes[4], launches[4] (host) receive, per kernel class (0 fused GEMV, 1 DeltaNet step,
- * 2 attention, 3 embedding), the summed durations, the algorithmic bytes and the launch counts.
- * Advances the position like insg_engine_forward_token.  Synchronises.  No reference counterpart. */
-INSG_API int insg_engine_profile_token(insg_engine *e, int token, float *ms, uint64_t *bytes, int *launches);
-/* The fused-GEMV launches of one token step alone, captured as a CUDA graph with dependent-launch overlap and
- * replayed `replays` (1..64) times between two CUDA events: *ms_per_token = time of one replay, *bytes = the
- * algorithmic weight bytes of those launches, *launches = their count.  Needs one forwarded token first.  The
- * sequence state is meaningless afterwards (call insg_engine_reset).  Synchronises.  No reference counterpart. */
+/* The fused-GEMV operations of one token step alone, run `replays` (1..64) times between two CUDA events (one
+ * persistent launch per replay, or with launch_per_op a CUDA graph of launches with dependent-launch overlap):
+ * *ms_per_token = time of one replay, *bytes = the algorithmic weight bytes of those operations, *launches = their
+ * count.  Needs one forwarded token first.  The sequence state is meaningless afterwards (call insg_engine_reset).
+ * Synchronises.  No reference counterpart. */
 INSG_API int insg_engine_profile_gemv_chain(insg_engine *e, int replays, float *ms_per_token, uint64_t *bytes, int *launches);
-/* Profiling aid: every fused-GEMV launch of a token step writes its per-CTA phase timestamps (insg_gemv_op.trace) into
- * device_buffer + launch_index * 296 * 8 * 8 bytes (162 launches fit in 3.1 MB).  Must be set before the first
- * forward_token (the pointers are baked into the captured graph).  NULL disables. */
-INSG_API int insg_engine_set_trace(insg_engine *e, void *device_buffer);
+/* Prefetch distance of the persistent token kernel: 1088-byte weight records each warp keeps requested into L2 ahead
+ * of its own consumption (0 = off, < 0 = the default). */
+INSG_API int insg_engine_set_prefetch_records(insg_engine *e, int records);
+/* Failure-detection self-test of the persistent token kernel: one run whose first grid barrier can never be met, with a
+ * 2 ms wait limit.  Returns 1 when the kernel gave up, raised its error status and the engine recovered; 0 when the
+ * status was not raised; negative on error.  Synchronises; call insg_engine_reset afterwards. */
+INSG_API int insg_engine_selftest_barrier_timeout(insg_engine *e);
 INSG_API int insg_engine_position(insg_engine *e);
 INSG_API int insg_engine_set_position(insg_engine *e, int position);
 /* Re-zeroes the recurrent state and position (what constructing a fresh DecodeWorkspace does). */

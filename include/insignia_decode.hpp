@@ -2,9 +2,10 @@
 //
 // Drop-in for the reference header of the same name (include/insignia_decode.hpp:5-24,
 // behaviour: src/decode.cu:9-69): same classes, public fields, methods and error
-// strings.  Underneath, each layer is five fused sm_100a kernels instead of
-// eighteen launches, chained with programmatic dependent launch and (for
-// forward_token / decode_token / generate) replayed from a CUDA graph.
+// strings.  Underneath, each layer is five fused sm_100a operations instead of
+// eighteen launches; a token step (forward_token / decode_token / generate) is one
+// persistent cooperative launch that walks all of them, or, optionally, 162 launches
+// chained with programmatic dependent launch and replayed from a CUDA graph.
 // Additive members are marked.
 #pragma once
 #include "insignia_qwen35.hpp"
@@ -16,9 +17,9 @@
 #include <string>
 #include <vector>
 
-namespace insignia {
+struct insg_program;
 
-struct StepProfile;
+namespace insignia {
 
 // Additive knobs; the defaults reproduce the reference engine's behaviour.
 struct DecodeOptions {
@@ -26,7 +27,9 @@ struct DecodeOptions {
     bool gate_elementwise = false; // false: head-broadcast attention gate (src/qwen_kernels.cu:36);
                                    // true: element-wise gate (tools/reference_all_layers.py:13)
     bool accurate_trig = false;    // false: __powf/__sinf/__cosf for RoPE (src/ops.cu:9); true: powf/sincosf
-    bool use_graph = true;         // replay the token step from a CUDA graph
+    bool launch_per_op = false;    // false: the token step is one persistent cooperative launch (grid barriers between the
+                                   // fused operations); true: one launch per fused operation
+    bool use_graph = true;         // launch_per_op: replay the token step from a CUDA graph
     bool use_pdl = true;           // programmatic dependent launch between kernels
     bool gemv_tcgen05 = false;     // true: weights through tcgen05.mma kind::mxf4 (TMA-fed); false: the mma.sync streaming kernel
     bool prepared_inputs = true;   // a GEMV that writes the residual stream or the SwiGLU output also leaves the next GEMV's
@@ -62,8 +65,6 @@ public:
     void *argmax_scratch{};
     float *multi{};      // device: activations of up to four consecutive tokens (forward_tokens)
     void *prep{};        // device: prepared GEMV inputs, fp16 [2][4096] + fp16 [2][12288] + fp32 [2][296] sums of squares
-    void *trace{};       // optional profiling buffer: [GEMV launch of the step][296 CTAs][8] u64 timestamps (see insg_gemv_op.trace)
-    int trace_index{};   // GEMV launches enqueued since the step began
     void reset(); // zero recurrent state and position, as a fresh workspace
 
 private:
@@ -89,14 +90,17 @@ public:
     std::vector<int> generate(int first_token, int count);
     uint64_t launch_count() const noexcept { return launches_; }
     cudaStream_t execution_stream();
-    // Additive: one token step run eagerly with an event pair around every launch.  Index 0: fused GEMV,
-    // 1: DeltaNet step, 2: attention, 3: embedding.  ms = summed durations, bytes = algorithmic bytes moved.
-    void profile_token(int token, float ms[4], uint64_t bytes[4], int launches[4]);
-    // Additive: the fused-GEMV launches of one token step alone (no DeltaNet, attention or embedding kernels between
-    // them), captured as a graph with dependent-launch overlap and replayed `replays` times between two events.
-    // Gives the average in-flow duration of the dominant kernel.  The sequence state (hidden, convolution history)
-    // is meaningless afterwards: reset the workspace before decoding again.
+    // Additive: the fused-GEMV operations of one token step alone (no DeltaNet, attention or embedding work between
+    // them), run `replays` times between two events: as one persistent launch each, or with launch_per_op as a graph
+    // of launches with dependent-launch overlap.  Gives the weight-streaming time of a token.  The sequence state
+    // (hidden, convolution history) is meaningless afterwards: reset the workspace before decoding again.
     void profile_gemv_chain(int replays, float *ms_per_token, uint64_t *bytes, int *launches);
+    // Additive: the persistent program's prefetch distance (records per warp, 0 = off); takes effect at once.
+    void set_prefetch_records(int records);
+    // Additive: failure-detection self-test of the persistent launch: one run whose first grid barrier can never be
+    // met, with a short wait limit.  Returns true when the kernel gave up, raised its error status and the engine
+    // recovered.  The sequence state is meaningless afterwards (reset the workspace).
+    bool selftest_barrier_timeout();
     struct Plan; // resolved weight pointers + captured graph (opaque)
 
 private:
@@ -107,6 +111,7 @@ private:
     // this block's output next (the block then leaves that input prepared), or null when the caller may touch hidden
     void load_embed();
     void load_block(int layer);
+    void prefetch_block(int layer);
     void load_head();
     void enqueue_delta(int layer, bool hidden_prepared = false, const uint16_t *next_norm = nullptr);
     void enqueue_attention(int layer, bool hidden_prepared = false, const uint16_t *next_norm = nullptr);
@@ -116,8 +121,14 @@ private:
     Qwen35Weights &w_;
     DecodeWorkspace &x_;
     std::unique_ptr<Plan> plan_;
+    void build_program();
+    void run_program(int n_tokens, int token);
+    void recover_after_timeout();
+    bool persistent() const;
     uint64_t launches_{};
-    StepProfile *prof_{};
+    bool gemv_only_{};            // enqueue only the fused GEMVs (profile_gemv_chain)
+    insg_program *rec_{};         // non-null while a program is being recorded
+    uint64_t *gemv_bytes_{};      // optional byte counter of the GEMVs enqueued
     bool fused_token_valid_{};
 };
 

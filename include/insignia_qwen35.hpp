@@ -26,7 +26,8 @@ struct QuantMatrix {
     int rows{}, cols{};
 };
 
-// Tile-interleaved copy (see insg_mxfp4_repack); owned by Qwen35Weights, lives until it is destroyed.
+// Tile-interleaved copy (see insg_mxfp4_repack); owned by Qwen35Weights, lives until it is destroyed; its bytes are
+// charged to the storage budget (TieredStorage::reserve).
 struct PackedMatrix {
     const void *data{};
     int rows{}, cols{};
@@ -48,6 +49,8 @@ public:
     // Additive: packed copy of matrix `base` for the fused GEMV kernels (built on first call).
     PackedMatrix packed(const std::string &base, int layout = 0);
     uint64_t packed_bytes() const noexcept { return packed_bytes_; }
+    // Additive: starts the upload of a matrix' checkpoint-layout tensors in the background (see TieredStorage::prefetch).
+    void prefetch(const std::string &base);
 
 private:
     TieredStorage storage_;

@@ -24,7 +24,7 @@ class GemvSegment(C.Structure):
 class GemvOp(C.Structure):
     _fields_ = [("in_", vp), ("aux", vp), ("norm_w", vp), ("x_out", vp), ("cols", i32), ("prologue", i32),
                 ("n_segments", i32), ("seg", GemvSegment * 4), ("argmax_scratch", vp), ("token_out", vp),
-                ("token_feedback", vp), ("token_log", vp), ("position_inout", vp), ("trace", vp), ("layout", i32), ("error_flag", vp), ("pdl", i32),
+                ("token_feedback", vp), ("token_log", vp), ("token_log_capacity", i32), ("position_inout", vp), ("layout", i32), ("error_flag", vp), ("pdl", i32),
                 ("prep_partials", vp), ("prep_rms", i32), ("tokens", i32)]
 
 
@@ -37,7 +37,7 @@ class AttnOp(C.Structure):
 class EngineOptions(C.Structure):
     _fields_ = [("device_budget_bytes", u64), ("max_context", i32), ("kv_dtype", i32), ("gate_elementwise", i32),
                 ("accurate_trig", i32), ("use_graph", i32), ("use_pdl", i32), ("gemv_tcgen05", i32), ("n_layers", i32), ("vocab", i32),
-                ("device", i32), ("gemv_unprepared", i32)]
+                ("device", i32), ("launch_per_op", i32), ("gemv_unprepared", i32)]
 
 
 # name -> (restype, argtypes); every symbol include/insignia_b200.h declares
@@ -60,6 +60,19 @@ SIGNATURES = {
     "insg_mxfp4_gemv_packed": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "insg_gemv_argmax_scratch_bytes": (sz, []),
     "insg_gemv_fused": (i32, [C.POINTER(GemvOp), vp]),
+    "insg_program_create": (vp, []),
+    "insg_program_destroy": (None, [vp]),
+    "insg_program_add_gemv": (i32, [vp, C.POINTER(GemvOp)]),
+    "insg_program_add_deltanet": (i32, [vp] * 8),
+    "insg_program_add_attention": (i32, [vp, C.POINTER(AttnOp)]),
+    "insg_program_add_embed": (i32, [vp, vp, vp, vp, vp, i32, i32]),
+    "insg_program_finalize": (i32, [vp]),
+    "insg_program_set_option": (i32, [vp, C.c_char_p, C.c_longlong]),
+    "insg_program_run": (i32, [vp, i32, i32, i32, vp, vp, vp, vp]),
+    "insg_program_recover": (i32, [vp, vp]),
+    "insg_program_selftest_barrier_timeout": (i32, [vp, C.c_ulonglong, vp, vp]),
+    "insg_program_phase_count": (i32, [vp]),
+    "insg_program_weight_bytes": (u64, [vp]),
     "insg_deltanet_decode": (i32, [vp] * 7 + [i32, vp]),
     "insg_deltanet_decode_tokens": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "insg_gqa_scratch_bytes": (sz, [i32]),
@@ -81,6 +94,19 @@ SIGNATURES = {
     "insg_concat": (i32, [vp, vp, vp, i32, vp]),
     "insg_argmax_logits": (i32, [vp, i32, vp, vp]),
     "insg_bf16_gemv": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "insg_storage_open": (vp, [C.c_char_p, u64, i32]),
+    "insg_storage_close": (None, [vp]),
+    "insg_storage_acquire": (i32, [vp, C.c_char_p, C.POINTER(vp), C.POINTER(u64)]),
+    "insg_storage_release": (i32, [vp, C.c_char_p]),
+    "insg_storage_prefetch": (i32, [vp, C.c_char_p]),
+    "insg_storage_tier": (i32, [vp, C.c_char_p]),
+    "insg_storage_reserve": (i32, [vp, u64]),
+    "insg_storage_unreserve": (i32, [vp, u64]),
+    "insg_storage_set_host_cache": (i32, [vp, u64]),
+    "insg_storage_clear": (i32, [vp]),
+    "insg_storage_device_bytes": (u64, [vp]),
+    "insg_storage_reserved_bytes": (u64, [vp]),
+    "insg_storage_stats": (i32, [vp, C.POINTER(u64)]),
     "insg_engine_create": (vp, [C.c_char_p, C.POINTER(EngineOptions)]),
     "insg_engine_destroy": (None, [vp]),
     "insg_engine_embed": (i32, [vp, i32]),
@@ -91,9 +117,9 @@ SIGNATURES = {
     "insg_engine_decode_token": (i32, [vp, i32]),
     "insg_engine_mtp_draft": (i32, [vp, i32]),
     "insg_engine_generate": (i32, [vp, i32, i32, C.POINTER(i32)]),
-    "insg_engine_profile_token": (i32, [vp, i32, vp, vp, vp]),
     "insg_engine_profile_gemv_chain": (i32, [vp, i32, vp, vp, vp]),
-    "insg_engine_set_trace": (i32, [vp, vp]),
+    "insg_engine_set_prefetch_records": (i32, [vp, i32]),
+    "insg_engine_selftest_barrier_timeout": (i32, [vp]),
     "insg_engine_position": (i32, [vp]),
     "insg_engine_set_position": (i32, [vp, i32]),
     "insg_engine_reset": (i32, [vp]),

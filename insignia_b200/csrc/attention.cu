@@ -12,138 +12,15 @@
 // do not depend on scheduling.  The fused entry also does the per-head RMSNorm,
 // partial RoPE and the cache write of the current token (src/ops.cu:9,
 // src/qwen_kernels.cu:15,31) so one launch replaces five.
-#include "common.cuh"
+#include "attention_body.cuh"
 #include "host_util.h"
-
-#include <mutex>
 
 namespace insg {
 
 constexpr int kAtThreads = 256;
 constexpr int kAtWarps = 8;
-constexpr int kSplits = 37;                  // 4 kv heads x 37 = 148 CTAs
 constexpr int kGroup = 4;                    // tokens a warp scores at once
 constexpr int kMinChunk = kAtWarps * kGroup; // tokens per split at least: one group per warp
-constexpr int kPartFloats = 8 + 4 * 256;     // m[4], l[4], acc[4][256]
-
-struct AttnParams {
-    const float *q;        // plain: [16][256] normalised; fused: interleaved q_proj output [16][512]
-    const float *k_raw;    // fused only
-    const float *v_new;    // fused only
-    const uint16_t *q_w, *k_w;
-    void *kc, *vc;
-    float *out;
-    const int *position;   // fused: device scalar
-    int position_offset;
-    int tokens;            // plain
-    int max_context;
-    int fast_trig;
-    unsigned *counters;    // [4] at the head of scratch
-    float *partials;       // [4][kSplits][kPartFloats]
-};
-
-// A lane's 8 dims of one cache row, as loaded (converted only when used, so that two token groups can be in flight).
-template <bool BF16> struct KvRow;
-template <> struct KvRow<false> {
-    struct Raw { float4 a, b; };
-    static __device__ __forceinline__ Raw load_raw(const void *base, size_t row_elems, int lane)
-    {
-        const float4 *p = reinterpret_cast<const float4 *>(static_cast<const float *>(base) + row_elems) + lane * 2;
-        return Raw{__ldcg(p), __ldcg(p + 1)};
-    }
-    static __device__ __forceinline__ Raw zero() { return Raw{make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)}; }
-    static __device__ __forceinline__ void unpack(const Raw &r, float (&o)[8])
-    {
-        o[0] = r.a.x; o[1] = r.a.y; o[2] = r.a.z; o[3] = r.a.w; o[4] = r.b.x; o[5] = r.b.y; o[6] = r.b.z; o[7] = r.b.w;
-    }
-    static __device__ __forceinline__ float round(float v) { return v; }
-    static __device__ __forceinline__ void store(void *base, size_t idx, float v) { static_cast<float *>(base)[idx] = v; }
-};
-template <> struct KvRow<true> {
-    struct Raw { uint4 r; };
-    static __device__ __forceinline__ Raw load_raw(const void *base, size_t row_elems, int lane)
-    {
-        return Raw{__ldcg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + row_elems) + lane)};
-    }
-    static __device__ __forceinline__ Raw zero() { return Raw{make_uint4(0u, 0u, 0u, 0u)}; }
-    static __device__ __forceinline__ void unpack(const Raw &w, float (&o)[8])
-    {
-        const uint4 r = w.r;
-        o[0] = __uint_as_float(r.x << 16); o[1] = __uint_as_float(r.x & 0xffff0000u);
-        o[2] = __uint_as_float(r.y << 16); o[3] = __uint_as_float(r.y & 0xffff0000u);
-        o[4] = __uint_as_float(r.z << 16); o[5] = __uint_as_float(r.z & 0xffff0000u);
-        o[6] = __uint_as_float(r.w << 16); o[7] = __uint_as_float(r.w & 0xffff0000u);
-    }
-    static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-    static __device__ __forceinline__ void store(void *base, size_t idx, float v)
-    {
-        static_cast<__nv_bfloat16 *>(base)[idx] = __float2bfloat16_rn(v);
-    }
-};
-
-template <bool BF16> struct GroupRaw {
-    typename KvRow<BF16>::Raw k[kGroup], v[kGroup];
-};
-
-// Rows tb..tb+kGroup-1 of one kv head (those below `tend`; the rest read as zero).
-template <bool BF16>
-__device__ __forceinline__ void load_group(const void *kc, const void *vc, int kvh, int tb, int tend, int lane, GroupRaw<BF16> &g)
-{
-#pragma unroll
-    for (int i = 0; i < kGroup; i++) {
-        const int t = tb + i;
-        if (t < tend) {
-            const size_t row = (size_t(t) * 4 + kvh) * 256;
-            g.k[i] = KvRow<BF16>::load_raw(kc, row, lane);
-            g.v[i] = KvRow<BF16>::load_raw(vc, row, lane);
-        } else {
-            g.k[i] = KvRow<BF16>::zero();
-            g.v[i] = KvRow<BF16>::zero();
-        }
-    }
-}
-
-// cos/sin of the rotate-half RoPE for the 8 dims a lane owns (only lanes 0..7 rotate: dims 0..63).
-__device__ __forceinline__ void rope_table(int pos, int lane, bool fast, float (&c)[8], float (&s)[8])
-{
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const int half = (lane * 8 + j) & 31;
-        if (fast) {
-            const float a = float(pos) * __powf(10000000.0f, -float(2 * half) / 64.0f);
-            c[j] = __cosf(a);
-            s[j] = __sinf(a);
-        } else {
-            const float a = float(pos) * powf(10000000.0f, -float(2 * half) / 64.0f);
-            sincosf(a, &s[j], &c[j]);
-        }
-    }
-}
-
-// RMSNorm over 256 (one warp, 8 values per lane, dims lane*8..+7) then rotate-half
-// RoPE on dims 0..63 (lanes 0..7; the partner dim i+-32 lives 4 lanes away).
-__device__ __forceinline__ void norm_rope_256(float (&v)[8], const uint4 wv, int lane, int pos, const float (&c)[8],
-                                              const float (&s)[8])
-{
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; j++) ss = fmaf(v[j], v[j], ss);
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / 256.f + 1e-6f);
-    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const float wf = bf16_bits_to_float((j & 1) ? (ww[j >> 1] >> 16) : (ww[j >> 1] & 0xffff));
-        v[j] *= inv * wf;
-    }
-    if (pos != 0) {
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[j], 4);
-            if (lane < 8) v[j] = v[j] * c[j] + (lane < 4 ? -other : other) * s[j];
-        }
-    }
-}
 
 template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) attn_splitk_kernel(const __grid_constant__ AttnParams p)
 {
@@ -174,9 +51,9 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     int t0 = split * chunk, t1 = min(tokens, t0 + chunk);
     int fresh = tokens - 1; // the row the producer (or this kernel) is still writing
 
-    GroupRaw<BF16> ga, gb; // this warp's next two token groups, in flight while it works on earlier ones
-    load_group<BF16>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
-    load_group<BF16>(p.kc, p.vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
+    GroupRaw<BF16, kGroup> ga, gb; // this warp's next two token groups, in flight while it works on earlier ones
+    load_group<BF16, kGroup>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
+    load_group<BF16, kGroup>(p.kc, p.vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
     uint4 norm_wv = make_uint4(0u, 0u, 0u, 0u);
     float rope_c[8], rope_s[8];
     if constexpr (FUSED) {
@@ -198,8 +75,8 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
             t0 = split * chunk;
             t1 = min(tokens, t0 + chunk);
             fresh = tokens - 1;
-            load_group<BF16>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
-            load_group<BF16>(p.kc, p.vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
+            load_group<BF16, kGroup>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
+            load_group<BF16, kGroup>(p.kc, p.vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
             if (warp < 5 && lane < 8) rope_table(pos, lane, p.fast_trig != 0, rope_c, rope_s);
         }
     }
@@ -259,7 +136,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
             for (int j = 0; j < 8; j++) acc[h][j] = 0.f;
         }
         // one token group: scores of its (up to) four tokens for the four query heads, one online-softmax update
-        auto process = [&](const GroupRaw<BF16> &grp, int tb) {
+        auto process = [&](const GroupRaw<BF16, kGroup> &grp, int tb) {
             float kk[kGroup][8];
 #pragma unroll
             for (int g = 0; g < kGroup; g++) Row::unpack(grp.k[g], kk[g]);
@@ -335,11 +212,11 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         const int tend = min(t1, fresh);
         for (int tb = t0 + warp * kGroup; tb < t1; tb += 2 * kAtWarps * kGroup) {
             process(ga, tb);
-            load_group<BF16>(p.kc, p.vc, kvh, tb + 2 * kAtWarps * kGroup, tend, lane, ga);
+            load_group<BF16, kGroup>(p.kc, p.vc, kvh, tb + 2 * kAtWarps * kGroup, tend, lane, ga);
             const int tb2 = tb + kAtWarps * kGroup;
             if (tb2 < t1) {
                 process(gb, tb2);
-                load_group<BF16>(p.kc, p.vc, kvh, tb2 + 2 * kAtWarps * kGroup, tend, lane, gb);
+                load_group<BF16, kGroup>(p.kc, p.vc, kvh, tb2 + 2 * kAtWarps * kGroup, tend, lane, gb);
             }
         }
         // ---- fold the 8 warps --------------------------------------------------------
@@ -441,26 +318,14 @@ constexpr int kNoAllocMaxTokens = 262144; // the model's longest context
 constexpr size_t kNoAllocScratchBytes = 64 + size_t(4) * kSplits * kPartFloats * sizeof(float);
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
-namespace {
-std::mutex g_noalloc_mutex;
-void *g_noalloc_ptr[64] = {nullptr};
-} // namespace
-
-// Device address of the static scratch on the current device (first call per device resolves it).
+// Device address of the static scratch on the current device.  Looked up on every call: the lookup allocates nothing,
+// and an address cached across calls would dangle after the application resets the device or its primary context.
 static int noalloc_scratch(void **out)
 {
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-    if (dev < 0 || dev >= 64) return fail(INSG_E_LIMIT, "gqa_decode_noalloc: device ordinal beyond 63");
-    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
-    if (!g_noalloc_ptr[dev]) {
-        void *p = nullptr;
-        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static attention scratch)");
-        g_noalloc_ptr[dev] = p;
-    }
-    *out = g_noalloc_ptr[dev];
+    void *p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static attention scratch)");
+    *out = p;
     return INSG_OK;
 }
 

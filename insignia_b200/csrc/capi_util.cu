@@ -37,7 +37,6 @@ int sm_count()
     return cached[dev];
 }
 
-int gemv_tune(const char *key, int value);
 int umma_tune(const char *key, int value);
 
 } // namespace insg
@@ -50,7 +49,7 @@ int insg_tune_set(const char *key, int value)
 {
     if (!key) return insg::fail(INSG_E_ARG, "tune: null key");
     if (insg::umma_tune(key, value) == INSG_OK) return INSG_OK;
-    return insg::gemv_tune(key, value);
+    return insg::fail(INSG_E_ARG, "unknown tuning key");
 }
 
 } // extern "C"

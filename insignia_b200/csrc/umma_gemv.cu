@@ -61,7 +61,7 @@ struct UParams {
     unsigned *argmax_ticket;
     int *token_out, *token_feedback, *token_log, *position_inout;
     int *error_flag;
-    unsigned long long *trace;
+    int token_log_capacity;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -103,17 +103,6 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-
-__device__ __forceinline__ unsigned long long u_global_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define INSG_UTRACE(slot)                                                                  \
-    do {                                                                                   \
-        if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 8 + (slot)] = u_global_ns(); \
-    } while (0)
 
 // kblock i of this CTA's sequence -> global address of its record and its place in the tile sequence
 struct URun {
@@ -169,7 +158,6 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_gemv_kernel(const __grid_co
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort, s_last;
 
-    INSG_UTRACE(0);
     pdl_launch_dependents();
 
     const int G = int(gridDim.x), c = int(blockIdx.x);
@@ -201,9 +189,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_gemv_kernel(const __grid_co
     }
     uint2 wpre[kPreVec];
     preload_norm_weights(p.pro, wpre);
-    INSG_UTRACE(1);
     pdl_wait();
-    INSG_UTRACE(2);
 
     // ---- activation prologue: fp32 vector -> 24-bit fixed point -> twelve E2M1 digit columns ---------
     float4 v[kMaxVec];
@@ -246,7 +232,6 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_gemv_kernel(const __grid_co
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    INSG_UTRACE(3);
 
     const uint32_t tmem = s_tmem;
     volatile int *abort_flag = &s_abort;
@@ -379,11 +364,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_gemv_kernel(const __grid_co
             if (lane == 0) { scratch[32 + warp] = best; reinterpret_cast<int *>(scratch)[40 + warp] = best_idx; }
         }
     }
-    INSG_UTRACE(4);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    INSG_UTRACE(5);
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
     if (tid == 0 && s_abort && p.error_flag) *p.error_flag = 1;
 
@@ -422,14 +405,13 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_gemv_kernel(const __grid_co
                 if (p.token_feedback) *p.token_feedback = bi;
                 if (p.position_inout) {
                     const int pos = *p.position_inout;
-                    if (p.token_log) p.token_log[pos] = bi;
+                    if (p.token_log && pos >= 0 && pos < p.token_log_capacity) p.token_log[pos] = bi;
                     *p.position_inout = pos + 1;
                 }
                 *p.argmax_ticket = 0u;
             }
         }
     }
-    INSG_UTRACE(6);
 }
 
 // ---- repack: MLX layout -> shared-memory images ----------------------------------------------------
@@ -469,8 +451,8 @@ struct UTune {
     int prefetch = 8;
 } g_utune;
 
-std::once_flag g_attr_once;
-cudaError_t g_attr_err = cudaSuccess;
+std::mutex g_attr_mutex;
+bool g_attr_done[64] = {false}; // the shared-memory opt-in is a per-device function attribute
 } // namespace
 
 int umma_tune(const char *key, int value)
@@ -519,9 +501,10 @@ int gemv_umma_launch(const insg_gemv_op *op, cudaStream_t st)
         p.argmax_ticket = static_cast<unsigned *>(op->argmax_scratch);
         p.argmax_partial = reinterpret_cast<float2 *>(static_cast<uint8_t *>(op->argmax_scratch) + 64);
         p.token_out = op->token_out; p.token_feedback = op->token_feedback; p.token_log = op->token_log; p.position_inout = op->position_inout;
+        p.token_log_capacity = op->token_log_capacity;
+        if (op->token_log && op->token_log_capacity <= 0) return fail(INSG_E_ARG, "gemv: token_log needs its capacity");
     }
     p.error_flag = static_cast<int *>(op->error_flag);
-    p.trace = static_cast<unsigned long long *>(op->trace);
     const size_t fixed = size_t(p.nkb) * kBImgPerKb + 512 + 64 * 4 + 1024;
     int stages = std::min(g_utune.stages, int((size_t(220) * 1024 - fixed) / kURec));
     stages = std::max(2, std::min(stages, 24));
@@ -529,8 +512,18 @@ int gemv_umma_launch(const insg_gemv_op *op, cudaStream_t st)
     p.nacc = g_utune.nacc;
     p.prefetch = std::min(g_utune.prefetch, stages);
     const size_t smem = size_t(stages) * kURec + fixed;
-    std::call_once(g_attr_once, [] { g_attr_err = cudaFuncSetAttribute(umma_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024); });
-    if (g_attr_err != cudaSuccess) return cuda_fail(g_attr_err, "cudaFuncSetAttribute(umma gemv)");
+    {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+        if (dev < 0 || dev >= 64) return fail(INSG_E_LIMIT, "gemv: device ordinal beyond 63");
+        std::lock_guard<std::mutex> lock(g_attr_mutex);
+        if (!g_attr_done[dev]) {
+            e = cudaFuncSetAttribute(umma_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(umma gemv)");
+            g_attr_done[dev] = true;
+        }
+    }
     return launch(umma_gemv_kernel, dim3(grid), dim3(kUThreads), smem, st, op->pdl != 0, p);
 }
 

@@ -23,9 +23,12 @@ class Engine:
     def __init__(self, index_path: str, max_context: int = 4096, budget_bytes: int = 16 << 30, kv_bf16: bool = False,
                  gate_elementwise: bool = False, accurate_trig: bool = False, use_graph: bool = True,
                  use_pdl: bool = True, n_layers: int = 32, vocab: int = 248320, device: int = 0,
-                 gemv_tcgen05: bool = False, prepared_inputs: bool = True):
+                 gemv_tcgen05: bool = False, prepared_inputs: bool = True, launch_per_op: bool = False):
+        """``launch_per_op=False`` (default): a token step is one persistent cooperative launch; ``True``: one launch per
+        fused operation (replayed from a CUDA graph when ``use_graph``)."""
         o = EngineOptions(budget_bytes, max_context, int(kv_bf16), int(gate_elementwise), int(accurate_trig),
-                          int(use_graph), int(use_pdl), int(gemv_tcgen05), n_layers, vocab, device, int(not prepared_inputs))
+                          int(use_graph), int(use_pdl), int(gemv_tcgen05), n_layers, vocab, device, int(launch_per_op),
+                          int(not prepared_inputs))
         self.vocab = vocab
         self._destroy = _lib.lib().insg_engine_destroy  # held here: module globals may be gone when __del__ runs at exit
         self._h = _lib.lib().insg_engine_create(index_path.encode(), C.byref(o))
@@ -74,18 +77,20 @@ class Engine:
         check(_lib.lib().insg_engine_generate(self._h, first_token, count, buf))
         return list(buf)
 
-    def profile_token(self, token: int) -> dict:
-        """One eager token step with per-launch CUDA events; per kernel class: ms, algorithmic bytes, launches."""
-        ms, by, ln = (C.c_float * 4)(), (C.c_uint64 * 4)(), (C.c_int * 4)()
-        check(_lib.lib().insg_engine_profile_token(self._h, token, ms, by, ln))
-        names = ("gemv", "deltanet", "attention", "embed")
-        return {n: {"ms": ms[i], "bytes": by[i], "launches": ln[i]} for i, n in enumerate(names)}
-
     def profile_gemv_chain(self, replays: int = 8) -> dict:
-        """The token step's fused-GEMV launches alone as a replayed graph; the sequence state is garbage afterwards (reset())."""
+        """The token step's fused-GEMV operations alone, timed between two CUDA events; the sequence state is garbage afterwards (reset())."""
         ms, by, ln = C.c_float(), C.c_uint64(), C.c_int()
         check(_lib.lib().insg_engine_profile_gemv_chain(self._h, replays, C.byref(ms), C.byref(by), C.byref(ln)))
         return {"ms_per_token": ms.value, "bytes": by.value, "launches": ln.value}
+
+    def set_prefetch_records(self, records: int):
+        """Prefetch distance of the persistent token kernel (weight records per warp kept requested into L2); 0 = off."""
+        check(_lib.lib().insg_engine_set_prefetch_records(self._h, records))
+
+    def selftest_barrier_timeout(self) -> bool:
+        """Runs the persistent kernel once with a grid barrier that cannot be met and a 2 ms wait limit; True when the
+        kernel gave up and raised its error status.  Call reset() afterwards."""
+        return check(_lib.lib().insg_engine_selftest_barrier_timeout(self._h)) == 1
 
     @property
     def position(self) -> int:

@@ -8,7 +8,9 @@
 //   attention layer: q|k|v proj, norm/RoPE/KV store/split-K attention, o_proj(gated)+residual,
 //                    gate/up + SwiGLU, down + residual           5
 //   final norm + lm_head + arg-max                               1
-// = 162 launches, replayed from one CUDA graph with programmatic dependent launch edges.
+// = 162 fused operations per token.  Default: recorded once as a program and executed by ONE persistent cooperative
+// launch per token (or per run of tokens), with grid barriers between the operations (csrc/persistent.cu).  Option
+// launch_per_op: the same operations as 162 launches replayed from one CUDA graph with programmatic dependent launch.
 #include "insignia_decode.hpp"
 
 #include "insignia_b200.h"
@@ -142,6 +144,8 @@ struct Qwen35Decode::Plan {
     cudaGraphExec_t exec_multi{}; // kMultiSteps token steps in one graph, for device-fed generation
     cudaGraphExec_t exec_chunk{}; // one pass of forward_tokens over kChunk prompt tokens
     int *host_result{}; // pinned: {next token, wait-expired flag}, so the per-token read-back is a true asynchronous copy
+    insg_program *prog{};     // the token step as one persistent launch
+    int prefetch_records = -1; // -1: the program's default
 };
 
 Qwen35Decode::Qwen35Decode(Qwen35Weights &weights, DecodeWorkspace &workspace) : w_(weights), x_(workspace) {}
@@ -155,6 +159,7 @@ Qwen35Decode::~Qwen35Decode()
     if (p.exec_multi) cudaGraphExecDestroy(p.exec_multi);
     if (p.exec_chunk) cudaGraphExecDestroy(p.exec_chunk);
     if (p.graph) cudaGraphDestroy(p.graph);
+    if (p.prog) insg_program_destroy(p.prog);
     for (const std::string &n : p.pinned) w_.storage().release(n);
     for (const std::string &n : p.pinned_mats) w_.release(n);
     if (p.host_result) cudaFreeHost(p.host_result);
@@ -201,39 +206,16 @@ struct Loader {
 };
 } // namespace
 
-// Keeps the stream busy for a fixed time (bounded by the clock, not by another kernel) so that a
-// whole token's launches and their event pairs can be queued behind it: the events then bracket
-// device-side durations instead of the host's enqueue pace.
-__global__ void hold_stream_kernel(unsigned long long ns)
-{
-    unsigned long long t0, t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
-    do {
-        __nanosleep(2000);
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    } while (t - t0 < ns);
-}
-
 // --------------------------------------------------------------- enqueue helpers
-struct StepProfile {
-    struct Ev {
-        cudaEvent_t start, stop;
-        int cls;
-        uint64_t bytes;
-    };
-    std::vector<Ev> events;
-    bool gemv_only = false; // chain pass: only the fused GEMV launches are issued, no events
-    uint64_t gemv_bytes = 0;
-    int gemv_launches = 0;
-};
-
 namespace {
 struct Ctx {
     DecodeWorkspace &x;
     cudaStream_t st;
     bool pdl;
     uint64_t &launches;
-    StepProfile *prof;
+    bool gemv_only;                      // only the fused GEMVs are issued (timing of the weight-streaming chain alone)
+    insg_program *rec;                   // non-null: operations are appended to this program instead of being launched
+    uint64_t *gemv_bytes;                // optional: algorithmic weight bytes of the GEMVs issued are added here
     bool hidden_prepared = false;        // the previous block left this block's first input prepared
     const uint16_t *next_norm = nullptr; // weight of the RMSNorm that reads this block's output next, when known
     void *prep_hidden() const { return static_cast<uint8_t *>(x.prep) + kPrepHidden; }
@@ -270,26 +252,7 @@ void residual_output(const Ctx &c, insg_gemv_segment &s, const uint16_t *followi
     s.prep_partials = c.prep_sums();
 }
 
-// Brackets one launch with events when a profile is being taken (never during graph capture).
-struct Timed {
-    StepProfile *p;
-    cudaStream_t st;
-    Timed(Ctx &c, int cls, uint64_t bytes) : p(c.prof && !c.prof->gemv_only ? c.prof : nullptr), st(c.st)
-    {
-        if (!p) return;
-        cudaEvent_t a, b;
-        cuda_check(cudaEventCreate(&a), "event");
-        cuda_check(cudaEventCreate(&b), "event");
-        p->events.push_back({a, b, cls, bytes});
-        cuda_check(cudaEventRecord(a, st), "event record");
-    }
-    ~Timed()
-    {
-        if (p) cudaEventRecord(p->events.back().stop, st);
-    }
-};
-
-uint64_t gemv_bytes(const insg_gemv_op &op)
+uint64_t gemv_weight_bytes(const insg_gemv_op &op)
 {
     uint64_t b = 0;
     for (int i = 0; i < op.n_segments; i++)
@@ -302,13 +265,9 @@ void run_gemv(Ctx &c, insg_gemv_op &op)
     op.pdl = c.pdl ? 1 : 0;
     op.layout = c.x.options.gemv_tcgen05 ? 1 : 0;
     op.error_flag = c.x.d_token + 3;
-    if (c.x.trace) op.trace = static_cast<uint8_t *>(c.x.trace) + size_t(c.x.trace_index++) * 296 * 8 * 8;
-    Timed t(c, 0, gemv_bytes(op));
-    if (c.prof && c.prof->gemv_only) {
-        c.prof->gemv_bytes += gemv_bytes(op);
-        c.prof->gemv_launches++;
-    }
-    insg_check(insg_gemv_fused(&op, c.st));
+    if (c.gemv_bytes) *c.gemv_bytes += gemv_weight_bytes(op);
+    if (c.rec) insg_check(insg_program_add_gemv(c.rec, &op));
+    else insg_check(insg_gemv_fused(&op, c.st));
     c.launches++;
 }
 
@@ -370,10 +329,10 @@ static void enqueue_delta_block(Ctx &c, const Qwen35Decode::Plan::Block &b, int 
     in.seg[3] = seg(b.b, x.b, INSG_EPI_BETA);
     run_gemv(c, in);
 
-    if (!(c.prof && c.prof->gemv_only)) {
-        Timed t(c, 1, uint64_t(2) * 32 * 128 * 128 * 4); // state read + write
-        insg_check(insg_deltanet_decode(x.delta_state + size_t(di) * 32 * 128 * 128, x.qkv, x.qkv + 2048, x.qkv + 4096, x.a, x.b,
-                                        x.core, c.pdl ? 1 : 0, c.st));
+    if (!c.gemv_only) {
+        float *state = x.delta_state + size_t(di) * 32 * 128 * 128;
+        if (c.rec) insg_check(insg_program_add_deltanet(c.rec, state, x.qkv, x.qkv + 2048, x.qkv + 4096, x.a, x.b, x.core));
+        else insg_check(insg_deltanet_decode(state, x.qkv, x.qkv + 2048, x.qkv + 4096, x.a, x.b, x.core, c.pdl ? 1 : 0, c.st));
         c.launches++;
     }
 
@@ -419,9 +378,9 @@ static void enqueue_attention_block(Ctx &c, const Qwen35Decode::Plan::Block &b, 
     at.scratch = x.attn_scratch;
     at.scratch_bytes = insg_gqa_scratch_bytes(x.max_context);
     at.pdl = c.pdl ? 1 : 0;
-    if (!(c.prof && c.prof->gemv_only)) {
-        Timed t(c, 2, uint64_t(x.position + 1) * 1024 * 2 * (x.options.kv_bf16 ? 2 : 4)); // K and V rows read
-        insg_check(insg_attention_step(&at, c.st));
+    if (!c.gemv_only) {
+        if (c.rec) insg_check(insg_program_add_attention(c.rec, &at));
+        else insg_check(insg_attention_step(&at, c.st));
         c.launches++;
     }
 
@@ -631,12 +590,25 @@ void Qwen35Decode::enqueue_embed()
 {
     Plan &p = plan();
     load_embed();
-    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_};
-    if (prof_ && prof_->gemv_only) return;
-    Timed t(c, 3, uint64_t(kHidden) * 17 / 32);
-    insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
-                                x_.hidden, x_.d_token, p.embed.rows, kHidden, c.pdl ? 1 : 0, p.stream));
+    if (gemv_only_) return;
+    const uint32_t *w = static_cast<const uint32_t *>(p.embed.weight.data);
+    const uint8_t *s = static_cast<const uint8_t *>(p.embed.scales.data);
+    if (rec_) insg_check(insg_program_add_embed(rec_, w, s, x_.hidden, x_.d_token, p.embed.rows, kHidden));
+    else insg_check(insg_mxfp4_embed(w, s, x_.hidden, x_.d_token, p.embed.rows, kHidden, x_.options.use_pdl ? 1 : 0, p.stream));
     launches_++;
+}
+
+// Queues the matrices of block l for background upload, so that they arrive while the block before is being repacked.
+void Qwen35Decode::prefetch_block(int l)
+{
+    if (l < 0 || l >= x_.options.n_layers || plan().layers[l].ready) return;
+    const std::string name = std::string(kLM) + ".model.layers." + std::to_string(l);
+    if (Qwen35Shape::full_attention(l)) {
+        for (const char *m : {"q_proj", "k_proj", "v_proj", "o_proj"}) w_.prefetch(name + ".self_attn." + m);
+    } else {
+        for (const char *m : {"in_proj_qkv", "in_proj_z", "in_proj_a", "in_proj_b", "out_proj"}) w_.prefetch(name + ".linear_attn." + m);
+    }
+    for (const char *m : {"gate_proj", "up_proj", "down_proj"}) w_.prefetch(name + ".mlp." + m);
 }
 
 void Qwen35Decode::load_block(int l)
@@ -644,6 +616,7 @@ void Qwen35Decode::load_block(int l)
     Plan &p = plan();
     Plan::Block &b = p.layers[l];
     if (b.ready) return;
+    prefetch_block(l + 1);
     Loader L{w_, p.pinned, x_.options.gemv_tcgen05 ? 1 : 0};
     const std::string name = std::string(kLM) + ".model.layers." + std::to_string(l);
     if (Qwen35Shape::full_attention(l)) load_attention(L, name, b);
@@ -665,7 +638,7 @@ void Qwen35Decode::enqueue_delta(int l, bool hidden_prepared, const uint16_t *ne
 {
     Plan &p = plan();
     load_block(l);
-    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_, hidden_prepared, next_norm};
+    Ctx c{x_, p.stream, x_.options.use_pdl, launches_, gemv_only_, rec_, gemv_bytes_, hidden_prepared, next_norm};
     enqueue_delta_block(c, p.layers[l], l - l / 4);
 }
 
@@ -675,7 +648,7 @@ void Qwen35Decode::enqueue_attention(int l, bool hidden_prepared, const uint16_t
     load_block(l);
     const size_t esz = x_.options.kv_bf16 ? 2 : 4;
     const size_t off = size_t(l / 4) * x_.max_context * 1024 * esz;
-    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_, hidden_prepared, next_norm};
+    Ctx c{x_, p.stream, x_.options.use_pdl, launches_, gemv_only_, rec_, gemv_bytes_, hidden_prepared, next_norm};
     enqueue_attention_block(c, p.layers[l], reinterpret_cast<uint8_t *>(x_.kv_keys) + off, reinterpret_cast<uint8_t *>(x_.kv_values) + off, 0);
 }
 
@@ -683,7 +656,7 @@ void Qwen35Decode::enqueue_head(bool hidden_prepared)
 {
     Plan &p = plan();
     load_head();
-    Ctx c{x_, p.stream, x_.options.use_pdl && (!prof_ || prof_->gemv_only), launches_, prof_, hidden_prepared, nullptr};
+    Ctx c{x_, p.stream, x_.options.use_pdl, launches_, gemv_only_, rec_, gemv_bytes_, hidden_prepared, nullptr};
     insg_gemv_op op = {};
     rmsnorm_input(c, op, p.final_norm);
     op.n_segments = 1;
@@ -693,6 +666,7 @@ void Qwen35Decode::enqueue_head(bool hidden_prepared)
     op.token_out = x_.d_next;
     op.token_feedback = x_.d_token;
     op.token_log = x_.d_token + 4;
+    op.token_log_capacity = x_.max_context + 1;
     op.position_inout = x_.d_position;
     run_gemv(c, op);
 }
@@ -725,7 +699,6 @@ void Qwen35Decode::layer(int l)
 // embed, all layers, head: what one graph replay does
 void Qwen35Decode::enqueue_token_step()
 {
-    x_.trace_index = 0;
     Plan &p = plan();
     const int n = x_.options.n_layers;
     for (int l = 0; l < n; l++) load_block(l); // every block's norm weight is needed by the block before it
@@ -739,6 +712,71 @@ void Qwen35Decode::enqueue_token_step()
     }
     enqueue_head(n > 0);
 }
+
+// Records the token step as a program (every weight is made resident first: uploads and repacks allocate and
+// synchronise, which a recording tolerates and a running kernel does not need).
+void Qwen35Decode::build_program()
+{
+    Plan &p = plan();
+    if (p.prog) return;
+    insg_program *g = insg_program_create();
+    if (!g) throw std::runtime_error("insg_program_create failed");
+    const uint64_t before = launches_;
+    rec_ = g;
+    try {
+        enqueue_token_step();
+        rec_ = nullptr;
+        insg_check(insg_program_finalize(g));
+        if (p.prefetch_records >= 0) insg_check(insg_program_set_option(g, "prefetch_records", p.prefetch_records));
+    } catch (...) {
+        rec_ = nullptr;
+        launches_ = before;
+        insg_program_destroy(g);
+        throw;
+    }
+    launches_ = before;
+    p.prog = g;
+    p.capturing = true; // every weight is resident now
+}
+
+// One persistent launch: n_tokens token steps; token >= 0 is stored as the first input token, and the host's position
+// as the device position, by the kernel itself.
+void Qwen35Decode::run_program(int n_tokens, int token)
+{
+    Plan &p = plan();
+    build_program();
+    insg_check(insg_program_run(p.prog, n_tokens, token, x_.position, x_.d_token, x_.d_position, x_.d_token + 3, p.stream));
+    launches_++;
+}
+
+void Qwen35Decode::set_prefetch_records(int records)
+{
+    Plan &p = plan();
+    p.prefetch_records = records < 0 ? -1 : records;
+    if (p.prog && records >= 0) insg_check(insg_program_set_option(p.prog, "prefetch_records", records));
+}
+
+bool Qwen35Decode::selftest_barrier_timeout()
+{
+    if (!persistent()) throw std::runtime_error("selftest_barrier_timeout needs the persistent token kernel");
+    Plan &p = plan();
+    build_program();
+    insg_check(insg_program_selftest_barrier_timeout(p.prog, 2000000ull, x_.d_token + 3, p.stream)); // 2 ms
+    launches_++;
+    int *result = p.host_result;
+    result[1] = 0;
+    cuda_check(cudaMemcpyAsync(result + 1, x_.d_token + 3, sizeof(int), cudaMemcpyDeviceToHost, p.stream), "read status");
+    cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
+    const bool gave_up = result[1] != 0;
+    insg_check(insg_program_recover(p.prog, p.stream));
+    cuda_check(cudaMemsetAsync(x_.d_token + 3, 0, sizeof(int), p.stream), "clear status");
+    cuda_check(cudaMemsetAsync(x_.attn_scratch, 0, 64, p.stream), "clear attention tickets");
+    cuda_check(cudaMemsetAsync(x_.argmax_scratch, 0, 64, p.stream), "clear arg-max ticket");
+    fused_token_valid_ = false;
+    return gave_up;
+}
+
+bool Qwen35Decode::persistent() const { return !x_.options.launch_per_op && !x_.options.gemv_tcgen05; }
 
 void Qwen35Decode::replay_token_step()
 {
@@ -797,8 +835,12 @@ void Qwen35Decode::forward_token(int token)
 {
     if (token < 0 || token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
     if (x_.options.n_layers > 3 && x_.position >= x_.max_context) throw std::runtime_error("KV cache full");
-    sync_scalars(token);
-    replay_token_step();
+    if (persistent()) {
+        run_program(1, token);
+    } else {
+        sync_scalars(token);
+        replay_token_step();
+    }
     x_.position++;
     fused_token_valid_ = true;
 }
@@ -819,7 +861,7 @@ void Qwen35Decode::forward_tokens(const int *tokens, int count)
     for (int l = 0; l < n; l++) load_block(l);
     load_head();
     load_embed();
-    Ctx c{x_, p.stream, x_.options.use_pdl, launches_, nullptr};
+    Ctx c{x_, p.stream, x_.options.use_pdl, launches_, false, nullptr, nullptr};
     for (int done = 0; done < count;) {
         const int left = count - done, T = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
         Multi u(x_, T);
@@ -884,6 +926,18 @@ void Qwen35Decode::forward_tokens(const int *tokens, int count)
     p.capturing = true; // every weight is resident now: the next forward_token may capture its graph
 }
 
+// A kernel gave up on a wait: put the barrier state, the tickets and the status word back so that later calls work.
+void Qwen35Decode::recover_after_timeout()
+{
+    Plan &p = plan();
+    if (p.prog) insg_program_recover(p.prog, p.stream);
+    cudaMemsetAsync(x_.d_token + 3, 0, sizeof(int), p.stream);
+    cudaMemsetAsync(x_.attn_scratch, 0, 64, p.stream);
+    cudaMemsetAsync(x_.argmax_scratch, 0, 64, p.stream);
+    cudaStreamSynchronize(p.stream);
+    fused_token_valid_ = false;
+}
+
 int Qwen35Decode::logits_argmax()
 {
     Plan &p = plan();
@@ -896,7 +950,10 @@ int Qwen35Decode::logits_argmax()
     result[1] = 0;
     cuda_check(cudaMemcpyAsync(result, x_.d_next, 2 * sizeof(int), cudaMemcpyDeviceToHost, p.stream), "read token");
     cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
-    if (result[1]) throw std::runtime_error("a bounded wait inside a GPU kernel expired");
+    if (result[1]) {
+        recover_after_timeout();
+        throw std::runtime_error("a bounded wait inside a GPU kernel expired");
+    }
     return result[0];
 }
 
@@ -914,6 +971,23 @@ std::vector<int> Qwen35Decode::generate(int first_token, int count)
     if (x_.position + count > x_.max_context) throw std::runtime_error("KV cache full");
     Plan &p = plan();
     const int start = x_.position;
+    if (persistent()) {
+        // the kernel loops over the tokens itself: the head feeds its arg-max back and advances the position
+        run_program(count, first_token);
+        x_.position += count;
+        fused_token_valid_ = true;
+        int *flag = p.host_result + 1;
+        *flag = 0;
+        cuda_check(cudaMemcpyAsync(out.data(), x_.d_token + 4 + start, size_t(count) * sizeof(int), cudaMemcpyDeviceToHost, p.stream),
+                   "read tokens");
+        cuda_check(cudaMemcpyAsync(flag, x_.d_token + 3, sizeof(int), cudaMemcpyDeviceToHost, p.stream), "read status");
+        cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
+        if (*flag) {
+            recover_after_timeout();
+            throw std::runtime_error("a bounded wait inside a GPU kernel expired");
+        }
+        return out;
+    }
     sync_scalars(first_token);
     for (int i = 0; i < count;) {
         // The head feeds its arg-max back into d_token and advances d_position, so consecutive steps need nothing from
@@ -937,82 +1011,87 @@ std::vector<int> Qwen35Decode::generate(int first_token, int count)
     return out;
 }
 
-void Qwen35Decode::profile_token(int token, float ms[4], uint64_t bytes[4], int launches[4])
-{
-    if (token < 0 || token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
-    if (x_.position >= x_.max_context) throw std::runtime_error("KV cache full");
-    Plan &p = plan();
-    StepProfile prof;
-    sync_scalars(token);
-    prof_ = &prof;
-    hold_stream_kernel<<<1, 1, 0, p.stream>>>(4000000ull); // 4 ms: longer than the host needs to queue one token
-    try {
-        enqueue_token_step(); // eager, one event pair per launch, no dependent-launch overlap
-    } catch (...) {
-        prof_ = nullptr;
-        throw;
-    }
-    prof_ = nullptr;
-    x_.position++;
-    fused_token_valid_ = true;
-    cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
-    for (int i = 0; i < 4; i++) { ms[i] = 0.f; bytes[i] = 0; launches[i] = 0; }
-    for (auto &e : prof.events) {
-        float t = 0.f;
-        cudaEventElapsedTime(&t, e.start, e.stop);
-        ms[e.cls] += t;
-        bytes[e.cls] += e.bytes;
-        launches[e.cls]++;
-        cudaEventDestroy(e.start);
-        cudaEventDestroy(e.stop);
-    }
-}
-
 void Qwen35Decode::profile_gemv_chain(int replays, float *ms_per_token, uint64_t *bytes, int *launches)
 {
     Plan &p = plan();
-    if (!p.capturing && !p.exec) throw std::runtime_error("profile_gemv_chain needs a forwarded token (weights resident)");
+    if (!p.capturing && !p.exec && !p.prog) throw std::runtime_error("profile_gemv_chain needs a forwarded token (weights resident)");
     replays = std::max(1, std::min(replays, 64));
-    StepProfile only;
-    only.gemv_only = true;
-    cudaGraph_t graph = nullptr;
-    cudaGraphExec_t exec = nullptr;
+    if (x_.position + replays + 2 > x_.max_context) throw std::runtime_error("profile_gemv_chain: not enough context left");
+    uint64_t chain_bytes = 0;
     const uint64_t before = launches_;
-    prof_ = &only;
-    cuda_check(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal), "begin graph capture");
+    cudaGraphExec_t exec = nullptr;
+    insg_program *chain = nullptr;
+    gemv_only_ = true;
+    gemv_bytes_ = &chain_bytes;
     try {
-        enqueue_token_step();
+        if (persistent()) {
+            chain = insg_program_create();
+            if (!chain) throw std::runtime_error("insg_program_create failed");
+            rec_ = chain;
+            enqueue_token_step();
+            rec_ = nullptr;
+            insg_check(insg_program_finalize(chain));
+            if (p.prefetch_records >= 0) insg_check(insg_program_set_option(chain, "prefetch_records", p.prefetch_records));
+        } else {
+            cudaGraph_t graph = nullptr;
+            cuda_check(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal), "begin graph capture");
+            try {
+                enqueue_token_step();
+            } catch (...) {
+                cudaStreamEndCapture(p.stream, &graph);
+                if (graph) cudaGraphDestroy(graph);
+                throw;
+            }
+            cuda_check(cudaStreamEndCapture(p.stream, &graph), "end graph capture");
+            const cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            cuda_check(e, "instantiate graph");
+        }
     } catch (...) {
-        prof_ = nullptr;
-        cudaStreamEndCapture(p.stream, &graph);
-        if (graph) cudaGraphDestroy(graph);
+        rec_ = nullptr;
+        gemv_only_ = false;
+        gemv_bytes_ = nullptr;
+        launches_ = before;
+        if (chain) insg_program_destroy(chain);
         throw;
     }
-    prof_ = nullptr;
+    gemv_only_ = false;
+    gemv_bytes_ = nullptr;
+    const int chain_launches = int(launches_ - before);
     launches_ = before;
-    cuda_check(cudaStreamEndCapture(p.stream, &graph), "end graph capture");
-    cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
-    cudaGraphDestroy(graph);
-    cuda_check(e, "instantiate graph");
-    cudaEvent_t a, b;
-    cuda_check(cudaEventCreate(&a), "event");
-    cuda_check(cudaEventCreate(&b), "event");
-    cudaGraphLaunch(exec, p.stream); // warm
-    cudaEventRecord(a, p.stream);
-    for (int i = 0; i < replays; i++) cudaGraphLaunch(exec, p.stream);
-    cudaEventRecord(b, p.stream);
-    e = cudaStreamSynchronize(p.stream);
+    auto once = [&] {
+        if (chain) insg_check(insg_program_run(chain, 1, -1, -1, nullptr, nullptr, x_.d_token + 3, p.stream));
+        else cuda_check(cudaGraphLaunch(exec, p.stream), "launch graph");
+    };
+    cudaEvent_t a = nullptr, b = nullptr;
+    cudaError_t e = cudaSuccess;
     float ms = 0.f;
-    cudaEventElapsedTime(&ms, a, b);
+    try {
+        cuda_check(cudaEventCreate(&a), "event");
+        cuda_check(cudaEventCreate(&b), "event");
+        once(); // warm
+        cuda_check(cudaEventRecord(a, p.stream), "event record");
+        for (int i = 0; i < replays; i++) once();
+        cuda_check(cudaEventRecord(b, p.stream), "event record");
+        e = cudaStreamSynchronize(p.stream);
+        if (e == cudaSuccess) cudaEventElapsedTime(&ms, a, b);
+    } catch (...) {
+        if (a) cudaEventDestroy(a);
+        if (b) cudaEventDestroy(b);
+        if (exec) cudaGraphExecDestroy(exec);
+        if (chain) insg_program_destroy(chain);
+        throw;
+    }
     cudaEventDestroy(a);
     cudaEventDestroy(b);
-    cudaGraphExecDestroy(exec);
+    if (exec) cudaGraphExecDestroy(exec);
+    if (chain) insg_program_destroy(chain);
     cuda_check(e, "synchronize");
     *ms_per_token = ms / float(replays);
-    *bytes = only.gemv_bytes;
-    *launches = only.gemv_launches;
+    *bytes = chain_bytes;
+    *launches = chain_launches;
     fused_token_valid_ = false;
-    sync_scalars(-1); // the head launches advanced the device-side position; put the host's view back
+    sync_scalars(-1); // the head operations advanced the device-side position; put the host's view back
 }
 
 int Qwen35Decode::mtp_draft(int token)
@@ -1040,7 +1119,7 @@ int Qwen35Decode::mtp_draft(int token)
     insg_check(insg_rmsnorm_bf16(x_.hidden, p.mtp_norm_h, nullptr, x_.qkv + kHidden, 1, kHidden, 0, p.stream));
     insg_check(insg_bf16_gemv(p.mtp_fc, x_.qkv, x_.hidden, kHidden, 2 * kHidden, 0, p.stream)); // overwrites the residual, as the reference
     launches_ += 4;
-    Ctx c{x_, p.stream, pdl, launches_, nullptr};
+    Ctx c{x_, p.stream, pdl, launches_, false, nullptr, nullptr};
     enqueue_attention_block(c, p.mtp, x_.mtp_keys, x_.mtp_values, -1); // rotary position / cache row position-1, position rows attended
 
     insg_gemv_op op = {};

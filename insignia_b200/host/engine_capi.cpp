@@ -20,7 +20,23 @@ struct insg_engine {
     int device = 0;
 };
 
+// Handle over ModelFile + TieredStorage alone (include/insignia_storage.hpp), for callers without C++.
+struct insg_storage {
+    insignia::ModelFile model;
+    std::unique_ptr<insignia::TieredStorage> store;
+};
+
 namespace {
+template <class F> int storage_guarded(insg_storage *s, F &&f)
+{
+    if (!s) return insg::fail(INSG_E_ARG, "null storage");
+    try {
+        return f();
+    } catch (const std::exception &ex) {
+        return insg::fail(INSG_E_RUNTIME, ex.what());
+    }
+}
+
 template <class F> int guarded(insg_engine *e, F &&f)
 {
     if (!e) return insg::fail(INSG_E_ARG, "null engine");
@@ -60,6 +76,97 @@ float *field_ptr(insignia::DecodeWorkspace &x, const std::string &f)
 
 extern "C" {
 
+insg_storage *insg_storage_open(const char *index_path, uint64_t device_budget_bytes, int host_backend)
+{
+    if (!index_path) {
+        insg::fail(INSG_E_ARG, "null index path");
+        return nullptr;
+    }
+    try {
+        auto s = std::make_unique<insg_storage>();
+        s->model = insignia::ModelFile(index_path);
+        s->store = std::make_unique<insignia::TieredStorage>(s->model, device_budget_bytes, nullptr,
+                                                             host_backend ? insignia::make_host_backend() : nullptr);
+        return s.release();
+    } catch (const std::exception &ex) {
+        insg::fail(INSG_E_RUNTIME, ex.what());
+        return nullptr;
+    }
+}
+void insg_storage_close(insg_storage *s) { delete s; }
+int insg_storage_acquire(insg_storage *s, const char *name, void **data, uint64_t *bytes)
+{
+    return storage_guarded(s, [&] {
+        if (!name) return insg::fail(INSG_E_ARG, "null name");
+        const insignia::DeviceView v = s->store->acquire(name);
+        if (data) *data = v.data;
+        if (bytes) *bytes = v.bytes;
+        return int(INSG_OK);
+    });
+}
+int insg_storage_release(insg_storage *s, const char *name)
+{
+    return storage_guarded(s, [&] {
+        if (!name) return insg::fail(INSG_E_ARG, "null name");
+        s->store->release(name);
+        return int(INSG_OK);
+    });
+}
+int insg_storage_prefetch(insg_storage *s, const char *name)
+{
+    return storage_guarded(s, [&] {
+        if (!name) return insg::fail(INSG_E_ARG, "null name");
+        return s->store->prefetch(name) ? 1 : 0;
+    });
+}
+int insg_storage_tier(insg_storage *s, const char *name)
+{
+    return storage_guarded(s, [&] {
+        if (!name) return insg::fail(INSG_E_ARG, "null name");
+        return int(s->store->tier(name));
+    });
+}
+int insg_storage_reserve(insg_storage *s, uint64_t bytes)
+{
+    return storage_guarded(s, [&] {
+        s->store->reserve(bytes);
+        return int(INSG_OK);
+    });
+}
+int insg_storage_unreserve(insg_storage *s, uint64_t bytes)
+{
+    return storage_guarded(s, [&] {
+        s->store->unreserve(bytes);
+        return int(INSG_OK);
+    });
+}
+int insg_storage_set_host_cache(insg_storage *s, uint64_t bytes)
+{
+    return storage_guarded(s, [&] {
+        s->store->set_host_cache_bytes(bytes);
+        return int(INSG_OK);
+    });
+}
+int insg_storage_clear(insg_storage *s)
+{
+    return storage_guarded(s, [&] {
+        s->store->clear();
+        return int(INSG_OK);
+    });
+}
+uint64_t insg_storage_device_bytes(insg_storage *s) { return s ? s->store->device_bytes() : 0; }
+uint64_t insg_storage_reserved_bytes(insg_storage *s) { return s ? s->store->reserved_bytes() : 0; }
+int insg_storage_stats(insg_storage *s, uint64_t *out6)
+{
+    return storage_guarded(s, [&] {
+        if (!out6) return insg::fail(INSG_E_ARG, "null output");
+        const insignia::StorageStats st = s->store->stats();
+        out6[0] = st.uploads; out6[1] = st.upload_bytes; out6[2] = st.evictions; out6[3] = st.hits; out6[4] = st.pinned_cache_hits;
+        out6[5] = st.prefetches;
+        return int(INSG_OK);
+    });
+}
+
 insg_engine *insg_engine_create(const char *index_path, const insg_engine_options *opt)
 {
     if (!index_path) {
@@ -78,6 +185,7 @@ insg_engine *insg_engine_create(const char *index_path, const insg_engine_option
         d.kv_bf16 = o.kv_dtype == INSG_KV_BF16;
         d.gate_elementwise = o.gate_elementwise != 0;
         d.accurate_trig = o.accurate_trig != 0;
+        d.launch_per_op = o.launch_per_op != 0;
         d.use_graph = o.use_graph != 0;
         d.use_pdl = o.use_pdl != 0;
         d.gemv_tcgen05 = o.gemv_tcgen05 != 0;
@@ -154,14 +262,6 @@ int insg_engine_generate(insg_engine *e, int first_token, int count, int *out_to
         return int(INSG_OK);
     });
 }
-int insg_engine_profile_token(insg_engine *e, int token, float *ms, uint64_t *bytes, int *launches)
-{
-    return guarded(e, [&] {
-        if (!ms || !bytes || !launches) return insg::fail(INSG_E_ARG, "null output");
-        e->dec->profile_token(token, ms, bytes, launches);
-        return int(INSG_OK);
-    });
-}
 int insg_engine_profile_gemv_chain(insg_engine *e, int replays, float *ms_per_token, uint64_t *bytes, int *launches)
 {
     return guarded(e, [&] {
@@ -170,11 +270,16 @@ int insg_engine_profile_gemv_chain(insg_engine *e, int replays, float *ms_per_to
         return int(INSG_OK);
     });
 }
-int insg_engine_set_trace(insg_engine *e, void *device_buffer)
+int insg_engine_set_prefetch_records(insg_engine *e, int records)
 {
-    if (!e) return insg::fail(INSG_E_ARG, "null engine");
-    e->ws->trace = device_buffer;
-    return INSG_OK;
+    return guarded(e, [&] {
+        e->dec->set_prefetch_records(records);
+        return int(INSG_OK);
+    });
+}
+int insg_engine_selftest_barrier_timeout(insg_engine *e)
+{
+    return guarded(e, [&] { return e->dec->selftest_barrier_timeout() ? 1 : 0; });
 }
 int insg_engine_position(insg_engine *e) { return e ? e->ws->position : INSG_E_ARG; }
 int insg_engine_set_position(insg_engine *e, int position)

@@ -15,7 +15,10 @@ Qwen35Weights::Qwen35Weights(const ModelFile &model, uint64_t device_budget_byte
 Qwen35Weights::~Qwen35Weights()
 {
     cudaStreamSynchronize(stream_);
-    for (auto &kv : packed_) cudaFree(const_cast<void *>(kv.second.data));
+    for (auto &kv : packed_) {
+        cudaFree(const_cast<void *>(kv.second.data));
+        storage_.unreserve(kv.second.bytes);
+    }
 }
 
 QuantMatrix Qwen35Weights::matrix(const std::string &base)
@@ -55,6 +58,13 @@ void Qwen35Weights::embed(int token, float *device_hidden)
     if (rc != INSG_OK) throw std::runtime_error(insg_last_error());
 }
 
+void Qwen35Weights::prefetch(const std::string &base)
+{
+    if (packed_.count(base + "#rec") || packed_.count(base + "#umma")) return; // the checkpoint-layout copy is not needed again
+    storage_.prefetch(base + ".weight");
+    storage_.prefetch(base + ".scales");
+}
+
 PackedMatrix Qwen35Weights::packed(const std::string &base, int layout)
 {
     const std::string key = base + (layout ? "#umma" : "#rec");
@@ -69,9 +79,18 @@ PackedMatrix Qwen35Weights::packed(const std::string &base, int layout)
         release(base);
         throw std::runtime_error("matrix shape not packable (rows % 16, cols % 128): " + base);
     }
+    // The packed copy is weight memory like any other: it is charged to the storage budget (unpinned checkpoint-layout
+    // copies are evicted to make room; the budget errors are the storage's).
+    try {
+        storage_.reserve(p.bytes);
+    } catch (...) {
+        release(base);
+        throw;
+    }
     void *d = nullptr;
     cudaError_t e = cudaMalloc(&d, p.bytes);
     if (e != cudaSuccess) {
+        storage_.unreserve(p.bytes);
         release(base);
         throw std::runtime_error(std::string("cudaMalloc packed matrix: ") + cudaGetErrorString(e));
     }
@@ -82,6 +101,7 @@ PackedMatrix Qwen35Weights::packed(const std::string &base, int layout)
     release(base); // the MLX copy becomes evictable again
     if (rc != INSG_OK || e != cudaSuccess) {
         cudaFree(d);
+        storage_.unreserve(p.bytes);
         throw std::runtime_error(rc != INSG_OK ? insg_last_error() : cudaGetErrorString(e));
     }
     p.data = d;

@@ -87,11 +87,8 @@ def gemv_packed(packed, x, rows=None, cols=None):
     return y.reshape(*x.shape[:-1], rows)
 
 
-def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, trace=None, layout=0, error_flag=None,
-               prep_partials=None, prep_rms=False, cols=None, tokens=1):
-    """``segments``: list of dicts with packed, out, rows, epilogue (+ packed2 / conv_state, conv_w / A_log, dt_bias /
-    prep, prep_w, prep_partials).  ``argmax``: dict(scratch, token_out[, token_feedback, token_log, position]) for the
-    logits epilogue.  With ``prologue="prepared"`` ``inp`` is the fp16 image [2][cols] a producer left through ``prep``."""
+def _gemv_op(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, layout=0, error_flag=None,
+             prep_partials=None, prep_rms=False, cols=None, tokens=1):
     op = GemvOp()
     op.in_, op.aux, op.norm_w, op.x_out = _p(inp), _p(aux), _p(norm_w), _p(x_out)
     op.cols, op.prologue, op.n_segments = cols or inp.shape[-1], PRO[prologue], len(segments)
@@ -106,12 +103,91 @@ def gemv_fused(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=Non
     if argmax:
         op.argmax_scratch, op.token_out = _p(argmax["scratch"]), _p(argmax["token_out"])
         op.token_feedback, op.token_log = _p(argmax.get("token_feedback")), _p(argmax.get("token_log"))
+        op.token_log_capacity = argmax["token_log"].numel() if argmax.get("token_log") is not None else 0
         op.position_inout = _p(argmax.get("position"))
-    op.trace = _p(trace)
     op.layout = layout
     op.error_flag = _p(error_flag)
     op.pdl = int(pdl)
+    return op
+
+
+def gemv_fused(inp, segments, **kw):
+    """``segments``: list of dicts with packed, out, rows, epilogue (+ packed2 / conv_state, conv_w / A_log, dt_bias /
+    prep, prep_w, prep_partials).  Keywords: prologue, aux, norm_w, x_out, pdl, layout, error_flag, prep_partials,
+    prep_rms, cols, tokens, and ``argmax``: dict(scratch, token_out[, token_feedback, token_log, position]) for the
+    logits epilogue.  With ``prologue="prepared"`` ``inp`` is the fp16 image [2][cols] a producer left through ``prep``."""
+    op = _gemv_op(inp, segments, **kw)
     check(_lib.lib().insg_gemv_fused(C.byref(op), _stream()))
+
+
+class Program:
+    """A recorded sequence of fused operations run by ONE persistent cooperative launch (``insg_program_*``): the
+    ``add_*`` methods take what :func:`gemv_fused`, :func:`deltanet_decode`, :func:`attention_step` and the embedding
+    lookup take.  Tensors handed to ``add_*`` must stay alive while the program exists."""
+
+    def __init__(self):
+        self._destroy = _lib.lib().insg_program_destroy
+        self._h = _lib.lib().insg_program_create()
+        if not self._h:
+            raise RuntimeError("insg_program_create failed")
+        self._keep = []
+
+    def close(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._destroy(h)
+
+    def __del__(self):
+        self.close()
+
+    def add_gemv(self, inp, segments, **kw):
+        op = _gemv_op(inp, segments, **kw)
+        self._keep.append((inp, segments, kw))
+        check(_lib.lib().insg_program_add_gemv(self._h, C.byref(op)))
+
+    def add_deltanet(self, state, q16, k16, v32, g32, beta32, out):
+        self._keep.append((state, q16, k16, v32, g32, beta32, out))
+        check(_lib.lib().insg_program_add_deltanet(self._h, _p(state), _p(q16), _p(k16), _p(v32), _p(g32), _p(beta32), _p(out)))
+
+    def add_attention(self, qraw, k_raw, v, q_w, k_w, k_cache, v_cache, out, position, max_context, scratch, position_offset=0,
+                      fast_trig=True):
+        op = AttnOp()
+        op.qraw, op.k_raw, op.v, op.q_norm_w, op.k_norm_w = _p(qraw), _p(k_raw), _p(v), _p(q_w), _p(k_w)
+        op.k_cache, op.v_cache = _p(k_cache), _p(v_cache)
+        op.out, op.position, op.position_offset, op.max_context = _p(out), _p(position), position_offset, max_context
+        op.kv_dtype = KV_BF16 if k_cache.dtype == torch.bfloat16 else KV_F32
+        op.fast_trig, op.scratch, op.scratch_bytes = int(fast_trig), _p(scratch), scratch.numel()
+        self._keep.append((qraw, k_raw, v, q_w, k_w, k_cache, v_cache, out, position, scratch))
+        check(_lib.lib().insg_program_add_attention(self._h, C.byref(op)))
+
+    def add_embed(self, weight, scales, out, device_row):
+        self._keep.append((weight, scales, out, device_row))
+        check(_lib.lib().insg_program_add_embed(self._h, _p(weight), _p(scales), _p(out), _p(device_row), weight.shape[0],
+                                                weight.shape[1] * 8))
+
+    def finalize(self):
+        check(_lib.lib().insg_program_finalize(self._h))
+
+    def set_option(self, key: str, value: int):
+        check(_lib.lib().insg_program_set_option(self._h, key.encode(), value))
+
+    def run(self, n_tokens=1, token=-1, position=-1, device_token=None, device_position=None, error_flag=None):
+        check(_lib.lib().insg_program_run(self._h, n_tokens, token, position, _p(device_token), _p(device_position), _p(error_flag),
+                                          _stream()))
+
+    def recover(self):
+        check(_lib.lib().insg_program_recover(self._h, _stream()))
+
+    def selftest_barrier_timeout(self, timeout_ns, error_flag):
+        check(_lib.lib().insg_program_selftest_barrier_timeout(self._h, timeout_ns, _p(error_flag), _stream()))
+
+    @property
+    def phase_count(self) -> int:
+        return _lib.lib().insg_program_phase_count(self._h)
+
+    @property
+    def weight_bytes(self) -> int:
+        return _lib.lib().insg_program_weight_bytes(self._h)
 
 
 def argmax_scratch(device):

@@ -93,6 +93,48 @@ def test_greedy_tokens_identical_to_reference(cuda, full_ckpt):
         ref.close()
 
 
+@pytest.fixture(scope="module")
+def cfg3_reference(cuda, full_ckpt):
+    """BASELINE configs[3] on the reference engine: a 512-token seeded uniform-random prompt fed token by token
+    (src/generate_ids.cu:4), then 256 greedy tokens; also the smallest gap between its two largest logits on the way."""
+    n_prompt, n_gen = 512, 256
+    prompt = [int(t) for t in np.random.default_rng(3).integers(0, 248320, n_prompt)]
+    ref = ref_engine.RefEngine(full_ckpt[1], max_context=n_prompt + n_gen + 4)
+    try:
+        for t in prompt:
+            ref.forward_token(t)
+        first = ref.logits_argmax()
+        want, t, min_gap = [], first, 1e9
+        for _ in range(n_gen):
+            t = ref.decode_token(t)
+            want.append(t)
+            top2 = np.partition(ref.read("logits", 248320), -2)[-2:]
+            min_gap = min(min_gap, float(top2[1] - top2[0]))
+        hidden = ref.read("hidden", 4096)
+    finally:
+        ref.close()
+    print(f"configs[3]: smallest top-2 logit gap of the reference over {n_gen} steps: {min_gap:.3e}")
+    return prompt, first, want, min_gap, hidden
+
+
+@pytest.mark.parametrize("per_op", [False, True])
+def test_cfg3_512_prompt_256_generated_identical_to_reference(cuda, full_ckpt, cfg3_reference, per_op):
+    """The north-star identity check at its full length: 512 + 256 tokens, every generated id equal to the reference's,
+    through the persistent token kernel and through the launch-per-operation path."""
+    from insignia_b200.engine import Engine
+
+    prompt, first, want, min_gap, ref_hidden = cfg3_reference
+    with Engine(full_ckpt[1], max_context=len(prompt) + len(want) + 4, launch_per_op=per_op) as e:
+        for t in prompt:
+            e.forward_token(t)
+        assert e.logits_argmax() == first
+        got = e.generate(first, len(want))
+        assert got == want, (min_gap, [i for i, (a, b) in enumerate(zip(got, want)) if a != b][:3])
+        assert e.position == len(prompt) + len(want)
+        h = e.read("hidden")
+        assert cos(h, ref_hidden) >= 0.9999 and np.max(np.abs(h - ref_hidden)) <= 2e-2 * np.abs(ref_hidden).max()
+
+
 def test_prompt_in_passes_of_four_then_greedy_tokens_identical_to_reference(cuda, full_ckpt):
     """The prompt through forward_tokens (four tokens per pass over the weights), then greedy decode: same ids as the
     reference fed token by token."""

@@ -91,22 +91,15 @@ def test_gemv_mlx_ragged_rows(cuda):
         assert np.max(np.abs(y - y64)) <= 2e-6 * max(1.0, np.abs(y64).max()) * np.sqrt(cols)
 
 
-@pytest.mark.parametrize("unr,ring", [(2, 0), (3, 0), (4, 0), (4, 2), (4, 4)])
-def test_gemv_packed_reference_fixture(cuda, unr, ring):
+def test_gemv_packed_reference_fixture(cuda):
     from insignia_b200 import ops
 
-    ops.tune("gemv_unr", unr)
-    ops.tune("gemv_ring", ring)
-    try:
-        w, s, x, expected = fx.mxfp4_mlx(rows=4096)
-        packed = ops.repack(dev(w), dev(s))
-        y = host(ops.gemv_packed(packed, dev(x)))
-        assert fx.max_rel(y, expected, 1e-5) <= 3e-4
-        y64 = orc.gemv_mlx_f64(w, s, x)
-        assert np.max(np.abs(y - y64)) <= 1e-5 * np.abs(y64).max()
-    finally:
-        ops.tune("gemv_unr", 4)
-        ops.tune("gemv_ring", 0)
+    w, s, x, expected = fx.mxfp4_mlx(rows=4096)
+    packed = ops.repack(dev(w), dev(s))
+    y = host(ops.gemv_packed(packed, dev(x)))
+    assert fx.max_rel(y, expected, 1e-5) <= 3e-4
+    y64 = orc.gemv_mlx_f64(w, s, x)
+    assert np.max(np.abs(y - y64)) <= 1e-5 * np.abs(y64).max()
 
 
 @pytest.mark.parametrize("rows,cols", [(4096, 4096), (1024, 12288), (32, 4096), (16, 128), (48, 1152), (2048, 8192), (12352, 4096),
@@ -123,11 +116,7 @@ def test_gemv_packed_shapes_vs_oracle(cuda, rows, cols):
     yref = orc.gemv_mlx(w, s, x, warps=2)
     tol = 4e-6 * np.abs(y64).max() + 1e-7
     assert np.max(np.abs(y - y64)) <= tol
-    ops.tune("gemv_ring", 4)  # the shared-memory ring variant streams the same records: identical sums
-    try:
-        assert np.array_equal(host(ops.gemv_packed(packed, dev(x))), y)
-    finally:
-        ops.tune("gemv_ring", 0)
+    assert np.array_equal(host(ops.gemv_packed(packed, dev(x))), y)  # the same sums on every launch
     # the restated reference order is itself this close to the exact sum
     assert np.max(np.abs(yref - y64)) <= tol * 4
 
