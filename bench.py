@@ -65,7 +65,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gemv", default="mma", choices=["mma", "tcgen05"], help="GEMV kernel family of the engine")
     ap.add_argument("--tune", action="append", default=[], help="kernel tuning knob key=value (insg_tune_set)")
-    ap.add_argument("--launch-per-op", action="store_true", help="one launch per fused operation (CUDA graph) instead of the persistent token kernel")
+    ap.add_argument("--persistent", action="store_true", help="the persistent token kernel (one cooperative launch per token) instead of the graph of launches")
     ap.add_argument("--prefetch", type=int, default=-1, help="persistent kernel: weight records per warp kept prefetched into L2 (-1 = default)")
     return ap.parse_args()
 
@@ -185,9 +185,9 @@ def run_native(args, rank, world, local_rank):
         k, v = kv.split("=")
         ops.tune(k, int(v))
     eng = Engine(idx, max_context=ctx, budget_bytes=16 << 30, kv_bf16=args.kv_bf16, device=local_rank, gemv_tcgen05=args.gemv == "tcgen05",
-                 launch_per_op=args.launch_per_op)
+                 persistent=args.persistent)
     if args.prefetch >= 0:
-        eng.set_prefetch_records(args.prefetch)
+        eng.set_program_option("prefetch_records", args.prefetch)
     rng = np.random.default_rng(args.seed + 1000 * rank)
     prompt = rng.integers(0, VOCAB, args.prompt)
     stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)

@@ -400,14 +400,14 @@ typedef struct insg_engine_options {
                                      (src/qwen_kernels.cu:36); 1: element-wise gate as its NumPy
                                      tools (tools/reference_all_layers.py:13)                   */
     int accurate_trig;            /* 0: fast intrinsics for RoPE as the reference; 1: sincosf   */
-    int use_graph;                /* launch_per_op: 1 = capture the token step in a CUDA graph  */
-    int use_pdl;                  /* launch_per_op: 1 = programmatic dependent launch between kernels */
+    int use_graph;                /* 1: capture the token step in a CUDA graph                  */
+    int use_pdl;                  /* 1: programmatic dependent launch between kernels           */
     int gemv_tcgen05;             /* 1: tcgen05 kind::mxf4 GEMV; 0: mma.sync register-streaming GEMV */
     int n_layers;                 /* 0 = 32                                                     */
     int vocab;                    /* 0 = 248320 (rows of lm_head used for logits)               */
     int device;                   /* CUDA device ordinal                                        */
-    int launch_per_op;            /* 0: a token step is ONE persistent cooperative launch (insg_program_*); 1: one launch per
-                                     fused operation (162 per token), replayed from a CUDA graph when use_graph is set */
+    int persistent;               /* 0: one launch per fused operation (162 per token), replayed from a CUDA graph when
+                                     use_graph is set; 1: a token step is ONE persistent cooperative launch (insg_program_*) */
     int gemv_unprepared;          /* 0: a GEMV that writes the residual stream or the SwiGLU output leaves the next
                                      GEMV's input prepared (insg_gemv_segment.prep); 1: every GEMV converts its own */
 } insg_engine_options;
@@ -435,14 +435,15 @@ INSG_API int insg_engine_mtp_draft(insg_engine *e, int token);
  * Synchronises once at the end.  No reference counterpart (its loop is src/generate_ids.cu:4). */
 INSG_API int insg_engine_generate(insg_engine *e, int first_token, int count, int *out_tokens /* host */);
 /* The fused-GEMV operations of one token step alone, run `replays` (1..64) times between two CUDA events (one
- * persistent launch per replay, or with launch_per_op a CUDA graph of launches with dependent-launch overlap):
+ * CUDA graph of launches with dependent-launch overlap per replay, or with `persistent` one persistent launch):
  * *ms_per_token = time of one replay, *bytes = the algorithmic weight bytes of those operations, *launches = their
  * count.  Needs one forwarded token first.  The sequence state is meaningless afterwards (call insg_engine_reset).
  * Synchronises.  No reference counterpart. */
 INSG_API int insg_engine_profile_gemv_chain(insg_engine *e, int replays, float *ms_per_token, uint64_t *bytes, int *launches);
-/* Prefetch distance of the persistent token kernel: 1088-byte weight records each warp keeps requested into L2 ahead
- * of its own consumption (0 = off, < 0 = the default). */
-INSG_API int insg_engine_set_prefetch_records(insg_engine *e, int records);
+/* Sets an option of the engine's persistent token program (see insg_program_set_option), now and for programs it builds
+ * later: "prefetch_records" = 1088-byte weight records each warp keeps requested into L2 ahead of its own consumption
+ * (0 = off). */
+INSG_API int insg_engine_set_program_option(insg_engine *e, const char *key /* host */, long long value);
 /* Failure-detection self-test of the persistent token kernel: one run whose first grid barrier can never be met, with a
  * 2 ms wait limit.  Returns 1 when the kernel gave up, raised its error status and the engine recovered; 0 when the
  * status was not raised; negative on error.  Synchronises; call insg_engine_reset afterwards. */

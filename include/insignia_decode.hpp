@@ -3,9 +3,9 @@
 // Drop-in for the reference header of the same name (include/insignia_decode.hpp:5-24,
 // behaviour: src/decode.cu:9-69): same classes, public fields, methods and error
 // strings.  Underneath, each layer is five fused sm_100a operations instead of
-// eighteen launches; a token step (forward_token / decode_token / generate) is one
-// persistent cooperative launch that walks all of them, or, optionally, 162 launches
-// chained with programmatic dependent launch and replayed from a CUDA graph.
+// eighteen launches; a token step (forward_token / decode_token / generate) is 162
+// launches chained with programmatic dependent launch and replayed from a CUDA graph,
+// or, optionally, one persistent cooperative launch that walks all of them.
 // Additive members are marked.
 #pragma once
 #include "insignia_qwen35.hpp"
@@ -27,9 +27,11 @@ struct DecodeOptions {
     bool gate_elementwise = false; // false: head-broadcast attention gate (src/qwen_kernels.cu:36);
                                    // true: element-wise gate (tools/reference_all_layers.py:13)
     bool accurate_trig = false;    // false: __powf/__sinf/__cosf for RoPE (src/ops.cu:9); true: powf/sincosf
-    bool launch_per_op = false;    // false: the token step is one persistent cooperative launch (grid barriers between the
-                                   // fused operations); true: one launch per fused operation
-    bool use_graph = true;         // launch_per_op: replay the token step from a CUDA graph
+    bool persistent = false;       // false: one launch per fused operation (162 per token); true: the token step is ONE
+                                   // persistent cooperative launch with grid barriers between the operations (measured
+                                   // slower than the graph of launches on B200: the barrier chain costs what the
+                                   // dependent-launch chain costs, and its phases cannot overlap one another's tails)
+    bool use_graph = true;         // launch per operation: replay the token step from a CUDA graph
     bool use_pdl = true;           // programmatic dependent launch between kernels
     bool gemv_tcgen05 = false;     // true: weights through tcgen05.mma kind::mxf4 (TMA-fed); false: the mma.sync streaming kernel
     bool prepared_inputs = true;   // a GEMV that writes the residual stream or the SwiGLU output also leaves the next GEMV's
@@ -91,12 +93,13 @@ public:
     uint64_t launch_count() const noexcept { return launches_; }
     cudaStream_t execution_stream();
     // Additive: the fused-GEMV operations of one token step alone (no DeltaNet, attention or embedding work between
-    // them), run `replays` times between two events: as one persistent launch each, or with launch_per_op as a graph
-    // of launches with dependent-launch overlap.  Gives the weight-streaming time of a token.  The sequence state
+    // them), run `replays` times between two events: as a graph of launches with dependent-launch overlap, or with
+    // `persistent` as one persistent launch each.  Gives the weight-streaming time of a token.  The sequence state
     // (hidden, convolution history) is meaningless afterwards: reset the workspace before decoding again.
     void profile_gemv_chain(int replays, float *ms_per_token, uint64_t *bytes, int *launches);
-    // Additive: the persistent program's prefetch distance (records per warp, 0 = off); takes effect at once.
-    void set_prefetch_records(int records);
+    // Additive: an option of the persistent program (insg_program_set_option), e.g. "prefetch_records"; takes effect at
+    // once and is applied again to programs built later.
+    void set_program_option(const std::string &key, long long value);
     // Additive: failure-detection self-test of the persistent launch: one run whose first grid barrier can never be
     // met, with a short wait limit.  Returns true when the kernel gave up, raised its error status and the engine
     // recovered.  The sequence state is meaningless afterwards (reset the workspace).

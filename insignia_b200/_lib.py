@@ -37,7 +37,7 @@ class AttnOp(C.Structure):
 class EngineOptions(C.Structure):
     _fields_ = [("device_budget_bytes", u64), ("max_context", i32), ("kv_dtype", i32), ("gate_elementwise", i32),
                 ("accurate_trig", i32), ("use_graph", i32), ("use_pdl", i32), ("gemv_tcgen05", i32), ("n_layers", i32), ("vocab", i32),
-                ("device", i32), ("launch_per_op", i32), ("gemv_unprepared", i32)]
+                ("device", i32), ("persistent", i32), ("gemv_unprepared", i32)]
 
 
 # name -> (restype, argtypes); every symbol include/insignia_b200.h declares
@@ -118,7 +118,7 @@ SIGNATURES = {
     "insg_engine_mtp_draft": (i32, [vp, i32]),
     "insg_engine_generate": (i32, [vp, i32, i32, C.POINTER(i32)]),
     "insg_engine_profile_gemv_chain": (i32, [vp, i32, vp, vp, vp]),
-    "insg_engine_set_prefetch_records": (i32, [vp, i32]),
+    "insg_engine_set_program_option": (i32, [vp, C.c_char_p, C.c_longlong]),
     "insg_engine_selftest_barrier_timeout": (i32, [vp]),
     "insg_engine_position": (i32, [vp]),
     "insg_engine_set_position": (i32, [vp, i32]),

@@ -467,7 +467,7 @@ __device__ __forceinline__ void gemv_finish(const GemvParams &p, const GemvRange
     }
 
     // ---- this CTA's share of sum(out^2), for the RMSNorm of the launch that consumes the prepared image ----
-    if (p.prep_partials_out) {
+    if (p.prep_partials_out && c < G) {
         ss = warp_sum(ss);
         __syncthreads(); // scratch[0] was the prologue's
         if (lane == 0) scratch[warp] = ss;
@@ -482,7 +482,7 @@ __device__ __forceinline__ void gemv_finish(const GemvParams &p, const GemvRange
             for (int i = G + tid; i < kMaxGrid; i += kThreads) p.prep_partials_out[i] = 0.f;
     }
     // ---- arg-max over the rows this launch produced (lm_head) ----------------
-    if (p.argmax_partial) {
+    if (p.argmax_partial && c < G) { // CTA-uniform (a persistent grid may be larger than the G CTAs that take part)
         float *sv = scratch + 16;
         int *si = reinterpret_cast<int *>(scratch + 32);
 #pragma unroll

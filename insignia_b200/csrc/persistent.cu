@@ -27,6 +27,11 @@
 
 namespace insg {
 
+// Records per register prefetch chunk in the phases: one fewer than the stand-alone kernel's, which sits exactly at the
+// register ceiling; the loop here also carries the phase bookkeeping and would spill.  The chunk depth does not change
+// the order of any sum.
+constexpr int kPersistUnr = 2;
+
 enum { PH_GEMV = 0, PH_DELTANET = 1, PH_ATTENTION = 2, PH_EMBED = 3 };
 
 struct DnParams {
@@ -48,7 +53,7 @@ struct AttnPhase {
     int bf16;
 };
 
-struct Phase {
+struct alignas(16) Phase {
     int type;
     int next_gemv; // index of the next GEMV phase after this one, or -1
     int grid;      // GEMV: CTAs that take part (the stand-alone kernel's grid for the same operation)
@@ -81,7 +86,21 @@ struct RunArgs {
     unsigned long long timeout_ns;
     int arrivals;                // CTAs a barrier waits for (the grid size; a self-test passes more)
     int pf_records;              // per-warp L2 prefetch distance in records, 0 = off
+    int work_offset;             // bytes of dynamic shared memory taken by the program copy; the phases' buffers follow
+    unsigned long long *times;   // development builds (INSG_PHASE_TIMES): [step][CTA][4] nanosecond stamps, or null
 };
+
+// Development aid, compiled in only with -DINSG_PHASE_TIMES: every CTA stamps the clock at four points of every phase.
+#ifdef INSG_PHASE_TIMES
+#define INSG_STAMP(slot)                                                                                              \
+    do {                                                                                                              \
+        if (a.times && threadIdx.x == 0) a.times[(size_t(step) * gridDim.x + blockIdx.x) * 4 + (slot)] = globaltimer_ns(); \
+    } while (0)
+#else
+#define INSG_STAMP(slot) \
+    do {                 \
+    } while (0)
+#endif
 
 __device__ __forceinline__ unsigned long long globaltimer_ns()
 {
@@ -128,12 +147,15 @@ __device__ __forceinline__ bool grid_barrier(const RunArgs &a, unsigned target, 
 }
 
 // ---- L2 prefetch cursor -------------------------------------------------------------------------------------------
-// Runs along this warp's records of the GEMV phases, in program order, wrapping to the next token while tokens remain.
+// One cursor per CTA, run by its last warp: it walks the CTA's records of the GEMV phases in program order (wrapping to
+// the next token while tokens remain) and stays a fixed number of records ahead of the phase being consumed.  Records
+// of one (tile, matrix) run are contiguous in memory, and so are consecutive runs of one matrix: a lane takes one run
+// and issues ONE bulk prefetch for the part of it inside the range (the copy engine is slow on many small requests).
 struct PfCursor {
     int ph;       // phase the cursor is in, -1 = finished
-    int u, end;   // next record and end of this warp's share in that phase
+    int u, end;   // next record and end of this CTA's share in that phase
     int wraps;    // token wraps still allowed
-    int ahead;    // records between the end of the phase being consumed and the cursor
+    int ahead;    // records between the end of the share being consumed and the cursor
 };
 
 __device__ __forceinline__ GemvRange phase_range(const Phase &P, int c, int warp)
@@ -142,47 +164,51 @@ __device__ __forceinline__ GemvRange phase_range(const Phase &P, int c, int warp
     return gemv_range(P.g, P.grid, c, warp);
 }
 
-__device__ __forceinline__ void pf_enter(const RunArgs &a, PfCursor &pf, int ph, int c, int warp)
+__device__ __forceinline__ void pf_enter(const Phase *prog, PfCursor &pf, int ph, int c)
 {
     pf.ph = ph;
     if (ph < 0) return;
-    const GemvRange r = phase_range(a.phases[ph], c, warp);
-    pf.u = r.ua;
-    pf.end = r.ub;
+    const GemvRange r = phase_range(prog[ph], c, 0);
+    pf.u = r.a;
+    pf.end = r.b;
 }
 
-__device__ __forceinline__ void pf_next_phase(const RunArgs &a, PfCursor &pf, int c, int warp)
+__device__ __forceinline__ void pf_next_phase(const RunArgs &a, const Phase *prog, PfCursor &pf, int c)
 {
-    int nx = a.phases[pf.ph].next_gemv;
+    int nx = prog[pf.ph].next_gemv;
     if (nx < 0) {
         if (pf.wraps > 0) { pf.wraps--; nx = a.first_gemv; }
     }
-    pf_enter(a, pf, nx, c, warp);
+    pf_enter(prog, pf, nx, c);
 }
 
-// Called when the warp starts consuming GEMV phase `ph` (its share is [r.ua, r.ub)): the cursor is moved past that
-// share if it is still inside it, then advanced until it is pf_records ahead of the share's end.
-__device__ __forceinline__ void pf_advance(const RunArgs &a, PfCursor &pf, int ph, const GemvRange &r, int c, int warp, int lane)
+// Called by one warp when the CTA starts consuming GEMV phase `ph` (its share is [ra, rb)): the cursor is moved past
+// that share if it is still inside it, then advanced until it is `distance` records ahead of the share's end.
+__device__ __forceinline__ void pf_advance(const RunArgs &a, const Phase *prog, PfCursor &pf, int ph, int ra, int rb, int c, int lane)
 {
-    if (a.pf_records <= 0 || pf.ph < 0) return;
-    pf.ahead -= r.ub - r.ua;
+    const int distance = a.pf_records * kWarps;
+    if (pf.ph < 0) return;
+    pf.ahead -= rb - ra;
     if (pf.ahead < 0) { // the cursor is still inside the share being consumed now: move it to the phase after
         pf.ahead = 0;
         pf.ph = ph;
-        pf_next_phase(a, pf, c, warp);
+        pf_next_phase(a, prog, pf, c);
     }
     int guard = 0;
-    while (pf.ph >= 0 && pf.ahead < a.pf_records && ++guard < 64) {
-        const GemvParams &q = a.phases[pf.ph].g;
-        const int n = min(a.pf_records - pf.ahead, pf.end - pf.u);
-        for (int i = lane; i < n; i += 32) {
-            UnitIt it;
-            it_set(q, it, pf.u + i);
-            if (it.ptr) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(it.ptr), "r"(kRec) : "memory");
+    while (pf.ph >= 0 && pf.ahead < distance && ++guard < 64) {
+        const GemvParams &q = prog[pf.ph].g;
+        const int n = min(distance - pf.ahead, pf.end - pf.u);
+        if (n > 0) {
+            const int nkb = q.nkb, u0 = pf.u, u1 = pf.u + n;
+            for (int tm = u0 / nkb + lane; tm * nkb < u1; tm += 32) { // one run per lane
+                const int lo = max(tm * nkb, u0), hi = min((tm + 1) * nkb, u1);
+                const uint8_t *ptr = run_base(q, tm) + size_t(lo - tm * nkb) * kRec;
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"((hi - lo) * kRec) : "memory");
+            }
         }
         pf.u += n;
         pf.ahead += n;
-        if (pf.u >= pf.end) pf_next_phase(a, pf, c, warp);
+        if (pf.u >= pf.end) pf_next_phase(a, prog, pf, c);
     }
 }
 
@@ -521,6 +547,18 @@ __global__ void __launch_bounds__(kThreads, 1) persistent_token_kernel(const __g
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = int(gridDim.x), c = int(blockIdx.x);
 
+    // The program is copied into shared memory once: every descriptor read of every phase (the current one, the next one
+    // whose first chunks are issued early, the ones the prefetch cursor walks) is then an on-chip read.  From global
+    // memory each of them would be an L2 round trip, several of them dependent on one another, after every barrier
+    // (the barrier's acquire drops the SM's L1 contents).
+    Phase *prog = reinterpret_cast<Phase *>(smem_raw);
+    uint8_t *work = smem_raw + a.work_offset;
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.phases);
+        uint4 *dst = reinterpret_cast<uint4 *>(prog);
+        const int n16 = int(size_t(a.nphases) * sizeof(Phase) / 16);
+        for (int i = tid; i < n16; i += kThreads) dst[i] = src[i];
+    }
     if (tid == 0) {
         s_base = ld_acquire(&a.sync->base);
         if (c == 0) {
@@ -531,51 +569,64 @@ __global__ void __launch_bounds__(kThreads, 1) persistent_token_kernel(const __g
     __syncthreads();
     unsigned target = s_base;
 
-    PfCursor pf;
-    pf.wraps = a.n_tokens - 1;
-    pf.ahead = 0;
-    pf_enter(a, pf, a.first_gemv, c, warp);
+    // the prefetch cursors live in shared memory between phases: they must not cost registers in the record loop
+    __shared__ PfCursor s_pf;
+    if (warp == kWarps - 1) {
+        PfCursor pf;
+        pf.wraps = a.n_tokens - 1;
+        pf.ahead = 0;
+        pf_enter(prog, pf, a.first_gemv, c);
+        if (lane == 0) s_pf = pf;
+        __syncwarp();
+    }
 
     const int total = a.n_tokens * a.nphases;
     int step = 0, ph = 0;
     while (step < total) {
-        if (a.phases[ph].type == PH_GEMV) {
+        if (prog[ph].type == PH_GEMV) {
             // A run of consecutive GEMV phases.  The chunk registers live only inside this scope, so the recurrent phases
             // below have the whole register file; inside the run the next phase's first chunks are issued before the
             // current phase is closed and stay in flight across its epilogue and the barrier.
-            Chunk<kUnr> A, B;
+            // Every CTA runs every stage, CTAs beyond the phase's grid with an empty range: the weight loads must not sit
+            // inside a branch (the compiler then waits for them where the branch rejoins, and a phase that keeps its loads
+            // in flight across stages streams at two thirds of the rate).
+            Chunk<kPersistUnr> A, B;
             UnitIt lit;
-            GemvRange r = phase_range(a.phases[ph], c, warp);
-            if (c < a.phases[ph].grid) gemv_issue_first<kUnr>(a.phases[ph].g, r, A, B, lit, lane);
+            GemvRange r = phase_range(prog[ph], c, warp);
+            gemv_issue_first<kPersistUnr>(prog[ph].g, r, A, B, lit, lane);
             for (;;) {
-                const Phase &P = a.phases[ph];
+                const Phase &P = prog[ph];
                 const GemvParams &p = P.g;
-                pf_advance(a, pf, ph, r, c, warp, lane);
+                INSG_STAMP(0);
+                if (a.pf_records > 0 && warp == kWarps - 1) {
+                    PfCursor pf = s_pf;
+                    pf_advance(a, prog, pf, ph, r.a, r.b, c, lane);
+                    __syncwarp();
+                    if (lane == 0) s_pf = pf;
+                    __syncwarp();
+                }
                 const int nph = ph + 1 < a.nphases ? ph + 1 : 0;
                 const bool more = step + 1 < total;
-                const bool chain = more && a.phases[nph].type == PH_GEMV;
-                GemvRange rn = GemvRange{0, 0, 0, 0, 0};
-                if (c < P.grid) {
-                    const int xstride = p.cols + 8;
-                    __half *xs = reinterpret_cast<__half *>(smem_raw);
-                    float *rec = reinterpret_cast<float *>(smem_raw + size_t(2) * xstride * sizeof(__half));
-                    float *scratch = rec + size_t(kWarps) * p.slots * 16;
-                    gemv_publish_range(r, sh, lane, warp);
-                    uint2 wpre[kPreVec];
-                    preload_norm_weights(ProIn{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue}, wpre);
-                    float inv_alpha[1];
-                    gemv_activation<1>(p, xs, xstride, scratch, wpre, inv_alpha);
-                    gemv_stream<kUnr, 1>(p, r, A, B, lit, xs, xstride, rec + size_t(warp) * p.slots * 16, inv_alpha, lane);
-                    if (chain) {
-                        rn = phase_range(a.phases[nph], c, warp);
-                        if (c < a.phases[nph].grid) gemv_issue_first<kUnr>(a.phases[nph].g, rn, A, B, lit, lane);
-                    }
-                    __syncthreads();
-                    gemv_finish<1>(p, r, P.grid, c, rec, scratch, sh);
-                } else if (chain) {
-                    rn = phase_range(a.phases[nph], c, warp);
-                    if (c < a.phases[nph].grid) gemv_issue_first<kUnr>(a.phases[nph].g, rn, A, B, lit, lane);
-                }
+                const bool chain = more && prog[nph].type == PH_GEMV;
+                const int xstride = p.cols + 8;
+                __half *xs = reinterpret_cast<__half *>(work);
+                float *rec = reinterpret_cast<float *>(work + size_t(2) * xstride * sizeof(__half));
+                float *scratch = rec + size_t(kWarps) * p.slots * 16;
+                gemv_publish_range(r, sh, lane, warp);
+                uint2 wpre[kPreVec];
+                preload_norm_weights(ProIn{p.in, p.aux, p.norm_w, p.x_out, p.cols, p.prologue}, wpre);
+                float inv_alpha[1];
+                gemv_activation<1>(p, xs, xstride, scratch, wpre, inv_alpha);
+                INSG_STAMP(1);
+                gemv_stream<kPersistUnr, 1>(p, r, A, B, lit, xs, xstride, rec + size_t(warp) * p.slots * 16, inv_alpha, lane);
+                // the next phase's first chunks go out now and stay in flight across this phase's closing and the barrier
+                const Phase &N = prog[chain ? nph : ph];
+                const GemvRange rn = chain ? phase_range(N, c, warp) : GemvRange{0, 0, 0, 0, 0};
+                gemv_issue_first<kPersistUnr>(N.g, rn, A, B, lit, lane);
+                __syncthreads();
+                INSG_STAMP(2);
+                gemv_finish<1>(p, r, P.grid, c, rec, scratch, sh);
+                INSG_STAMP(3);
                 if (more) {
                     target += unsigned(a.arrivals);
                     if (!grid_barrier(a, target, &s_ok)) return;
@@ -586,15 +637,17 @@ __global__ void __launch_bounds__(kThreads, 1) persistent_token_kernel(const __g
                 r = rn;
             }
         } else {
-            const Phase &P = a.phases[ph];
+            const Phase &P = prog[ph];
+            INSG_STAMP(0);
             if (P.type == PH_DELTANET) {
-                deltanet_phase(P.d, smem_raw, c);
+                deltanet_phase(P.d, work, c);
             } else if (P.type == PH_ATTENTION) {
-                if (P.a.bf16) attention_phase<true>(P.a.p, smem_raw, G, c);
-                else attention_phase<false>(P.a.p, smem_raw, G, c);
+                if (P.a.bf16) attention_phase<true>(P.a.p, work, G, c);
+                else attention_phase<false>(P.a.p, work, G, c);
             } else if (P.type == PH_EMBED) {
                 embed_phase(P.e, c);
             }
+            INSG_STAMP(3);
             if (step + 1 < total) {
                 target += unsigned(a.arrivals);
                 if (!grid_barrier(a, target, &s_ok)) return;
@@ -619,13 +672,15 @@ struct insg_program {
     std::vector<Phase> phases;
     Phase *d_phases = nullptr;
     SyncState *d_sync = nullptr;
-    size_t smem = 0;
+    size_t smem = 0;      // largest working area of any phase
+    size_t prog_bytes = 0; // the program copy in front of it
     int grid = 0;
     int device = 0;
     bool final = false;
     int pf_records = 24;
     unsigned long long timeout_ns = 2000000000ull;
     uint64_t weight_bytes = 0;
+    unsigned long long *times = nullptr;
 };
 
 namespace {
@@ -743,8 +798,11 @@ int insg_program_finalize(insg_program *g)
     cudaError_t e = cudaFuncSetAttribute(persistent_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(persistent)");
     g->smem = std::max<size_t>(g->smem, 1024);
+    g->prog_bytes = (g->phases.size() * sizeof(Phase) + 127) / 128 * 128;
+    if (g->prog_bytes + g->smem > 220 * 1024)
+        return fail(INSG_E_LIMIT, "program: too many operations for the shared-memory copy of the program (about 180 with full-size GEMVs)");
     int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, persistent_token_kernel, kThreads, g->smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, persistent_token_kernel, kThreads, g->prog_bytes + g->smem);
     if (e != cudaSuccess) return cuda_fail(e, "occupancy query");
     if (per_sm < 1) return fail(INSG_E_LIMIT, "program: the kernel does not fit an SM");
     e = cudaMalloc(&g->d_phases, g->phases.size() * sizeof(Phase));
@@ -765,6 +823,9 @@ int insg_program_set_option(insg_program *g, const char *key, long long value)
     const std::string k = key;
     if (k == "prefetch_records") g->pf_records = int(std::max(0ll, std::min(value, 4096ll)));
     else if (k == "timeout_ns") g->timeout_ns = (unsigned long long)std::max(1000ll, value);
+#ifdef INSG_PHASE_TIMES
+    else if (k == "phase_times") g->times = reinterpret_cast<unsigned long long *>(value);
+#endif
     else return fail(INSG_E_ARG, "program: unknown option");
     return INSG_OK;
 }
@@ -788,9 +849,11 @@ static int program_launch(insg_program *g, int n_tokens, int token, int position
     a.timeout_ns = g->timeout_ns;
     a.arrivals = arrivals;
     a.pf_records = g->pf_records;
+    a.work_offset = int(g->prog_bytes);
+    a.times = g->times;
     void *args[] = {&a};
     const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(persistent_token_kernel), dim3(g->grid), dim3(kThreads), args,
-                                                      g->smem, stream);
+                                                      g->prog_bytes + g->smem, stream);
     if (e != cudaSuccess) return cuda_fail(e, "cooperative launch");
     return INSG_OK;
 }

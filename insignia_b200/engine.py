@@ -23,11 +23,11 @@ class Engine:
     def __init__(self, index_path: str, max_context: int = 4096, budget_bytes: int = 16 << 30, kv_bf16: bool = False,
                  gate_elementwise: bool = False, accurate_trig: bool = False, use_graph: bool = True,
                  use_pdl: bool = True, n_layers: int = 32, vocab: int = 248320, device: int = 0,
-                 gemv_tcgen05: bool = False, prepared_inputs: bool = True, launch_per_op: bool = False):
-        """``launch_per_op=False`` (default): a token step is one persistent cooperative launch; ``True``: one launch per
-        fused operation (replayed from a CUDA graph when ``use_graph``)."""
+                 gemv_tcgen05: bool = False, prepared_inputs: bool = True, persistent: bool = False):
+        """``persistent=False`` (default): one launch per fused operation, replayed from a CUDA graph when ``use_graph``;
+        ``True``: a token step is one persistent cooperative launch (``insg_program_*``)."""
         o = EngineOptions(budget_bytes, max_context, int(kv_bf16), int(gate_elementwise), int(accurate_trig),
-                          int(use_graph), int(use_pdl), int(gemv_tcgen05), n_layers, vocab, device, int(launch_per_op),
+                          int(use_graph), int(use_pdl), int(gemv_tcgen05), n_layers, vocab, device, int(persistent),
                           int(not prepared_inputs))
         self.vocab = vocab
         self._destroy = _lib.lib().insg_engine_destroy  # held here: module globals may be gone when __del__ runs at exit
@@ -83,9 +83,10 @@ class Engine:
         check(_lib.lib().insg_engine_profile_gemv_chain(self._h, replays, C.byref(ms), C.byref(by), C.byref(ln)))
         return {"ms_per_token": ms.value, "bytes": by.value, "launches": ln.value}
 
-    def set_prefetch_records(self, records: int):
-        """Prefetch distance of the persistent token kernel (weight records per warp kept requested into L2); 0 = off."""
-        check(_lib.lib().insg_engine_set_prefetch_records(self._h, records))
+    def set_program_option(self, key: str, value: int):
+        """Option of the persistent token program, e.g. ``prefetch_records`` (weight records per warp kept requested into
+        L2 ahead of consumption; 0 = off)."""
+        check(_lib.lib().insg_engine_set_program_option(self._h, key.encode(), value))
 
     def selftest_barrier_timeout(self) -> bool:
         """Runs the persistent kernel once with a grid barrier that cannot be met and a 2 ms wait limit; True when the

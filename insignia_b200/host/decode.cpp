@@ -8,9 +8,9 @@
 //   attention layer: q|k|v proj, norm/RoPE/KV store/split-K attention, o_proj(gated)+residual,
 //                    gate/up + SwiGLU, down + residual           5
 //   final norm + lm_head + arg-max                               1
-// = 162 fused operations per token.  Default: recorded once as a program and executed by ONE persistent cooperative
-// launch per token (or per run of tokens), with grid barriers between the operations (csrc/persistent.cu).  Option
-// launch_per_op: the same operations as 162 launches replayed from one CUDA graph with programmatic dependent launch.
+// = 162 fused operations per token.  Default: 162 launches replayed from one CUDA graph with programmatic dependent
+// launch.  Option `persistent`: the same operations recorded once as a program and executed by ONE persistent
+// cooperative launch per token (or per run of tokens), with grid barriers between them (csrc/persistent.cu).
 #include "insignia_decode.hpp"
 
 #include "insignia_b200.h"
@@ -145,7 +145,7 @@ struct Qwen35Decode::Plan {
     cudaGraphExec_t exec_chunk{}; // one pass of forward_tokens over kChunk prompt tokens
     int *host_result{}; // pinned: {next token, wait-expired flag}, so the per-token read-back is a true asynchronous copy
     insg_program *prog{};     // the token step as one persistent launch
-    int prefetch_records = -1; // -1: the program's default
+    std::vector<std::pair<std::string, long long>> program_options; // applied to every program this engine builds
 };
 
 Qwen35Decode::Qwen35Decode(Qwen35Weights &weights, DecodeWorkspace &workspace) : w_(weights), x_(workspace) {}
@@ -727,7 +727,7 @@ void Qwen35Decode::build_program()
         enqueue_token_step();
         rec_ = nullptr;
         insg_check(insg_program_finalize(g));
-        if (p.prefetch_records >= 0) insg_check(insg_program_set_option(g, "prefetch_records", p.prefetch_records));
+        for (const auto &kv : p.program_options) insg_check(insg_program_set_option(g, kv.first.c_str(), kv.second));
     } catch (...) {
         rec_ = nullptr;
         launches_ = before;
@@ -749,11 +749,16 @@ void Qwen35Decode::run_program(int n_tokens, int token)
     launches_++;
 }
 
-void Qwen35Decode::set_prefetch_records(int records)
+void Qwen35Decode::set_program_option(const std::string &key, long long value)
 {
     Plan &p = plan();
-    p.prefetch_records = records < 0 ? -1 : records;
-    if (p.prog && records >= 0) insg_check(insg_program_set_option(p.prog, "prefetch_records", records));
+    if (p.prog) insg_check(insg_program_set_option(p.prog, key.c_str(), value));
+    for (auto &kv : p.program_options)
+        if (kv.first == key) {
+            kv.second = value;
+            return;
+        }
+    p.program_options.emplace_back(key, value);
 }
 
 bool Qwen35Decode::selftest_barrier_timeout()
@@ -776,7 +781,7 @@ bool Qwen35Decode::selftest_barrier_timeout()
     return gave_up;
 }
 
-bool Qwen35Decode::persistent() const { return !x_.options.launch_per_op && !x_.options.gemv_tcgen05; }
+bool Qwen35Decode::persistent() const { return x_.options.persistent && !x_.options.gemv_tcgen05; }
 
 void Qwen35Decode::replay_token_step()
 {
@@ -1031,7 +1036,7 @@ void Qwen35Decode::profile_gemv_chain(int replays, float *ms_per_token, uint64_t
             enqueue_token_step();
             rec_ = nullptr;
             insg_check(insg_program_finalize(chain));
-            if (p.prefetch_records >= 0) insg_check(insg_program_set_option(chain, "prefetch_records", p.prefetch_records));
+            for (const auto &kv : p.program_options) insg_check(insg_program_set_option(chain, kv.first.c_str(), kv.second));
         } else {
             cudaGraph_t graph = nullptr;
             cuda_check(cudaStreamBeginCapture(p.stream, cudaStreamCaptureModeThreadLocal), "begin graph capture");

@@ -185,7 +185,7 @@ insg_engine *insg_engine_create(const char *index_path, const insg_engine_option
         d.kv_bf16 = o.kv_dtype == INSG_KV_BF16;
         d.gate_elementwise = o.gate_elementwise != 0;
         d.accurate_trig = o.accurate_trig != 0;
-        d.launch_per_op = o.launch_per_op != 0;
+        d.persistent = o.persistent != 0;
         d.use_graph = o.use_graph != 0;
         d.use_pdl = o.use_pdl != 0;
         d.gemv_tcgen05 = o.gemv_tcgen05 != 0;
@@ -270,10 +270,11 @@ int insg_engine_profile_gemv_chain(insg_engine *e, int replays, float *ms_per_to
         return int(INSG_OK);
     });
 }
-int insg_engine_set_prefetch_records(insg_engine *e, int records)
+int insg_engine_set_program_option(insg_engine *e, const char *key, long long value)
 {
     return guarded(e, [&] {
-        e->dec->set_prefetch_records(records);
+        if (!key) return insg::fail(INSG_E_ARG, "null key");
+        e->dec->set_program_option(key, value);
         return int(INSG_OK);
     });
 }

@@ -117,14 +117,14 @@ def cfg3_reference(cuda, full_ckpt):
     return prompt, first, want, min_gap, hidden
 
 
-@pytest.mark.parametrize("per_op", [False, True])
-def test_cfg3_512_prompt_256_generated_identical_to_reference(cuda, full_ckpt, cfg3_reference, per_op):
+@pytest.mark.parametrize("persistent", [False, True])
+def test_cfg3_512_prompt_256_generated_identical_to_reference(cuda, full_ckpt, cfg3_reference, persistent):
     """The north-star identity check at its full length: 512 + 256 tokens, every generated id equal to the reference's,
-    through the persistent token kernel and through the launch-per-operation path."""
+    through the graph of launches and through the persistent token kernel."""
     from insignia_b200.engine import Engine
 
     prompt, first, want, min_gap, ref_hidden = cfg3_reference
-    with Engine(full_ckpt[1], max_context=len(prompt) + len(want) + 4, launch_per_op=per_op) as e:
+    with Engine(full_ckpt[1], max_context=len(prompt) + len(want) + 4, persistent=persistent) as e:
         for t in prompt:
             e.forward_token(t)
         assert e.logits_argmax() == first

@@ -43,17 +43,17 @@ def test_layers_match_numpy_tool_golden(cuda, golden_ckpt):
             assert np.max(np.abs(h - gold[l])) <= 1e-4 * np.abs(gold[l]).max(), l
 
 
-# (launch per operation?, graph, dependent launch): the persistent token kernel, then the three launch-per-operation forms
-MODES = [(False, False, False), (True, False, False), (True, False, True), (True, True, True)]
+# (persistent token kernel?, graph, dependent launch): the three launch-per-operation forms, then the persistent kernel
+MODES = [(False, False, False), (False, False, True), (False, True, True), (True, False, False)]
 
 
-@pytest.mark.parametrize("per_op,graph,pdl", MODES)
-def test_multi_token_decode_vs_oracle(cuda, golden_ckpt, per_op, graph, pdl):
+@pytest.mark.parametrize("persistent,graph,pdl", MODES)
+def test_multi_token_decode_vs_oracle(cuda, golden_ckpt, persistent, graph, pdl):
     from insignia_b200.checkpoint_io import SafetensorsReader
 
     m = orc.OracleModel(SafetensorsReader(golden_ckpt[0]), max_context=64, gate="broadcast", n_layers=4)
     tokens = [42, 7, 63, 0, 21, 5, 33, 60, 1, 2]
-    with small_engine(golden_ckpt[1], launch_per_op=per_op, use_graph=graph, use_pdl=pdl) as e:
+    with small_engine(golden_ckpt[1], persistent=persistent, use_graph=graph, use_pdl=pdl) as e:
         for i, t in enumerate(tokens):
             got = e.decode_token(t)
             want = m.decode_token(t)
@@ -69,8 +69,8 @@ def test_multi_token_decode_vs_oracle(cuda, golden_ckpt, per_op, graph, pdl):
         assert e.launch_count > 0
 
 
-def _run_tokens(idx, graph, pdl, use_generate, per_op=True):
-    with small_engine(idx, launch_per_op=per_op, use_graph=graph, use_pdl=pdl) as e:
+def _run_tokens(idx, graph, pdl, use_generate, persistent=False):
+    with small_engine(idx, persistent=persistent, use_graph=graph, use_pdl=pdl) as e:
         for t in (3, 9):
             e.forward_token(t)
         first = e.logits_argmax()
@@ -98,8 +98,8 @@ def test_generate_equals_decode_token_loop_bitwise(cuda, golden_ckpt):
     # The persistent token kernel: one launch per token (decode_token loop) and one launch for all twenty tokens
     # (generate) are bit-identical to each other.  Against the launch-per-operation path the GEMVs are bit-identical
     # too, while the DeltaNet and attention phases reduce over 16 warps instead of 8: same tokens, state within rounding.
-    pa = _run_tokens(golden_ckpt[1], False, False, False, per_op=False)
-    pb = _run_tokens(golden_ckpt[1], False, False, True, per_op=False)
+    pa = _run_tokens(golden_ckpt[1], False, False, False, persistent=True)
+    pb = _run_tokens(golden_ckpt[1], False, False, True, persistent=True)
     assert pa[0] == pb[0] == base[0]
     assert np.array_equal(pa[1], pb[1]) and np.array_equal(pa[2], pb[2])
     assert np.max(np.abs(pa[1] - base[1])) <= 2e-5 * np.abs(base[1]).max()
@@ -112,7 +112,7 @@ def test_tcgen05_and_mma_sync_gemv_paths_agree(cuda, golden_ckpt):
     from insignia_b200.checkpoint_io import SafetensorsReader
 
     m = orc.OracleModel(SafetensorsReader(golden_ckpt[0]), max_context=64, gate="broadcast", n_layers=4)
-    with small_engine(golden_ckpt[1], gemv_tcgen05=True) as a, small_engine(golden_ckpt[1], gemv_tcgen05=False, launch_per_op=True) as b:
+    with small_engine(golden_ckpt[1], gemv_tcgen05=True) as a, small_engine(golden_ckpt[1], gemv_tcgen05=False) as b:
         for i, t in enumerate([42, 7, 63, 0, 21, 5, 33, 60]):
             ta, tb, tm = a.decode_token(t), b.decode_token(t), m.decode_token(t)
             assert ta == tb == tm, i
@@ -149,8 +149,7 @@ def test_forward_tokens_equals_token_loop(cuda, golden_ckpt, count):
     without prepared inputs, which only the one-token path uses; within rounding of the default path), the same
     arg-max, and decoding continues identically afterwards."""
     prompt = [42, 7, 63, 0, 21, 5, 33, 60, 11, 12, 1, 2, 3][:count]
-    with small_engine(golden_ckpt[1], prepared_inputs=False, launch_per_op=True) as a, \
-            small_engine(golden_ckpt[1], prepared_inputs=False, launch_per_op=True) as b, \
+    with small_engine(golden_ckpt[1], prepared_inputs=False) as a, small_engine(golden_ckpt[1], prepared_inputs=False) as b, \
             small_engine(golden_ckpt[1]) as c:
         a.forward_tokens(prompt)
         for t in prompt:

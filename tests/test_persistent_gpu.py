@@ -200,7 +200,7 @@ def test_program_attention_phase_sequence_vs_oracle(cuda, kv_bf16):
         if pos % 7 == 0 or pos > 140 or pos < 40:
             want = orc.gqa_decode(q, kc_ref, vc_ref, pos + 1)
             assert np.max(np.abs(host(out) - want)) <= 5e-5, pos
-    assert np.max(np.abs(host(kc.float())[:150 * 1024] - kc_ref[:150 * 1024])) <= (2.0 ** -7 * np.abs(kc_ref).max() if kv_bf16 else 1e-5)
+    assert np.max(np.abs(host(kc.float())[:150 * 1024] - kc_ref[:150 * 1024])) <= (2.0 ** -7 * np.abs(kc_ref).max() if kv_bf16 else 5e-5)
     assert int(scratch[:16].view(torch.int32).abs().sum().item()) == 0  # tickets left at zero
 
 
@@ -277,8 +277,8 @@ def test_engine_selftest_and_recovery(cuda, golden_ckpt):
     """The engine reports the expired wait and decodes correctly afterwards."""
     from insignia_b200.engine import Engine
 
-    with Engine(golden_ckpt[1], n_layers=4, vocab=64, max_context=64) as e, \
-            Engine(golden_ckpt[1], n_layers=4, vocab=64, max_context=64) as ref:
+    with Engine(golden_ckpt[1], n_layers=4, vocab=64, max_context=64, persistent=True) as e, \
+            Engine(golden_ckpt[1], n_layers=4, vocab=64, max_context=64, persistent=True) as ref:
         want = [ref.decode_token(t) for t in (42, 7, 63)]
         assert e.decode_token(42) == want[0]
         assert e.selftest_barrier_timeout() is True
