@@ -113,6 +113,14 @@ INSG_API int insg_mxfp4_repack_umma(const uint32_t *weight, const uint8_t *scale
 INSG_API int insg_mxfp4_gemv_packed(const void *packed, const float *x, float *y, int rows, int cols, int M,
                                     insg_stream_t stream);
 
+/* Y[m][rows] = W x[m] for M tokens on the tcgen05 tensor cores (kind::mxf4, weights in the insg_mxfp4_repack_umma
+ * layout, eight tokens per instruction, fp32-exact activations as base-4 digit columns); x fp32 [M][cols], y fp32
+ * [M][rows].  The M >= 8 counterpart of insg_mxfp4_gemv_packed (src/decode.cu:13 applied to M tokens; the reference
+ * has no batched form).  scratch: insg_umma_gemm_scratch_bytes(cols, M) of device memory. */
+INSG_API size_t insg_umma_gemm_scratch_bytes(int cols, int tokens);
+INSG_API int insg_mxfp4_gemm_umma(const void *packed_umma, const float *x, float *y, int rows, int cols, int M, void *scratch,
+                                  size_t scratch_bytes, insg_stream_t stream);
+
 /* ---------------------------------------------------------- fused GEMV op */
 
 /* What is done to the activation vector before the contraction. */
@@ -195,10 +203,15 @@ typedef struct insg_gemv_op {
     int pdl;                  /* 1: launch with programmatic dependent launch          */
     const float *prep_partials; /* INSG_PRO_PREPARED: the producer's prep_partials [296], or NULL                        */
     int prep_rms;               /* INSG_PRO_PREPARED: 1 = scale by the RMS factor computed from prep_partials            */
-    int tokens;                 /* 0 or 1: one token.  2 or 4: consecutive tokens of one sequence in one launch (the
-                                   weights are streamed once): in, aux and x_out are [tokens][cols], every out is
-                                   [tokens][rows]; the convolution history is advanced token by token.  Not with
-                                   INSG_PRO_PREPARED, prepared outputs or INSG_EPI_LOGITS. */
+    int tokens;                 /* 0 or 1: one token.  More: consecutive tokens of one sequence in one call (the weights are
+                                   streamed once per pass): in, aux and x_out are [tokens][cols], every out is
+                                   [tokens][rows]; the convolution history is advanced token by token.  layout 0: 2 or 4
+                                   tokens (one launch of the mma.sync kernel); layout 1: any count up to 4096, eight tokens
+                                   per tcgen05 instruction (needs umma_scratch).  Not with INSG_PRO_PREPARED, prepared
+                                   outputs or INSG_EPI_LOGITS. */
+    void *umma_scratch;         /* layout 1 with tokens > 1: device scratch of insg_umma_gemm_scratch_bytes(cols, tokens) for
+                                   the activations' digit image, rewritten by every call                                      */
+    size_t umma_scratch_bytes;
 } insg_gemv_op;
 
 INSG_API size_t insg_gemv_argmax_scratch_bytes(void);
@@ -408,6 +421,9 @@ typedef struct insg_engine_options {
     int device;                   /* CUDA device ordinal                                        */
     int persistent;               /* 0: one launch per fused operation (162 per token), replayed from a CUDA graph when
                                      use_graph is set; 1: a token step is ONE persistent cooperative launch (insg_program_*) */
+    int prefill_mma_sync;         /* 0: insg_engine_forward_tokens sends 16 or more tokens through the tcgen05 kernel in passes
+                                     of up to 32 (second copy of the weights in its tile layout); 1: always passes of four
+                                     through the mma.sync kernel */
     int gemv_unprepared;          /* 0: a GEMV that writes the residual stream or the SwiGLU output leaves the next
                                      GEMV's input prepared (insg_gemv_segment.prep); 1: every GEMV converts its own */
 } insg_engine_options;

@@ -37,6 +37,9 @@ struct DecodeOptions {
     bool prepared_inputs = true;   // a GEMV that writes the residual stream or the SwiGLU output also leaves the next GEMV's
                                    // input ready as fp16 pieces (and its sum of squares), so that one starts streaming
                                    // without normalising or converting anything; false: every GEMV prepares its own input
+    bool prefill_tcgen05 = true;   // forward_tokens with 16 or more tokens: passes of up to 32 tokens through the tcgen05
+                                   // kernel (kind::mxf4, eight tokens per instruction; needs a second, tile-layout copy of
+                                   // the weights); false: always passes of four tokens through the mma.sync kernel
     int n_layers = Qwen35Shape::layers;
     int vocab = Qwen35Shape::vocab;
 };
@@ -65,7 +68,9 @@ public:
     int *d_next{};       // device: arg-max of the last logits
     void *attn_scratch{};
     void *argmax_scratch{};
-    float *multi{};      // device: activations of up to four consecutive tokens (forward_tokens)
+    float *multi{};      // device: activations of up to 32 consecutive tokens (forward_tokens)
+    void *umma_scratch{}; // device: digit image of the activations for the tcgen05 kernel (forward_tokens)
+    size_t umma_scratch_bytes{};
     void *prep{};        // device: prepared GEMV inputs, fp16 [2][4096] + fp16 [2][12288] + fp32 [2][296] sums of squares
     void reset(); // zero recurrent state and position, as a fresh workspace
 
@@ -114,6 +119,7 @@ private:
     // this block's output next (the block then leaves that input prepared), or null when the caller may touch hidden
     void load_embed();
     void load_block(int layer);
+    void load_block_umma(int layer);
     void prefetch_block(int layer);
     void load_head();
     void enqueue_delta(int layer, bool hidden_prepared = false, const uint16_t *next_norm = nullptr);

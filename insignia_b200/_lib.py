@@ -25,7 +25,7 @@ class GemvOp(C.Structure):
     _fields_ = [("in_", vp), ("aux", vp), ("norm_w", vp), ("x_out", vp), ("cols", i32), ("prologue", i32),
                 ("n_segments", i32), ("seg", GemvSegment * 4), ("argmax_scratch", vp), ("token_out", vp),
                 ("token_feedback", vp), ("token_log", vp), ("token_log_capacity", i32), ("position_inout", vp), ("layout", i32), ("error_flag", vp), ("pdl", i32),
-                ("prep_partials", vp), ("prep_rms", i32), ("tokens", i32)]
+                ("prep_partials", vp), ("prep_rms", i32), ("tokens", i32), ("umma_scratch", vp), ("umma_scratch_bytes", sz)]
 
 
 class AttnOp(C.Structure):
@@ -37,7 +37,7 @@ class AttnOp(C.Structure):
 class EngineOptions(C.Structure):
     _fields_ = [("device_budget_bytes", u64), ("max_context", i32), ("kv_dtype", i32), ("gate_elementwise", i32),
                 ("accurate_trig", i32), ("use_graph", i32), ("use_pdl", i32), ("gemv_tcgen05", i32), ("n_layers", i32), ("vocab", i32),
-                ("device", i32), ("persistent", i32), ("gemv_unprepared", i32)]
+                ("device", i32), ("persistent", i32), ("prefill_mma_sync", i32), ("gemv_unprepared", i32)]
 
 
 # name -> (restype, argtypes); every symbol include/insignia_b200.h declares
@@ -58,6 +58,8 @@ SIGNATURES = {
     "insg_mxfp4_packed_umma_bytes": (sz, [i32, i32]),
     "insg_mxfp4_repack_umma": (i32, [vp, vp, vp, i32, i32, vp]),
     "insg_mxfp4_gemv_packed": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "insg_umma_gemm_scratch_bytes": (sz, [i32, i32]),
+    "insg_mxfp4_gemm_umma": (i32, [vp, vp, vp, i32, i32, i32, vp, sz, vp]),
     "insg_gemv_argmax_scratch_bytes": (sz, []),
     "insg_gemv_fused": (i32, [C.POINTER(GemvOp), vp]),
     "insg_program_create": (vp, []),

@@ -38,6 +38,7 @@ int sm_count()
 }
 
 int umma_tune(const char *key, int value);
+int umma_gemm_tune(const char *key, int value);
 
 } // namespace insg
 
@@ -49,6 +50,7 @@ int insg_tune_set(const char *key, int value)
 {
     if (!key) return insg::fail(INSG_E_ARG, "tune: null key");
     if (insg::umma_tune(key, value) == INSG_OK) return INSG_OK;
+    if (insg::umma_gemm_tune(key, value) == INSG_OK) return INSG_OK;
     return insg::fail(INSG_E_ARG, "unknown tuning key");
 }
 

@@ -93,6 +93,7 @@ template <int UNR, int M> int launch_variant(const GemvParams &p, int grid, size
 } // namespace
 
 int gemv_umma_launch(const insg_gemv_op *op, cudaStream_t st);
+int gemm_umma_launch(const insg_gemv_op *op, cudaStream_t st);
 
 // Validates a fused-GEMV description and turns it into the kernel's parameter block for a grid of at most `max_grid`
 // CTAs (one per SM); *grid and *smem receive the launch shape.
@@ -197,10 +198,7 @@ size_t insg_gemv_argmax_scratch_bytes(void) { return 64 + size_t(8) * 512; }
 
 int insg_gemv_fused(const insg_gemv_op *op, insg_stream_t stream)
 {
-    if (op && op->layout == 1) {
-        if (op->tokens > 1) return fail(INSG_E_SHAPE, "gemv: the tcgen05 layout takes one token per launch");
-        return gemv_umma_launch(op, stream);
-    }
+    if (op && op->layout == 1) return op->tokens > 1 ? gemm_umma_launch(op, stream) : gemv_umma_launch(op, stream);
     return gemv_fused_launch(op, op && op->tokens > 1 ? op->tokens : 1, stream);
 }
 

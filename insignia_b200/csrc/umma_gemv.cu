@@ -26,8 +26,8 @@
 // releases, warps 0-3 read the accumulators (tcgen05.ld, TMEM lane = output row) and run the fused
 // epilogue.  Accumulators are double buffered so a tile's epilogue overlaps the next tile's MMAs.
 // Every wait is bounded: on expiry a flag is raised in global memory and all roles drain.
-#include "common.cuh"
 #include "gemv_prologue.cuh"
+#include "umma_common.cuh"
 #include "host_util.h"
 
 #include <algorithm>
@@ -35,13 +35,11 @@
 
 namespace insg {
 
-constexpr int kURec = 8704;          // bytes per (128-row tile, 128-k block) record
 constexpr int kUThreads = kProThreads;
 constexpr int kBImgPerKb = 1024;     // activation digits: 16 columns x 128 k x 4 bit
 constexpr int kAccMax = 8;           // independent accumulators per tile: consecutive MMAs must not wait on each other's result
 constexpr int kSfaBufs = 8;          // scale-factor column sets cycled by k-block
 constexpr int kTmemCols = 512;       // D set 0 [0,128) D set 1 [128,256) SFA [256,288) SFB [288,292)
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct USeg {
     const uint8_t *packed, *packed2;
@@ -64,46 +62,6 @@ struct UParams {
     int token_log_capacity;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-// shared-memory matrix descriptor: no swizzle, version 1 (sm_100); offsets in bytes
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo)
-{
-    return uint64_t((saddr >> 4) & 0x3FFF) | (uint64_t((lbo >> 4) & 0x3FFF) << 16) | (uint64_t((sbo >> 4) & 0x3FFF) << 32) | (uint64_t(1) << 46);
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t *b, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *b)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *b, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
-}
-// Bounded wait on a phase parity; false when the limit ran out or another role raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity, volatile int *abort_flag)
-{
-    for (uint32_t it = 0; it < kSpinLimit; it++) {
-        uint32_t done;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(done) : "r"(smem_u32(b)), "r"(parity) : "memory");
-        if (done) return true;
-        if ((it & 1023u) == 1023u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
-
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-
 // kblock i of this CTA's sequence -> global address of its record and its place in the tile sequence
 struct URun {
     const uint8_t *rec;
@@ -125,24 +83,6 @@ __device__ __forceinline__ const uint8_t *run_base(const UParams &p, int tile, i
 {
     const USeg &s = p.seg[useg_of(p, tile)];
     return (mat ? s.packed2 : s.packed) + size_t(tile - s.tile_begin) * p.nkb * kURec;
-}
-
-// Twelve base-4 digits of |v| (24 bits) as E2M1 codes, one per nibble: digits 0..7 in lo, 8..11 in hi; sign in bit 3.
-__device__ __forceinline__ void digit_codes(float x, float alpha, uint32_t &lo, uint32_t &hi)
-{
-    const float sc = fabsf(x) * alpha;                      // < 2^24
-    const uint32_t v = min(__float2uint_rn(sc), 0xFFFFFFu);
-    const uint32_t sgn = (__float_as_uint(x) >> 31) * 0x88888888u;
-    uint32_t t = v & 0xFFFFu;                               // 16 bits -> eight 2-bit digits, one per nibble
-    t = (t | (t << 8)) & 0x00FF00FFu;
-    t = (t | (t << 4)) & 0x0F0F0F0Fu;
-    t = (t | (t << 2)) & 0x33333333u;
-    uint32_t u = v >> 16;                                   // 8 bits -> four digits
-    u = (u | (u << 4)) & 0x0F0F0F0Fu;
-    u = (u | (u << 2)) & 0x33333333u;
-    // digit d -> E2M1 code of the value d: 0,1,2,3 -> 0,2,4,5 = 2d - (d == 3)
-    lo = ((t << 1) - ((t >> 1) & t & 0x11111111u)) | sgn;
-    hi = ((u << 1) - ((u >> 1) & u & 0x11111111u)) | (sgn & 0x0000FFFFu);
 }
 
 __global__ void __launch_bounds__(kUThreads, 1) umma_gemv_kernel(const __grid_constant__ UParams p)

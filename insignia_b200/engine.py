@@ -23,11 +23,11 @@ class Engine:
     def __init__(self, index_path: str, max_context: int = 4096, budget_bytes: int = 16 << 30, kv_bf16: bool = False,
                  gate_elementwise: bool = False, accurate_trig: bool = False, use_graph: bool = True,
                  use_pdl: bool = True, n_layers: int = 32, vocab: int = 248320, device: int = 0,
-                 gemv_tcgen05: bool = False, prepared_inputs: bool = True, persistent: bool = False):
+                 gemv_tcgen05: bool = False, prepared_inputs: bool = True, persistent: bool = False, prefill_tcgen05: bool = True):
         """``persistent=False`` (default): one launch per fused operation, replayed from a CUDA graph when ``use_graph``;
         ``True``: a token step is one persistent cooperative launch (``insg_program_*``)."""
         o = EngineOptions(budget_bytes, max_context, int(kv_bf16), int(gate_elementwise), int(accurate_trig),
-                          int(use_graph), int(use_pdl), int(gemv_tcgen05), n_layers, vocab, device, int(persistent),
+                          int(use_graph), int(use_pdl), int(gemv_tcgen05), n_layers, vocab, device, int(persistent), int(not prefill_tcgen05),
                           int(not prepared_inputs))
         self.vocab = vocab
         self._destroy = _lib.lib().insg_engine_destroy  # held here: module globals may be gone when __del__ runs at exit

@@ -25,12 +25,14 @@ constexpr int kHidden = Qwen35Shape::hidden, kInter = Qwen35Shape::intermediate;
 constexpr size_t kPrepHidden = 0, kPrepAct = size_t(2) * kHidden * 2, kPrepSums = kPrepAct + size_t(2) * kInter * 2;
 constexpr int kMultiSteps = 8; // token steps per graph in Qwen35Decode::generate
 // DecodeWorkspace::multi: activations of up to kChunk consecutive tokens for Qwen35Decode::forward_tokens, [token][width] each
-constexpr int kChunk = 4;
-constexpr size_t kMultiHidden = 0, kMultiQkv = kMultiHidden + size_t(kChunk) * 4096, kMultiZ = kMultiQkv + size_t(kChunk) * 8192,
-                 kMultiA = kMultiZ + size_t(kChunk) * 4096, kMultiB = kMultiA + size_t(kChunk) * 32, kMultiCore = kMultiB + size_t(kChunk) * 32,
-                 kMultiQg = kMultiCore + size_t(kChunk) * 4096, kMultiKey = kMultiQg + size_t(kChunk) * 8192,
-                 kMultiValue = kMultiKey + size_t(kChunk) * 1024, kMultiAct = kMultiValue + size_t(kChunk) * 1024,
-                 kMultiTokens = kMultiAct + size_t(kChunk) * 12288, kMultiFloats = kMultiTokens + kChunk;
+constexpr int kChunk = 4;     // tokens per pass of the mma.sync kernel
+constexpr int kBigChunk = 32; // tokens per pass of the tcgen05 kernel (four groups of eight)
+constexpr size_t kMultiHidden = 0, kMultiQkv = kMultiHidden + size_t(kBigChunk) * 4096, kMultiZ = kMultiQkv + size_t(kBigChunk) * 8192,
+                 kMultiA = kMultiZ + size_t(kBigChunk) * 4096, kMultiB = kMultiA + size_t(kBigChunk) * 32,
+                 kMultiCore = kMultiB + size_t(kBigChunk) * 32, kMultiQg = kMultiCore + size_t(kBigChunk) * 4096,
+                 kMultiKey = kMultiQg + size_t(kBigChunk) * 8192, kMultiValue = kMultiKey + size_t(kBigChunk) * 1024,
+                 kMultiAct = kMultiValue + size_t(kBigChunk) * 1024, kMultiTokens = kMultiAct + size_t(kBigChunk) * 12288,
+                 kMultiFloats = kMultiTokens + kBigChunk;
 constexpr size_t kPrepBytes = kPrepSums + 2 * 296 * sizeof(float); // one row of sums per image
 const char *const kLM = "language_model";
 
@@ -90,6 +92,8 @@ void DecodeWorkspace::allocate()
     cuda_check(cudaMalloc(&argmax_scratch, insg_gemv_argmax_scratch_bytes()), "cudaMalloc arg-max scratch");
     cuda_check(cudaMalloc(&prep, kPrepBytes), "cudaMalloc prepared inputs");
     cuda_check(cudaMalloc(&multi, kMultiFloats * sizeof(float)), "cudaMalloc multi-token buffers");
+    umma_scratch_bytes = insg_umma_gemm_scratch_bytes(kInter, kBigChunk);
+    cuda_check(cudaMalloc(&umma_scratch, umma_scratch_bytes), "cudaMalloc tcgen05 activation image");
     cuda_check(cudaMemsetAsync(prep, 0, kPrepBytes, stream), "memset");
     cuda_check(cudaMemsetAsync(attn_scratch, 0, 64, stream), "memset");
     cuda_check(cudaMemsetAsync(argmax_scratch, 0, 64, stream), "memset");
@@ -110,7 +114,7 @@ DecodeWorkspace::~DecodeWorkspace()
     for (void *p : {(void *)hidden, (void *)norm, (void *)qkv, (void *)attn_gate, (void *)key, (void *)value, (void *)z, (void *)a,
                     (void *)b, (void *)core, (void *)gate, (void *)up, (void *)down, (void *)logits, (void *)delta_state,
                     (void *)conv_state, (void *)kv_keys, (void *)kv_values, (void *)mtp_keys, (void *)mtp_values, (void *)d_token,
-                    attn_scratch, argmax_scratch, prep, (void *)multi})
+                    attn_scratch, argmax_scratch, prep, (void *)multi, umma_scratch})
         cudaFree(p);
 }
 
@@ -127,6 +131,7 @@ struct Qwen35Decode::Plan {
         PackedMatrix gate, up, down;                  // MLP
     };
     std::vector<Block> layers;
+    std::vector<Block> layers_umma; // the same blocks with their matrices in the tcgen05 tile layout (prompt processing)
     Block mtp;
     bool head_ready = false, embed_ready = false, mtp_ready = false;
     const uint16_t *final_norm{};
@@ -171,6 +176,7 @@ Qwen35Decode::Plan &Qwen35Decode::plan()
     if (!plan_) {
         plan_ = std::make_unique<Plan>();
         plan_->layers.resize(Qwen35Shape::layers);
+        plan_->layers_umma.resize(Qwen35Shape::layers);
         if (x_.stream) {
             plan_->stream = x_.stream;
         } else {
@@ -218,6 +224,7 @@ struct Ctx {
     uint64_t *gemv_bytes;                // optional: algorithmic weight bytes of the GEMVs issued are added here
     bool hidden_prepared = false;        // the previous block left this block's first input prepared
     const uint16_t *next_norm = nullptr; // weight of the RMSNorm that reads this block's output next, when known
+    int layout = -1;                     // >= 0: weight layout of the GEMVs issued (else the engine's gemv_tcgen05 option)
     void *prep_hidden() const { return static_cast<uint8_t *>(x.prep) + kPrepHidden; }
     void *prep_act() const { return static_cast<uint8_t *>(x.prep) + kPrepAct; }
     float *prep_sums() const { return reinterpret_cast<float *>(static_cast<uint8_t *>(x.prep) + kPrepSums); }
@@ -263,8 +270,12 @@ uint64_t gemv_weight_bytes(const insg_gemv_op &op)
 void run_gemv(Ctx &c, insg_gemv_op &op)
 {
     op.pdl = c.pdl ? 1 : 0;
-    op.layout = c.x.options.gemv_tcgen05 ? 1 : 0;
+    op.layout = c.layout >= 0 ? c.layout : (c.x.options.gemv_tcgen05 ? 1 : 0);
     op.error_flag = c.x.d_token + 3;
+    if (op.layout == 1 && op.tokens > 1) {
+        op.umma_scratch = c.x.umma_scratch;
+        op.umma_scratch_bytes = c.x.umma_scratch_bytes;
+    }
     if (c.gemv_bytes) *c.gemv_bytes += gemv_weight_bytes(op);
     if (c.rec) insg_check(insg_program_add_gemv(c.rec, &op));
     else insg_check(insg_gemv_fused(&op, c.st));
@@ -611,6 +622,17 @@ void Qwen35Decode::prefetch_block(int l)
     for (const char *m : {"gate_proj", "up_proj", "down_proj"}) w_.prefetch(name + ".mlp." + m);
 }
 
+void Qwen35Decode::load_block_umma(int l)
+{
+    Plan &p = plan();
+    Plan::Block &b = p.layers_umma[l];
+    if (b.ready) return;
+    Loader L{w_, p.pinned, 1};
+    const std::string name = std::string(kLM) + ".model.layers." + std::to_string(l);
+    if (Qwen35Shape::full_attention(l)) load_attention(L, name, b);
+    else load_delta(L, name, b);
+}
+
 void Qwen35Decode::load_block(int l)
 {
     Plan &p = plan();
@@ -867,8 +889,17 @@ void Qwen35Decode::forward_tokens(const int *tokens, int count)
     load_head();
     load_embed();
     Ctx c{x_, p.stream, x_.options.use_pdl, launches_, false, nullptr, nullptr};
+    // Long prompts go through the tcgen05 kernel in passes of up to kBigChunk tokens (eight tokens per instruction); what
+    // is left, and short prompts, through the mma.sync kernel in passes of four.
+    const bool big = x_.options.prefill_tcgen05 && count >= 16;
+    if (big)
+        for (int l = 0; l < n; l++) load_block_umma(l);
     for (int done = 0; done < count;) {
-        const int left = count - done, T = left >= 4 ? 4 : (left >= 2 ? 2 : 1);
+        const int left = count - done;
+        const bool use_umma = big && left >= 8;
+        const int T = use_umma ? std::min(left, kBigChunk) : (left >= 4 ? 4 : (left >= 2 ? 2 : 1));
+        c.layout = use_umma ? 1 : -1;
+        const std::vector<Plan::Block> &blocks = use_umma ? p.layers_umma : p.layers;
         Multi u(x_, T);
         sync_scalars(-1); // the chunk's first position; token m of the chunk sits at position + m
         cuda_check(cudaMemcpyAsync(u.tokens, tokens + done, size_t(T) * sizeof(int), cudaMemcpyHostToDevice, p.stream), "copy tokens");
@@ -882,14 +913,14 @@ void Qwen35Decode::forward_tokens(const int *tokens, int count)
                 if (Qwen35Shape::full_attention(l)) {
                     const size_t esz = x_.options.kv_bf16 ? 2 : 4;
                     const size_t off = size_t(l / 4) * x_.max_context * 1024 * esz;
-                    attention_block_multi(c, p.layers[l], reinterpret_cast<uint8_t *>(x_.kv_keys) + off,
+                    attention_block_multi(c, blocks[l], reinterpret_cast<uint8_t *>(x_.kv_keys) + off,
                                           reinterpret_cast<uint8_t *>(x_.kv_values) + off, u);
                 } else {
-                    delta_block_multi(c, p.layers[l], l - l / 4, u);
+                    delta_block_multi(c, blocks[l], l - l / 4, u);
                 }
             }
         };
-        if (T == kChunk && x_.options.use_graph && p.chunk_warm) {
+        if (!use_umma && T == kChunk && x_.options.use_graph && p.chunk_warm) {
             // full chunks replay one graph (tokens and position are read from device memory); the first full chunk ran
             // eagerly (first launches of a kernel variant set function attributes)
             const uint64_t before = launches_;
@@ -913,7 +944,7 @@ void Qwen35Decode::forward_tokens(const int *tokens, int count)
             cuda_check(cudaGraphLaunch(p.exec_chunk, p.stream), "launch graph");
         } else {
             enqueue_chunk();
-            p.chunk_warm |= T == kChunk;
+            p.chunk_warm |= !use_umma && T == kChunk;
         }
         x_.position += T;
         done += T;

@@ -186,6 +186,7 @@ insg_engine *insg_engine_create(const char *index_path, const insg_engine_option
         d.gate_elementwise = o.gate_elementwise != 0;
         d.accurate_trig = o.accurate_trig != 0;
         d.persistent = o.persistent != 0;
+        d.prefill_tcgen05 = o.prefill_mma_sync == 0;
         d.use_graph = o.use_graph != 0;
         d.use_pdl = o.use_pdl != 0;
         d.gemv_tcgen05 = o.gemv_tcgen05 != 0;

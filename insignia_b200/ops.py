@@ -88,8 +88,10 @@ def gemv_packed(packed, x, rows=None, cols=None):
 
 
 def _gemv_op(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None, argmax=None, pdl=False, layout=0, error_flag=None,
-             prep_partials=None, prep_rms=False, cols=None, tokens=1):
+             prep_partials=None, prep_rms=False, cols=None, tokens=1, umma_scratch=None):
     op = GemvOp()
+    if umma_scratch is not None:
+        op.umma_scratch, op.umma_scratch_bytes = _p(umma_scratch), umma_scratch.numel()
     op.in_, op.aux, op.norm_w, op.x_out = _p(inp), _p(aux), _p(norm_w), _p(x_out)
     op.cols, op.prologue, op.n_segments = cols or inp.shape[-1], PRO[prologue], len(segments)
     op.prep_partials, op.prep_rms, op.tokens = _p(prep_partials), int(prep_rms), tokens
@@ -109,6 +111,22 @@ def _gemv_op(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None,
     op.error_flag = _p(error_flag)
     op.pdl = int(pdl)
     return op
+
+
+def umma_gemm_scratch(cols, tokens, device="cuda"):
+    return torch.empty(_lib.lib().insg_umma_gemm_scratch_bytes(cols, tokens), dtype=torch.uint8, device=device)
+
+
+def gemm_umma(packed_umma, x, rows=None, cols=None, scratch=None):
+    """``y[m] = W x[m]`` for all rows of ``x`` on the tcgen05 tensor cores (weights from :func:`repack_umma`)."""
+    rows = rows or packed_umma.rows
+    cols = cols or packed_umma.cols
+    x2 = x.reshape(-1, cols)
+    M = x2.shape[0]
+    scratch = scratch if scratch is not None else umma_gemm_scratch(cols, M, x.device)
+    y = torch.empty((M, rows), dtype=torch.float32, device=x.device)
+    check(_lib.lib().insg_mxfp4_gemm_umma(_p(packed_umma), _p(x2), _p(y), rows, cols, M, _p(scratch), scratch.numel(), _stream()))
+    return y.reshape(*x.shape[:-1], rows)
 
 
 def gemv_fused(inp, segments, **kw):

@@ -174,6 +174,31 @@ def test_forward_tokens_equals_token_loop(cuda, golden_ckpt, count):
             e.forward_tokens([1, 248320])
 
 
+@pytest.mark.parametrize("count", [16, 37, 50])
+def test_forward_tokens_through_tcgen05_passes(cuda, golden_ckpt, count):
+    """Prompts of 16 tokens or more go through the tcgen05 kernel in passes of up to 32 tokens (the rest in passes of
+    four): the same state as the token loop to rounding, the same arg-max, and decoding continues with the same tokens."""
+    rng = np.random.default_rng(count)
+    prompt = [int(t) for t in rng.integers(0, 64, count)]
+    with small_engine(golden_ckpt[1]) as a, small_engine(golden_ckpt[1], prefill_tcgen05=False) as b, small_engine(golden_ckpt[1]) as c:
+        a.forward_tokens(prompt)
+        b.forward_tokens(prompt)
+        for t in prompt:
+            c.forward_token(t)
+        assert a.position == b.position == c.position == count
+        for field, n in (("hidden", 4096), ("delta_state", 3 * 32 * 128 * 128), ("conv_state", 3 * 8192 * 3), ("kv_keys", count * 1024),
+                         ("kv_values", count * 1024)):
+            ra, rc = a.read(field, n), c.read(field, n)
+            assert np.max(np.abs(ra - rc)) <= 2e-4 * max(np.abs(rc).max(), 1e-6), field
+            assert np.max(np.abs(b.read(field, n) - rc)) <= 2e-4 * max(np.abs(rc).max(), 1e-6), field
+        ta = a.logits_argmax()
+        assert ta == b.logits_argmax() == c.logits_argmax()
+        tc = ta
+        for _ in range(6):
+            ta, tc = a.decode_token(ta), c.decode_token(tc)
+            assert ta == tc
+
+
 def test_kv_bf16_and_accurate_trig_modes(cuda, golden_ckpt):
     from insignia_b200.checkpoint_io import SafetensorsReader
 
