@@ -174,6 +174,10 @@ typedef struct insg_gemv_segment {
     void *prep;
     const uint16_t *prep_w;
     float *prep_partials;
+    /* CONV_SILU with several tokens.  0: the tokens are consecutive positions of ONE sequence, the history is carried
+     * through them in order.  Otherwise the tokens belong to independent sequences (a decode batch) and token m's
+     * history is conv_state + m * conv_token_stride floats. */
+    long long conv_token_stride;
 } insg_gemv_segment;
 
 /* A fused launch: prologue on the shared input vector, up to 4 matrices that
@@ -276,6 +280,13 @@ INSG_API int insg_deltanet_decode_tokens(float *state, const float *q16, const f
                                          const float *g32, const float *beta32, float *out32, int tokens, int qkv_stride,
                                          int pdl, insg_stream_t stream);
 
+/* One step for `sequences` (1..64) independent sequences in one launch (a decode batch): sequence s has its state at
+ * state + s * state_stride floats, q16/k16/v32 at + s * qkv_stride, g32/beta32 at + s * 32, out32 at + s * 4096.  Same
+ * arithmetic as `sequences` calls of insg_deltanet_decode.  No reference counterpart (it is strictly batch 1). */
+INSG_API int insg_deltanet_decode_batch(float *state, long long state_stride, const float *q16, const float *k16, const float *v32,
+                                        const float *g32, const float *beta32, float *out32, int sequences, int qkv_stride, int pdl,
+                                        insg_stream_t stream);
+
 /* ------------------------------------------------------------ attention */
 
 /* KV cache element type. */
@@ -369,6 +380,11 @@ INSG_API int insg_expand_gate_heads(const float *head_gate, float *gate256, insg
 INSG_API int insg_concat(const float *a, const float *b, float *out, int n, insg_stream_t stream);
 /* src/qwen_kernels.cu:21 ; ties resolve to the lowest index */
 INSG_API int insg_argmax_logits(const float *logits, int n, int *device_token, insg_stream_t stream);
+/* The same arg-max for `count` rows of logits [count][stride] at once (one per sequence of a decode batch), and the end
+ * of a batch step: tokens[i] = next[i], log[*position][i] = next[i] (while *position < capacity), then ++*position.
+ * No reference counterpart (it decodes one sequence). */
+INSG_API int insg_argmax_rows(const float *logits, long long stride, int n, int count, int *device_tokens, insg_stream_t stream);
+INSG_API int insg_commit_tokens(const int *next, int *tokens, int *log, int capacity, int *position, int n, insg_stream_t stream);
 /* src/qwen_kernels.cu:26 : y[rows] = W_bf16[rows][cols] x (mtp.fc) */
 INSG_API int insg_bf16_gemv(const uint16_t *w, const float *x, float *y, int rows, int cols, int pdl,
                             insg_stream_t stream);
@@ -479,6 +495,28 @@ INSG_API insg_stream_t insg_engine_stream(insg_engine *e);
 /* Kernel launches issued by the engine since creation (own kernels only). */
 INSG_API uint64_t insg_engine_launch_count(insg_engine *e);
 INSG_API uint64_t insg_engine_device_bytes(insg_engine *e);
+
+/* ---------------------------------------------------------------- batch */
+/* 1..8 independent sequences decoded in lock step on the weights of an engine (ONE copy of the weights; every weight
+ * matrix is streamed once per step for all sequences): insignia::Qwen35BatchDecode of include/insignia_batch.hpp.  Each
+ * sequence has its own recurrent state and KV cache (allocated at create, max_context <= 0 takes the engine's).  No
+ * reference counterpart: the reference decodes one sequence (include/insignia_decode.hpp:5-24).  The batch must be
+ * destroyed before its engine. */
+typedef struct insg_batch insg_batch;
+INSG_API insg_batch *insg_batch_create(insg_engine *e, int sequences, int max_context);
+INSG_API void insg_batch_destroy(insg_batch *b);
+/* one step, tokens[s] into sequence s (host array of `sequences` ints); no read-back */
+INSG_API int insg_batch_forward_tokens(insg_batch *b, const int *tokens /* host */);
+/* one step; next[s] (host) = greedy next token of sequence s; synchronises */
+INSG_API int insg_batch_decode_tokens(insg_batch *b, const int *tokens /* host */, int *next /* host */);
+/* count steps with the arg-max fed back on the device; out[step * sequences + s] (host); synchronises once */
+INSG_API int insg_batch_generate(insg_batch *b, const int *first_tokens /* host */, int count, int *out /* host */);
+INSG_API int insg_batch_reset(insg_batch *b);
+INSG_API int insg_batch_position(insg_batch *b);
+/* "hidden" (count 4096) or "delta_state" (first count floats) of one sequence to the host */
+INSG_API int insg_batch_read(insg_batch *b, const char *field, int sequence, float *out /* host */, uint64_t count);
+INSG_API uint64_t insg_batch_launch_count(insg_batch *b);
+INSG_API insg_stream_t insg_batch_stream(insg_batch *b);
 
 #ifdef __cplusplus
 }

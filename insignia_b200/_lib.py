@@ -18,7 +18,7 @@ vp, i32, u64, sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t
 
 class GemvSegment(C.Structure):
     _fields_ = [("packed", vp), ("packed2", vp), ("out", vp), ("rows", i32), ("epilogue", i32), ("conv_state", vp),
-                ("conv_w", vp), ("A_log", vp), ("dt_bias", vp), ("prep", vp), ("prep_w", vp), ("prep_partials", vp)]
+                ("conv_w", vp), ("A_log", vp), ("dt_bias", vp), ("prep", vp), ("prep_w", vp), ("prep_partials", vp), ("conv_token_stride", C.c_longlong)]
 
 
 class GemvOp(C.Structure):
@@ -77,6 +77,7 @@ SIGNATURES = {
     "insg_program_weight_bytes": (u64, [vp]),
     "insg_deltanet_decode": (i32, [vp] * 7 + [i32, vp]),
     "insg_deltanet_decode_tokens": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "insg_deltanet_decode_batch": (i32, [vp, C.c_longlong, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "insg_gqa_scratch_bytes": (sz, [i32]),
     "insg_gqa_decode": (i32, [vp, vp, vp, vp, i32, i32, vp, sz, vp]),
     "insg_gqa_decode_noalloc": (i32, [vp, vp, vp, vp, i32, i32, vp]),
@@ -95,6 +96,8 @@ SIGNATURES = {
     "insg_expand_gate_heads": (i32, [vp, vp, vp]),
     "insg_concat": (i32, [vp, vp, vp, i32, vp]),
     "insg_argmax_logits": (i32, [vp, i32, vp, vp]),
+    "insg_argmax_rows": (i32, [vp, C.c_longlong, i32, i32, vp, vp]),
+    "insg_commit_tokens": (i32, [vp, vp, vp, i32, vp, i32, vp]),
     "insg_bf16_gemv": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "insg_storage_open": (vp, [C.c_char_p, u64, i32]),
     "insg_storage_close": (None, [vp]),
@@ -131,6 +134,16 @@ SIGNATURES = {
     "insg_engine_stream": (vp, [vp]),
     "insg_engine_launch_count": (u64, [vp]),
     "insg_engine_device_bytes": (u64, [vp]),
+    "insg_batch_create": (vp, [vp, i32, i32]),
+    "insg_batch_destroy": (None, [vp]),
+    "insg_batch_forward_tokens": (i32, [vp, vp]),
+    "insg_batch_decode_tokens": (i32, [vp, vp, vp]),
+    "insg_batch_generate": (i32, [vp, vp, i32, vp]),
+    "insg_batch_reset": (i32, [vp]),
+    "insg_batch_position": (i32, [vp]),
+    "insg_batch_read": (i32, [vp, C.c_char_p, i32, vp, u64]),
+    "insg_batch_launch_count": (u64, [vp]),
+    "insg_batch_stream": (vp, [vp]),
 }
 
 

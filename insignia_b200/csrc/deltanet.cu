@@ -30,7 +30,7 @@ constexpr int kSlices = 4; // 32 columns each
 __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__restrict__ state, const float *__restrict__ q16,
                                                                    const float *__restrict__ k16, const float *__restrict__ v32,
                                                                    const float *__restrict__ g32, const float *__restrict__ beta32,
-                                                                   float *__restrict__ out32, int tokens, int qkv_stride)
+                                                                   float *__restrict__ out32, int tokens, int qkv_stride, long long state_stride)
 {
     __shared__ __align__(16) float s_qk[8][2][128]; // per warp: its own copy of the normalised q and k (no block barrier)
     __shared__ __align__(16) float s_part[2][8][32]; // per-warp partial sums over k: [0] memory read-out, [1] output
@@ -42,7 +42,11 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
 
     pdl_launch_dependents();
 
-    float *S = state + size_t(head) * 128 * 128;
+    // blockIdx.y: independent sequence of a decode batch (its own state, its own inputs and outputs)
+    const int seq = blockIdx.y;
+    q16 += size_t(seq) * qkv_stride; k16 += size_t(seq) * qkv_stride; v32 += size_t(seq) * qkv_stride;
+    g32 += seq * 32; beta32 += seq * 32; out32 += size_t(seq) * 4096;
+    float *S = state + size_t(seq) * state_stride + size_t(head) * 128 * 128;
     float4 cell[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) cell[j] = __ldcg(reinterpret_cast<const float4 *>(S + size_t(kr + 32 * j) * 128 + v0));
@@ -139,7 +143,7 @@ extern "C" int insg_deltanet_decode(float *state, const float *q16, const float 
 {
     if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
     return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
-                  beta32, out32, 1, 0);
+                  beta32, out32, 1, 0, 0ll);
 }
 
 extern "C" int insg_deltanet_decode_tokens(float *state, const float *q16, const float *k16, const float *v32, const float *g32,
@@ -149,5 +153,15 @@ extern "C" int insg_deltanet_decode_tokens(float *state, const float *q16, const
     if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
     if (tokens < 1 || tokens > 64 || qkv_stride < 0) return fail(INSG_E_SHAPE, "deltanet: 1..64 tokens per launch");
     return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
-                  beta32, out32, tokens, qkv_stride);
+                  beta32, out32, tokens, qkv_stride, 0ll);
+}
+
+extern "C" int insg_deltanet_decode_batch(float *state, long long state_stride, const float *q16, const float *k16, const float *v32,
+                                          const float *g32, const float *beta32, float *out32, int sequences, int qkv_stride, int pdl,
+                                          insg_stream_t stream)
+{
+    if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
+    if (sequences < 1 || sequences > 64 || qkv_stride < 0 || state_stride < 32 * 128 * 128) return fail(INSG_E_SHAPE, "deltanet: 1..64 sequences");
+    return launch(deltanet_step_kernel, dim3(32 * kSlices, sequences), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
+                  beta32, out32, 1, qkv_stride, state_stride);
 }

@@ -144,6 +144,23 @@ __global__ void concat_kernel(const float *a, const float *b, float *out, int n)
 
 // arg-max with a fixed reduction order, lowest index on ties (src/qwen_kernels.cu:20 is
 // single-CTA; so is this, it is not on the engine's path)
+// One CTA per row of [count][stride] logits: the arg-max of its first n entries (lowest index on ties).
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *x, long long stride, int n, int *out);
+
+// A decode batch's step end: the arg-max of every sequence becomes its next input token and is logged under the
+// current position, which then advances.
+__global__ void commit_tokens_kernel(const int *next, int *tokens, int *log, int capacity, int *position, int n)
+{
+    const int pos = *position;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int t = next[i];
+        tokens[i] = t;
+        if (log && pos >= 0 && pos < capacity) log[size_t(pos) * n + i] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *position = pos + 1;
+}
+
 __global__ void __launch_bounds__(1024) argmax_kernel(const float *x, int n, int *out)
 {
     __shared__ float sv[32];
@@ -205,6 +222,33 @@ static int check_launch(const char *what)
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? INSG_OK : cuda_fail(e, what);
 }
+
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *x, long long stride, int n, int *out)
+{
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    x += size_t(blockIdx.x) * stride;
+    float best = -3.402823466e38f;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += 1024) {
+        const float v = __ldcg(x + i);
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+#pragma unroll
+    for (int m = 16; m; m >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, m);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, m);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 32; w++)
+            if (sv[w] > best || (sv[w] == best && si[w] < idx)) { best = sv[w]; idx = si[w]; }
+        out[blockIdx.x] = idx;
+    }
+}
+
 
 } // namespace insg
 
@@ -298,6 +342,18 @@ int insg_argmax_logits(const float *logits, int n, int *device_token, insg_strea
     if (!logits || !device_token || n <= 0) return fail(INSG_E_ARG, "argmax_logits: bad argument");
     argmax_kernel<<<1, 1024, 0, stream>>>(logits, n, device_token);
     return check_launch("argmax_logits");
+}
+int insg_argmax_rows(const float *logits, long long stride, int n, int count, int *device_tokens, insg_stream_t stream)
+{
+    if (!logits || !device_tokens || n <= 0 || count <= 0 || stride < n) return fail(INSG_E_ARG, "argmax_rows: bad argument");
+    argmax_rows_kernel<<<count, 1024, 0, stream>>>(logits, stride, n, device_tokens);
+    return check_launch("argmax_rows");
+}
+int insg_commit_tokens(const int *next, int *tokens, int *log, int capacity, int *position, int n, insg_stream_t stream)
+{
+    if (!next || !tokens || !position || n <= 0) return fail(INSG_E_ARG, "commit_tokens: bad argument");
+    commit_tokens_kernel<<<1, 64, 0, stream>>>(next, tokens, log, capacity, position, n);
+    return check_launch("commit_tokens");
 }
 int insg_bf16_gemv(const uint16_t *w, const float *x, float *y, int rows, int cols, int pdl, insg_stream_t stream)
 {

@@ -38,6 +38,8 @@ struct SegDev {
     int epilogue, rows;
     __half *prep;            // optional fp16 image [2][rows] of out * prep_w / 16 for a later INSG_PRO_PREPARED launch
     const uint16_t *prep_w;  // bf16 [rows] or null
+    long long conv_stride;   // CONV_SILU with several tokens: 0 = one sequence (history carried through the tokens in order),
+                             // else the tokens are independent sequences and token m's history is conv_state + m * conv_stride
 };
 
 struct GemvParams {
@@ -308,7 +310,7 @@ __device__ __forceinline__ void row_epilogue(const SegDev &s, int row, int m, fl
         break;
     }
     case INSG_EPI_CONV_SILU: {
-        float *st = s.conv_state + size_t(row) * 3;
+        float *st = s.conv_state + size_t(m) * s.conv_stride + size_t(row) * 3;
         const uint2 wv = reinterpret_cast<const uint2 *>(s.conv_w)[row];
         const float w0 = bf16_bits_to_float(wv.x & 0xffff), w1 = bf16_bits_to_float(wv.x >> 16);
         const float w2 = bf16_bits_to_float(wv.y & 0xffff), w3 = bf16_bits_to_float(wv.y >> 16);
@@ -445,7 +447,7 @@ __device__ __forceinline__ void gemv_finish(const GemvParams &p, const GemvRange
             const int tm0 = tmq - (s.nmat == 2 ? (local & 1) : 0);
             // Tokens are independent except for the convolution, whose history is carried from one token to the next:
             // there the 16 row lanes walk the tokens in order, elsewhere the two half-warps take alternate tokens.
-            const bool serial = M > 1 && s.epilogue == INSG_EPI_CONV_SILU;
+            const bool serial = M > 1 && s.epilogue == INSG_EPI_CONV_SILU && s.conv_stride == 0;
             for (int m = serial ? (lane < 16 ? 0 : M) : lane >> 4; m < M; m += serial ? 1 : 2) {
                 float y[2] = {0.f, 0.f};
                 for (int mat = 0; mat < s.nmat; mat++) {

@@ -127,6 +127,7 @@ int gemv_build_params(const insg_gemv_op *op, int M, int max_grid, GemvParams *o
         d.packed = static_cast<const uint8_t *>(s.packed);
         d.packed2 = static_cast<const uint8_t *>(s.packed2);
         d.out = s.out; d.conv_state = s.conv_state; d.conv_w = s.conv_w; d.A_log = s.A_log; d.dt_bias = s.dt_bias;
+        d.conv_stride = s.conv_token_stride;
         if (s.prep) {
             if (s.epilogue != INSG_EPI_RESIDUAL && s.epilogue != INSG_EPI_SWIGLU) return fail(INSG_E_ARG, "gemv: prepared output needs the residual or SwiGLU epilogue");
             if (M != 1) return fail(INSG_E_SHAPE, "gemv: a prepared output carries one token");

@@ -44,6 +44,7 @@ struct GSeg {
     const uint16_t *conv_w;
     const float *A_log;
     const uint16_t *dt_bias;
+    long long conv_stride; // 0: one sequence (history carried through the tokens); else token m's history at conv_state + m * stride
     int tile_begin, ntiles, nmat, epilogue, rows;
 };
 
@@ -290,9 +291,12 @@ __global__ void __launch_bounds__(kGThreads, 1) umma_gemm_kernel(const __grid_co
             if (row < s.rows) {
                 // tokens in order: the convolution history is carried from one token to the next, in registers
                 float h0 = 0.f, h1 = 0.f, h2 = 0.f, cw0 = 0.f, cw1 = 0.f, cw2 = 0.f, cw3 = 0.f;
+                const bool carried = s.epilogue == INSG_EPI_CONV_SILU && s.conv_stride == 0;
                 if (s.epilogue == INSG_EPI_CONV_SILU) {
-                    const float *st = s.conv_state + size_t(row) * 3;
-                    h0 = __ldcg(st); h1 = __ldcg(st + 1); h2 = __ldcg(st + 2);
+                    if (carried) {
+                        const float *st = s.conv_state + size_t(row) * 3;
+                        h0 = __ldcg(st); h1 = __ldcg(st + 1); h2 = __ldcg(st + 2);
+                    }
                     const uint2 wv = reinterpret_cast<const uint2 *>(s.conv_w)[row];
                     cw0 = bf16_bits_to_float(wv.x & 0xffff); cw1 = bf16_bits_to_float(wv.x >> 16);
                     cw2 = bf16_bits_to_float(wv.y & 0xffff); cw3 = bf16_bits_to_float(wv.y >> 16);
@@ -307,6 +311,11 @@ __global__ void __launch_bounds__(kGThreads, 1) umma_gemm_kernel(const __grid_co
                     case INSG_EPI_STORE: out[row] = yv; break;
                     case INSG_EPI_RESIDUAL: out[row] = __ldcg(out + row) + yv; break;
                     case INSG_EPI_CONV_SILU: {
+                        if (!carried) { // independent sequences: each token has its own history
+                            float *st = s.conv_state + size_t(m) * s.conv_stride + size_t(row) * 3;
+                            h0 = __ldcg(st); h1 = __ldcg(st + 1); h2 = __ldcg(st + 2);
+                            st[0] = h1; st[1] = h2; st[2] = yv;
+                        }
                         const float z = fmaf(h0, cw0, fmaf(h1, cw1, fmaf(h2, cw2, yv * cw3)));
                         h0 = h1; h1 = h2; h2 = yv;
                         out[row] = fast_silu(z);
@@ -326,7 +335,7 @@ __global__ void __launch_bounds__(kGThreads, 1) umma_gemm_kernel(const __grid_co
                     default: break;
                     }
                 }
-                if (s.epilogue == INSG_EPI_CONV_SILU) {
+                if (carried) {
                     float *st = s.conv_state + size_t(row) * 3;
                     st[0] = h0; st[1] = h1; st[2] = h2;
                 }
@@ -401,6 +410,7 @@ int gemm_umma_launch(const insg_gemv_op *op, cudaStream_t st)
         g.packed = static_cast<const uint8_t *>(s.packed);
         g.packed2 = static_cast<const uint8_t *>(s.packed2);
         g.out = s.out; g.conv_state = s.conv_state; g.conv_w = s.conv_w; g.A_log = s.A_log; g.dt_bias = s.dt_bias;
+        g.conv_stride = s.conv_token_stride;
         g.nmat = s.epilogue == INSG_EPI_SWIGLU ? 2 : 1;
         if (nmat_all && nmat_all != g.nmat) return fail(INSG_E_SHAPE, "gemm: SwiGLU segments cannot be mixed with others");
         nmat_all = g.nmat;
@@ -410,7 +420,7 @@ int gemm_umma_launch(const insg_gemv_op *op, cudaStream_t st)
     // (tile, token group) items only where whole tiles would leave SMs idle: the groups of a tile then run on different SMs
     // at different times and each streams the tile's weights again
     p.tile_major = tiles >= sm_count() ? 1 : 0;
-    for (int i = 0; i < op->n_segments; i++) p.tile_major |= op->seg[i].epilogue == INSG_EPI_CONV_SILU;
+    for (int i = 0; i < op->n_segments; i++) p.tile_major |= op->seg[i].epilogue == INSG_EPI_CONV_SILU && op->seg[i].conv_token_stride == 0;
     p.error_flag = op->error_flag;
     p.stages = 12;
     p.sfa_lookahead = std::max(0, std::min(g_gemm_lookahead, kGSfaBufs - 2));

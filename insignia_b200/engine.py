@@ -128,3 +128,67 @@ class Engine:
     @property
     def device_bytes(self) -> int:
         return _lib.lib().insg_engine_device_bytes(self._h)
+
+
+class Batch:
+    """1..8 independent sequences decoded in lock step on the weights of an :class:`Engine` (one weight copy, every
+    matrix streamed once per step for all sequences): ``insg_batch_*``.  Close it before its engine."""
+
+    def __init__(self, engine: Engine, sequences: int, max_context: int = 0):
+        self.n = sequences
+        self._engine = engine
+        self._destroy = _lib.lib().insg_batch_destroy
+        self._h = _lib.lib().insg_batch_create(engine._h, sequences, max_context)
+        if not self._h:
+            raise InsigniaError(_lib.lib().insg_last_error().decode())
+
+    def close(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._destroy(h)
+
+    def __del__(self):
+        self.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def _arr(self, tokens):
+        assert len(tokens) == self.n
+        return (C.c_int * self.n)(*[int(t) for t in tokens])
+
+    def forward_tokens(self, tokens):
+        check(_lib.lib().insg_batch_forward_tokens(self._h, self._arr(tokens)))
+
+    def decode_tokens(self, tokens) -> list[int]:
+        out = (C.c_int * self.n)()
+        check(_lib.lib().insg_batch_decode_tokens(self._h, self._arr(tokens), out))
+        return list(out)
+
+    def generate(self, first_tokens, count: int) -> np.ndarray:
+        out = (C.c_int * (self.n * count))()
+        check(_lib.lib().insg_batch_generate(self._h, self._arr(first_tokens), count, out))
+        return np.array(out, dtype=np.int64).reshape(count, self.n)
+
+    def reset(self):
+        check(_lib.lib().insg_batch_reset(self._h))
+
+    @property
+    def position(self) -> int:
+        return _lib.lib().insg_batch_position(self._h)
+
+    def read(self, field: str, sequence: int, count: int = 4096) -> np.ndarray:
+        out = np.empty(count, np.float32)
+        check(_lib.lib().insg_batch_read(self._h, field.encode(), sequence, out.ctypes.data, count))
+        return out
+
+    @property
+    def stream(self) -> int:
+        return _lib.lib().insg_batch_stream(self._h) or 0
+
+    @property
+    def launch_count(self) -> int:
+        return _lib.lib().insg_batch_launch_count(self._h)

@@ -1,5 +1,6 @@
 // Handle-based C face of the C++ host classes (declarations: include/insignia_b200.h, "engine" section).
 #include "insignia_b200.h"
+#include "insignia_batch.hpp"
 #include "insignia_decode.hpp"
 
 #include <cstring>
@@ -18,6 +19,12 @@ struct insg_engine {
     std::unique_ptr<insignia::DecodeWorkspace> ws;
     std::unique_ptr<insignia::Qwen35Decode> dec;
     int device = 0;
+};
+
+// Several sequences in lock step on the weights of an engine (include/insignia_batch.hpp).
+struct insg_batch {
+    insg_engine *engine;
+    std::unique_ptr<insignia::Qwen35BatchDecode> dec;
 };
 
 // Handle over ModelFile + TieredStorage alone (include/insignia_storage.hpp), for callers without C++.
@@ -71,6 +78,19 @@ float *field_ptr(insignia::DecodeWorkspace &x, const std::string &f)
     if (f == "mtp_keys") return x.mtp_keys;
     if (f == "mtp_values") return x.mtp_values;
     return nullptr;
+}
+} // namespace
+
+namespace {
+template <class F> int batch_guarded(insg_batch *b, F &&f)
+{
+    if (!b) return insg::fail(INSG_E_ARG, "null batch");
+    try {
+        cudaSetDevice(b->engine->device);
+        return f();
+    } catch (const std::exception &ex) {
+        return insg::fail(INSG_E_RUNTIME, ex.what());
+    }
 }
 } // namespace
 
@@ -323,6 +343,81 @@ int insg_engine_write(insg_engine *e, const char *field, const float *in, uint64
         return int(INSG_OK);
     });
 }
+insg_batch *insg_batch_create(insg_engine *e, int sequences, int max_context)
+{
+    if (!e) {
+        insg::fail(INSG_E_ARG, "null engine");
+        return nullptr;
+    }
+    try {
+        cudaSetDevice(e->device);
+        auto b = std::make_unique<insg_batch>();
+        b->engine = e;
+        insignia::BatchOptions o;
+        const insignia::DecodeOptions &d = e->ws->options;
+        o.kv_bf16 = d.kv_bf16;
+        o.gate_elementwise = d.gate_elementwise;
+        o.accurate_trig = d.accurate_trig;
+        o.use_graph = d.use_graph;
+        o.n_layers = d.n_layers;
+        o.vocab = d.vocab;
+        b->dec = std::make_unique<insignia::Qwen35BatchDecode>(*e->weights, sequences, max_context > 0 ? max_context : e->ws->max_context, nullptr, o);
+        return b.release();
+    } catch (const std::exception &ex) {
+        insg::fail(INSG_E_RUNTIME, ex.what());
+        return nullptr;
+    }
+}
+void insg_batch_destroy(insg_batch *b)
+{
+    if (!b) return;
+    cudaSetDevice(b->engine->device);
+    delete b;
+}
+int insg_batch_forward_tokens(insg_batch *b, const int *tokens)
+{
+    return batch_guarded(b, [&] {
+        b->dec->forward_tokens(tokens);
+        return int(INSG_OK);
+    });
+}
+int insg_batch_decode_tokens(insg_batch *b, const int *tokens, int *next)
+{
+    return batch_guarded(b, [&] {
+        b->dec->decode_tokens(tokens, next);
+        return int(INSG_OK);
+    });
+}
+int insg_batch_generate(insg_batch *b, const int *first_tokens, int count, int *out)
+{
+    return batch_guarded(b, [&] {
+        b->dec->generate(first_tokens, count, out);
+        return int(INSG_OK);
+    });
+}
+int insg_batch_reset(insg_batch *b)
+{
+    return batch_guarded(b, [&] {
+        cudaStreamSynchronize(b->dec->execution_stream());
+        b->dec->reset();
+        cudaStreamSynchronize(b->dec->execution_stream());
+        return int(INSG_OK);
+    });
+}
+int insg_batch_position(insg_batch *b) { return b ? b->dec->position() : INSG_E_ARG; }
+int insg_batch_read(insg_batch *b, const char *field, int sequence, float *out, uint64_t count)
+{
+    return batch_guarded(b, [&] {
+        const std::string f = field ? field : "";
+        if (f == "hidden" && count == 4096) b->dec->read_hidden(sequence, out);
+        else if (f == "delta_state") b->dec->read_delta_state(sequence, out, count);
+        else return insg::fail(INSG_E_ARG, "unknown batch field");
+        return int(INSG_OK);
+    });
+}
+uint64_t insg_batch_launch_count(insg_batch *b) { return b ? b->dec->launch_count() : 0; }
+insg_stream_t insg_batch_stream(insg_batch *b) { return b ? b->dec->execution_stream() : nullptr; }
+
 void *insg_engine_buffer(insg_engine *e, const char *field)
 {
     if (!e || !field) return nullptr;

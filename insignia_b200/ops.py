@@ -102,6 +102,7 @@ def _gemv_op(inp, segments, prologue="plain", aux=None, norm_w=None, x_out=None,
         g.conv_state, g.conv_w = _p(s.get("conv_state")), _p(s.get("conv_w"))
         g.A_log, g.dt_bias = _p(s.get("A_log")), _p(s.get("dt_bias"))
         g.prep, g.prep_w, g.prep_partials = _p(s.get("prep")), _p(s.get("prep_w")), _p(s.get("prep_partials"))
+        g.conv_token_stride = s.get("conv_token_stride", 0)
     if argmax:
         op.argmax_scratch, op.token_out = _p(argmax["scratch"]), _p(argmax["token_out"])
         op.token_feedback, op.token_log = _p(argmax.get("token_feedback")), _p(argmax.get("token_log"))
@@ -225,6 +226,15 @@ def deltanet_decode_tokens(state, q16, k16, v32, g32, beta32, tokens, qkv_stride
     check(_lib.lib().insg_deltanet_decode_tokens(_p(state), _p(q16), _p(k16), _p(v32), _p(g32), _p(beta32), _p(out), tokens,
                                                  qkv_stride, int(pdl), _stream()))
     return out.reshape(tokens, 32 * 128)
+
+
+def deltanet_decode_batch(state, q16, k16, v32, g32, beta32, sequences, qkv_stride, pdl=False):
+    """One DeltaNet step for ``sequences`` independent sequences; state [sequences][32][128][128], inputs strided like
+    :func:`deltanet_decode_tokens`."""
+    out = torch.empty(sequences * 32 * 128, dtype=torch.float32, device=state.device)
+    check(_lib.lib().insg_deltanet_decode_batch(_p(state), 32 * 128 * 128, _p(q16), _p(k16), _p(v32), _p(g32), _p(beta32), _p(out), sequences,
+                                                qkv_stride, int(pdl), _stream()))
+    return out.reshape(sequences, 32 * 128)
 
 
 def gqa_scratch(device, tokens=0):
