@@ -287,6 +287,17 @@ INSG_API int insg_deltanet_decode_batch(float *state, long long state_stride, co
                                         const float *g32, const float *beta32, float *out32, int sequences, int qkv_stride, int pdl,
                                         insg_stream_t stream);
 
+/* Two consecutive steps for a speculative verify pass: reads `state`, writes the state after the first step to
+ * state_first (may be `state` itself: in place) and the state after the second step to state_second (a different
+ * buffer), so the caller continues from either.  Inputs of step m at + m * qkv_stride / + m * 32, outputs at
+ * + m * 4096, as insg_deltanet_decode_tokens.  No reference counterpart (it has no verify step, src/decode.cu:24-68). */
+INSG_API int insg_deltanet_decode_verify(const float *state, float *state_first, float *state_second, const float *q16,
+                                         const float *k16, const float *v32, const float *g32, const float *beta32, float *out32,
+                                         int qkv_stride, int pdl, insg_stream_t stream);
+/* Convolution history [channels][3] after a rejected second token: from the history after two tokens (`state`, in
+ * place) and the history before them (`snapshot`).  No reference counterpart. */
+INSG_API int insg_conv_rollback(float *state, const float *snapshot, long long channels, insg_stream_t stream);
+
 /* ------------------------------------------------------------ attention */
 
 /* KV cache element type. */
@@ -466,6 +477,15 @@ INSG_API int insg_engine_mtp_draft(insg_engine *e, int token);
  * arg-max back in, `count` times; writes the `count` produced ids to out_tokens (host).
  * Synchronises once at the end.  No reference counterpart (its loop is src/generate_ids.cu:4). */
 INSG_API int insg_engine_generate(insg_engine *e, int first_token, int count, int *out_tokens /* host */);
+/* Speculative greedy decode, draft-1 / verify, on top of Qwen35Decode::mtp_draft (src/decode.cu:24-68; the reference has
+ * no verify step).  prime: the prompt (host array) token by token, every position's row left in the MTP cache; returns
+ * the greedy next token (>= 0).  generate: `count` tokens into out_tokens (host); each step one MTP draft and one
+ * two-token verify pass; a wrong draft is rolled back, so the ids equal plain greedy decode; *accepted (host, may be
+ * NULL) = drafts that were right; forced_drafts (host, `count` ints, may be NULL) replaces the MTP head as the draft
+ * source.  Synchronises every step. */
+INSG_API int insg_engine_prime_speculative(insg_engine *e, const int *prompt /* host */, int count);
+INSG_API int insg_engine_generate_speculative(insg_engine *e, int first_token, int count, int *out_tokens /* host */,
+                                              int *accepted /* host */, const int *forced_drafts /* host */);
 /* The fused-GEMV operations of one token step alone, run `replays` (1..64) times between two CUDA events (one
  * CUDA graph of launches with dependent-launch overlap per replay, or with `persistent` one persistent launch):
  * *ms_per_token = time of one replay, *bytes = the algorithmic weight bytes of those operations, *launches = their

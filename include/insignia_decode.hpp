@@ -93,6 +93,15 @@ public:
     int logits_argmax();
     int mtp_draft(int input_token);
 
+    // Additive: speculative greedy decode, draft-1 / verify (the reference has the draft half only).
+    // prime_speculative: the prompt token by token like forward_token, also leaving every position's row in the MTP
+    // head's cache; returns the greedy next token.  generate_speculative: `count` tokens, each step one MTP draft and
+    // one two-token verify pass of the main model; a right draft yields two tokens per pass, a wrong one is rolled back
+    // (DeltaNet state, convolution history).  Output identical to plain greedy decode.  *accepted receives the number of
+    // drafts that were right.  forced_drafts (optional, `count` entries): drafts from the caller instead of the MTP head.
+    int prime_speculative(const int *prompt, int count);
+    std::vector<int> generate_speculative(int first_token, int count, int *accepted = nullptr, const int *forced_drafts = nullptr);
+
     // Additive: greedy generation with the arg-max fed back on the device; one sync at the end.
     std::vector<int> generate(int first_token, int count);
     uint64_t launch_count() const noexcept { return launches_; }
@@ -130,6 +139,7 @@ private:
     Qwen35Weights &w_;
     DecodeWorkspace &x_;
     std::unique_ptr<Plan> plan_;
+    int mtp_step(int token, bool draft);
     void build_program();
     void run_program(int n_tokens, int token);
     void recover_after_timeout();

@@ -78,6 +78,8 @@ SIGNATURES = {
     "insg_deltanet_decode": (i32, [vp] * 7 + [i32, vp]),
     "insg_deltanet_decode_tokens": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "insg_deltanet_decode_batch": (i32, [vp, C.c_longlong, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "insg_deltanet_decode_verify": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp]),
+    "insg_conv_rollback": (i32, [vp, vp, C.c_longlong, vp]),
     "insg_gqa_scratch_bytes": (sz, [i32]),
     "insg_gqa_decode": (i32, [vp, vp, vp, vp, i32, i32, vp, sz, vp]),
     "insg_gqa_decode_noalloc": (i32, [vp, vp, vp, vp, i32, i32, vp]),
@@ -122,6 +124,8 @@ SIGNATURES = {
     "insg_engine_decode_token": (i32, [vp, i32]),
     "insg_engine_mtp_draft": (i32, [vp, i32]),
     "insg_engine_generate": (i32, [vp, i32, i32, C.POINTER(i32)]),
+    "insg_engine_prime_speculative": (i32, [vp, vp, i32]),
+    "insg_engine_generate_speculative": (i32, [vp, i32, i32, vp, vp, vp]),
     "insg_engine_profile_gemv_chain": (i32, [vp, i32, vp, vp, vp]),
     "insg_engine_set_program_option": (i32, [vp, C.c_char_p, C.c_longlong]),
     "insg_engine_selftest_barrier_timeout": (i32, [vp]),

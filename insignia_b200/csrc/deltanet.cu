@@ -30,7 +30,8 @@ constexpr int kSlices = 4; // 32 columns each
 __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__restrict__ state, const float *__restrict__ q16,
                                                                    const float *__restrict__ k16, const float *__restrict__ v32,
                                                                    const float *__restrict__ g32, const float *__restrict__ beta32,
-                                                                   float *__restrict__ out32, int tokens, int qkv_stride, long long state_stride)
+                                                                   float *__restrict__ out32, int tokens, int qkv_stride, long long state_stride,
+                                                                   float *__restrict__ state_first, float *__restrict__ state_last)
 {
     __shared__ __align__(16) float s_qk[8][2][128]; // per warp: its own copy of the normalised q and k (no block barrier)
     __shared__ __align__(16) float s_part[2][8][32]; // per-warp partial sums over k: [0] memory read-out, [1] output
@@ -114,7 +115,10 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
             po.y = fmaf(cell[j].y, qq[j], po.y);
             po.z = fmaf(cell[j].z, qq[j], po.z);
             po.w = fmaf(cell[j].w, qq[j], po.w);
-            if (step == tokens - 1) *reinterpret_cast<float4 *>(S + size_t(kr + 32 * j) * 128 + v0) = cell[j];
+            // the state after the last step goes to state_last (default: in place); a speculative verify pass also keeps the
+            // state after its first step (state_first), which is the one to continue from when the second token is rejected
+            if (step == tokens - 1) *reinterpret_cast<float4 *>((state_last ? state_last + size_t(head) * 128 * 128 : S) + size_t(kr + 32 * j) * 128 + v0) = cell[j];
+            else if (step == 0 && state_first) *reinterpret_cast<float4 *>(state_first + size_t(head) * 128 * 128 + size_t(kr + 32 * j) * 128 + v0) = cell[j];
         }
 #pragma unroll
         for (int m = 8; m <= 16; m <<= 1) {
@@ -143,7 +147,7 @@ extern "C" int insg_deltanet_decode(float *state, const float *q16, const float 
 {
     if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
     return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
-                  beta32, out32, 1, 0, 0ll);
+                  beta32, out32, 1, 0, 0ll, nullptr, nullptr);
 }
 
 extern "C" int insg_deltanet_decode_tokens(float *state, const float *q16, const float *k16, const float *v32, const float *g32,
@@ -153,7 +157,17 @@ extern "C" int insg_deltanet_decode_tokens(float *state, const float *q16, const
     if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
     if (tokens < 1 || tokens > 64 || qkv_stride < 0) return fail(INSG_E_SHAPE, "deltanet: 1..64 tokens per launch");
     return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
-                  beta32, out32, tokens, qkv_stride, 0ll);
+                  beta32, out32, tokens, qkv_stride, 0ll, nullptr, nullptr);
+}
+
+extern "C" int insg_deltanet_decode_verify(const float *state, float *state_first, float *state_second, const float *q16, const float *k16,
+                                           const float *v32, const float *g32, const float *beta32, float *out32, int qkv_stride, int pdl,
+                                           insg_stream_t stream)
+{
+    if (!state || !state_first || !state_second || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
+    if (qkv_stride < 0 || state_second == state) return fail(INSG_E_SHAPE, "deltanet: the second state needs a buffer of its own");
+    return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, const_cast<float *>(state), q16, k16, v32, g32,
+                  beta32, out32, 2, qkv_stride, 0ll, state_first, state_second);
 }
 
 extern "C" int insg_deltanet_decode_batch(float *state, long long state_stride, const float *q16, const float *k16, const float *v32,
@@ -163,5 +177,5 @@ extern "C" int insg_deltanet_decode_batch(float *state, long long state_stride, 
     if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
     if (sequences < 1 || sequences > 64 || qkv_stride < 0 || state_stride < 32 * 128 * 128) return fail(INSG_E_SHAPE, "deltanet: 1..64 sequences");
     return launch(deltanet_step_kernel, dim3(32 * kSlices, sequences), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
-                  beta32, out32, 1, qkv_stride, state_stride);
+                  beta32, out32, 1, qkv_stride, state_stride, nullptr, nullptr);
 }

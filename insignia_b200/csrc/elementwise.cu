@@ -144,6 +144,18 @@ __global__ void concat_kernel(const float *a, const float *b, float *out, int n)
 
 // arg-max with a fixed reduction order, lowest index on ties (src/qwen_kernels.cu:20 is
 // single-CTA; so is this, it is not on the engine's path)
+// Convolution history after a rejected second token.  `state` holds the history after two tokens (s2, y1, y2) and
+// `snapshot` the history before them (s0, s1, s2): after the first token alone it is (s1, s2, y1).
+__global__ void conv_rollback_kernel(float *state, const float *snapshot, size_t channels)
+{
+    const size_t c = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const float y1 = state[c * 3 + 1];
+    state[c * 3] = snapshot[c * 3 + 1];
+    state[c * 3 + 1] = snapshot[c * 3 + 2];
+    state[c * 3 + 2] = y1;
+}
+
 // One CTA per row of [count][stride] logits: the arg-max of its first n entries (lowest index on ties).
 __global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *x, long long stride, int n, int *out);
 
@@ -342,6 +354,12 @@ int insg_argmax_logits(const float *logits, int n, int *device_token, insg_strea
     if (!logits || !device_token || n <= 0) return fail(INSG_E_ARG, "argmax_logits: bad argument");
     argmax_kernel<<<1, 1024, 0, stream>>>(logits, n, device_token);
     return check_launch("argmax_logits");
+}
+int insg_conv_rollback(float *state, const float *snapshot, long long channels, insg_stream_t stream)
+{
+    if (!state || !snapshot || channels <= 0) return fail(INSG_E_ARG, "conv_rollback: bad argument");
+    conv_rollback_kernel<<<unsigned((channels + 255) / 256), 256, 0, stream>>>(state, snapshot, size_t(channels));
+    return check_launch("conv_rollback");
 }
 int insg_argmax_rows(const float *logits, long long stride, int n, int count, int *device_tokens, insg_stream_t stream)
 {

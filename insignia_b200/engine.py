@@ -77,6 +77,18 @@ class Engine:
         check(_lib.lib().insg_engine_generate(self._h, first_token, count, buf))
         return list(buf)
 
+    def prime_speculative(self, prompt) -> int:
+        """The prompt token by token, every position's row left in the MTP cache; returns the greedy next token."""
+        arr = (C.c_int * len(prompt))(*[int(t) for t in prompt])
+        return check(_lib.lib().insg_engine_prime_speculative(self._h, arr, len(prompt)))
+
+    def generate_speculative(self, first_token: int, count: int, forced_drafts=None):
+        """``count`` greedy tokens by draft-1 / verify; returns (tokens, number of accepted drafts)."""
+        buf, acc = (C.c_int * count)(), C.c_int()
+        forced = None if forced_drafts is None else (C.c_int * count)(*[int(t) for t in forced_drafts])
+        check(_lib.lib().insg_engine_generate_speculative(self._h, first_token, count, buf, C.byref(acc), forced))
+        return list(buf), acc.value
+
     def profile_gemv_chain(self, replays: int = 8) -> dict:
         """The token step's fused-GEMV operations alone, timed between two CUDA events; the sequence state is garbage afterwards (reset())."""
         ms, by, ln = C.c_float(), C.c_uint64(), C.c_int()

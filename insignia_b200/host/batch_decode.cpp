@@ -161,7 +161,7 @@ void Qwen35BatchDecode::enqueue_step()
         op.tokens = B;
         op.layout = m.layout;
         op.error_flag = m.d_error;
-        op.pdl = 0;
+        op.pdl = 1; // every kernel of the step waits for its predecessor before it reads activations
         if (m.layout == 1 && B > 1) {
             op.umma_scratch = m.umma_scratch;
             op.umma_scratch_bytes = m.umma_scratch_bytes;
@@ -190,7 +190,7 @@ void Qwen35BatchDecode::enqueue_step()
     const uint32_t *ew = static_cast<const uint32_t *>(m.embed.weight.data);
     const uint8_t *es = static_cast<const uint8_t *>(m.embed.scales.data);
     for (int s = 0; s < B; s++) {
-        insg_check(insg_mxfp4_embed(ew, es, m.hidden + size_t(s) * kHidden, m.d_tokens + s, m.embed.rows, kHidden, 0, st));
+        insg_check(insg_mxfp4_embed(ew, es, m.hidden + size_t(s) * kHidden, m.d_tokens + s, m.embed.rows, kHidden, 1, st));
         launches_++;
     }
     for (int l = 0; l < n; l++) {
@@ -214,7 +214,7 @@ void Qwen35BatchDecode::enqueue_step()
             in.seg[3] = seg(blk.b, m.b, INSG_EPI_BETA);
             gemv(in);
             insg_check(insg_deltanet_decode_batch(m.delta_state + size_t(di) * kStateLayer, (long long)(24 * kStateLayer), m.qkv, m.qkv + 2048,
-                                                  m.qkv + 4096, m.a, m.b, m.core, B, 8192, 0, st));
+                                                  m.qkv + 4096, m.a, m.b, m.core, B, 8192, 1, st));
             launches_++;
             insg_gemv_op out = {};
             out.in = m.core;
@@ -253,6 +253,9 @@ void Qwen35BatchDecode::enqueue_step()
                 at.fast_trig = options_.accurate_trig ? 0 : 1;
                 at.scratch = static_cast<uint8_t *>(m.attn_scratch) + size_t(s) * m.attn_scratch_each;
                 at.scratch_bytes = m.attn_scratch_each;
+                // safe with dependent-launch overlap: the cache rows a launch fetches before its dependency wait were written
+                // a whole step ago (the launches right before it belong to other sequences, with caches of their own)
+                at.pdl = 1;
                 insg_check(insg_attention_step(&at, st));
                 launches_++;
             }

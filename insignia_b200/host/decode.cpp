@@ -142,6 +142,8 @@ struct Qwen35Decode::Plan {
     cudaGraphExec_t exec_multi{}; // kMultiSteps token steps in one graph, for device-fed generation
     cudaGraphExec_t exec_chunk{}; // one pass of forward_tokens over kChunk prompt tokens
     int *host_result{}; // pinned: {next token, wait-expired flag}, so the per-token read-back is a true asynchronous copy
+    float *spec_state{}, *spec_conv{}, *spec_logits{}; // speculative decode: second DeltaNet state, convolution snapshot, [2][vocab] logits
+    int *spec_pair{};                                  // device: the two arg-max results of a verify pass
     insg_program *prog{};     // the token step as one persistent launch
     std::vector<std::pair<std::string, long long>> program_options; // applied to every program this engine builds
 };
@@ -158,6 +160,7 @@ Qwen35Decode::~Qwen35Decode()
     if (p.exec_chunk) cudaGraphExecDestroy(p.exec_chunk);
     if (p.graph) cudaGraphDestroy(p.graph);
     if (p.prog) insg_program_destroy(p.prog);
+    for (void *q : {(void *)p.spec_state, (void *)p.spec_conv, (void *)p.spec_logits, (void *)p.spec_pair}) cudaFree(q);
     for (const std::string &n : p.pinned) w_.storage().release(n);
     for (const std::string &n : p.pinned_mats) w_.release(n);
     if (p.host_result) cudaFreeHost(p.host_result);
@@ -386,6 +389,10 @@ struct Multi {
     float *hidden, *qkv, *z, *a, *b, *core, *qg, *key, *value, *act;
     int *tokens;
     int T;
+    // speculative verify pass (T == 2): the DeltaNet state is read from dn_in, the state after the first token goes to
+    // dn_first and the state after the second to dn_second (bases of [24][32][128][128]); null = the workspace's state in place
+    const float *dn_in = nullptr;
+    float *dn_first = nullptr, *dn_second = nullptr;
     explicit Multi(DecodeWorkspace &x, int t)
         : hidden(x.multi + kMultiHidden), qkv(x.multi + kMultiQkv), z(x.multi + kMultiZ), a(x.multi + kMultiA), b(x.multi + kMultiB),
           core(x.multi + kMultiCore), qg(x.multi + kMultiQg), key(x.multi + kMultiKey), value(x.multi + kMultiValue),
@@ -439,8 +446,13 @@ void delta_block_multi(Ctx &c, const Qwen35Decode::Plan::Block &b, int di, const
 
     // all T steps in one launch: the state stays on chip between them.  No dependent-launch overlap: the kernel fetches
     // its state before the dependency wait, which is safe because the launch before it (the GEMV) does not write state.
-    insg_check(insg_deltanet_decode_tokens(x.delta_state + size_t(di) * 32 * 128 * 128, u.qkv, u.qkv + 2048, u.qkv + 4096, u.a, u.b, u.core,
-                                           u.T, 8192, c.pdl ? 1 : 0, c.st));
+    const size_t soff = size_t(di) * 32 * 128 * 128;
+    if (u.dn_second)
+        insg_check(insg_deltanet_decode_verify(u.dn_in + soff, u.dn_first + soff, u.dn_second + soff, u.qkv, u.qkv + 2048, u.qkv + 4096, u.a, u.b,
+                                               u.core, 8192, c.pdl ? 1 : 0, c.st));
+    else
+        insg_check(insg_deltanet_decode_tokens(x.delta_state + soff, u.qkv, u.qkv + 2048, u.qkv + 4096, u.a, u.b, u.core, u.T, 8192,
+                                               c.pdl ? 1 : 0, c.st));
     c.launches++;
 
     insg_gemv_op out = {};
@@ -1060,7 +1072,11 @@ void Qwen35Decode::profile_gemv_chain(int replays, float *ms_per_token, uint64_t
     sync_scalars(-1); // the head operations advanced the device-side position; put the host's view back
 }
 
-int Qwen35Decode::mtp_draft(int token)
+int Qwen35Decode::mtp_draft(int token) { return mtp_step(token, true); }
+
+// The MTP block at the current position (reference: src/decode.cu:24-68).  draft = false stops before the head: the call
+// then only leaves the position's row in the MTP cache (a speculative decoder needs every row, the prompt's included).
+int Qwen35Decode::mtp_step(int token, bool draft)
 {
     if (token < 0 || token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
     if (x_.position < 1) throw std::runtime_error("mtp_draft needs a forwarded token");
@@ -1087,6 +1103,10 @@ int Qwen35Decode::mtp_draft(int token)
     launches_ += 4;
     Ctx c{x_, p.stream, pdl, launches_, false, nullptr, nullptr};
     enqueue_attention_block(c, p.mtp, x_.mtp_keys, x_.mtp_values, -1); // rotary position / cache row position-1, position rows attended
+    if (!draft) {
+        fused_token_valid_ = false;
+        return -1;
+    }
 
     insg_gemv_op op = {};
     op.in = x_.hidden;
@@ -1102,6 +1122,130 @@ int Qwen35Decode::mtp_draft(int token)
     run_gemv(c, op);
     fused_token_valid_ = true;
     return logits_argmax();
+}
+
+// ---- speculative greedy decode: draft-1 / verify ---------------------------------------------------------------------
+// The reference has the draft half only (src/decode.cu:24-68).  Verification runs the main model on [token, draft] as
+// one two-token pass over the weights; the first token's state is always kept, the second one's only when the draft
+// was right: the DeltaNet step writes the state after its first token in place and the state after its second into a
+// second buffer (accept = swap the two), the convolution history is rebuilt from a snapshot on a reject, and the KV row
+// of a rejected draft is simply overwritten later.  Greedy output is identical to plain greedy decode.
+int Qwen35Decode::prime_speculative(const int *prompt, int count)
+{
+    if (!prompt || count < 1) throw std::runtime_error("prime_speculative: empty prompt");
+    for (int i = 0; i < count; i++) {
+        forward_token(prompt[i]);
+        if (i + 1 < count) mtp_step(prompt[i + 1], false); // row i of the MTP cache: hidden state i with the embedding of token i + 1
+    }
+    return logits_argmax();
+}
+
+std::vector<int> Qwen35Decode::generate_speculative(int first_token, int count, int *accepted, const int *forced_drafts)
+{
+    std::vector<int> out;
+    if (accepted) *accepted = 0;
+    if (count <= 0) return out;
+    if (first_token < 0 || first_token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
+    if (x_.position + count > x_.max_context) throw std::runtime_error("KV cache full");
+    if (x_.options.gemv_tcgen05) throw std::runtime_error("speculative decode runs on the mma.sync weight layout");
+    Plan &p = plan();
+    const int n = x_.options.n_layers;
+    for (int l = 0; l < n; l++) load_block(l);
+    load_head();
+    load_embed();
+    const size_t state_floats = size_t(24) * 32 * 128 * 128, conv_floats = size_t(24) * 8192 * 3;
+    if (!p.spec_state) {
+        dev_alloc(&p.spec_state, state_floats);
+        dev_alloc(&p.spec_conv, conv_floats);
+        dev_alloc(&p.spec_logits, size_t(2) * Qwen35Shape::vocab);
+        dev_alloc(&p.spec_pair, 2);
+    }
+    Ctx c{x_, p.stream, x_.options.use_pdl, launches_, false, nullptr, nullptr};
+    c.layout = 0;
+    float *cur = x_.delta_state, *alt = p.spec_state;
+    int tok = first_token, hits = 0;
+    out.reserve(size_t(count));
+    auto settle = [&] { // the workspace's own buffer holds the live state again (plain decode and its graph use that pointer)
+        if (cur != x_.delta_state) {
+            cuda_check(cudaMemcpyAsync(x_.delta_state, cur, state_floats * sizeof(float), cudaMemcpyDeviceToDevice, p.stream), "copy state");
+            std::swap(cur, alt);
+        }
+    };
+    while (int(out.size()) < count) {
+        if (count - int(out.size()) == 1) { // one token left: a plain step
+            settle();
+            tok = decode_token(tok);
+            out.push_back(tok);
+            break;
+        }
+        const int P = x_.position;
+        const int draft = forced_drafts ? forced_drafts[out.size()] : mtp_draft(tok);
+        if (draft < 0 || draft >= Qwen35Shape::vocab) throw std::runtime_error("draft token out of range");
+        // ---- verify: tokens [tok, draft] at positions P, P + 1 ----
+        Multi u(x_, 2);
+        u.dn_in = cur;
+        u.dn_first = cur;
+        u.dn_second = alt;
+        const int pair_in[2] = {tok, draft};
+        sync_scalars(-1);
+        cuda_check(cudaMemcpyAsync(u.tokens, pair_in, sizeof(pair_in), cudaMemcpyHostToDevice, p.stream), "copy tokens");
+        cuda_check(cudaMemcpyAsync(p.spec_conv, x_.conv_state, conv_floats * sizeof(float), cudaMemcpyDeviceToDevice, p.stream), "snapshot history");
+        for (int m = 0; m < 2; m++) {
+            insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
+                                        u.hidden + size_t(m) * kHidden, u.tokens + m, p.embed.rows, kHidden, 0, p.stream));
+            launches_++;
+        }
+        for (int l = 0; l < n; l++) {
+            if (Qwen35Shape::full_attention(l)) {
+                const size_t off = size_t(l / 4) * x_.max_context * 1024 * (x_.options.kv_bf16 ? 2 : 4);
+                attention_block_multi(c, p.layers[l], reinterpret_cast<uint8_t *>(x_.kv_keys) + off, reinterpret_cast<uint8_t *>(x_.kv_values) + off, u);
+            } else {
+                delta_block_multi(c, p.layers[l], l - l / 4, u);
+            }
+        }
+        insg_gemv_op head = {};
+        head.in = u.hidden;
+        head.norm_w = p.final_norm;
+        head.cols = kHidden;
+        head.prologue = INSG_PRO_RMSNORM;
+        head.tokens = 2;
+        head.n_segments = 1;
+        head.seg[0] = seg(p.lm_head, p.spec_logits, INSG_EPI_STORE);
+        head.seg[0].rows = x_.options.vocab;
+        run_gemv(c, head);
+        insg_check(insg_argmax_rows(p.spec_logits, x_.options.vocab, x_.options.vocab, 2, p.spec_pair, p.stream));
+        launches_++;
+        int *res = p.host_result;
+        cuda_check(cudaMemcpyAsync(res, p.spec_pair, 2 * sizeof(int), cudaMemcpyDeviceToHost, p.stream), "read tokens");
+        cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
+        const int r1 = res[0], r2 = res[1];
+        out.push_back(r1);
+        if (r1 == draft) { // accepted: both positions stand
+            hits++;
+            out.push_back(r2);
+            std::swap(cur, alt);
+            if (!forced_drafts) { // row P of the MTP cache: hidden state P with the embedding of the accepted draft
+                cuda_check(cudaMemcpyAsync(x_.hidden, u.hidden, kHidden * sizeof(float), cudaMemcpyDeviceToDevice, p.stream), "copy hidden");
+                x_.position = P + 1;
+                mtp_step(draft, false);
+            }
+            cuda_check(cudaMemcpyAsync(x_.hidden, u.hidden + kHidden, kHidden * sizeof(float), cudaMemcpyDeviceToDevice, p.stream), "copy hidden");
+            x_.position = P + 2;
+            tok = r2;
+        } else { // rejected: the state after the first token is the live one
+            insg_check(insg_conv_rollback(x_.conv_state, p.spec_conv, (long long)(conv_floats / 3), p.stream));
+            launches_++;
+            cuda_check(cudaMemcpyAsync(x_.hidden, u.hidden, kHidden * sizeof(float), cudaMemcpyDeviceToDevice, p.stream), "copy hidden");
+            x_.position = P + 1;
+            tok = r1;
+        }
+    }
+    settle();
+    cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
+    fused_token_valid_ = false;
+    p.capturing = true;
+    if (accepted) *accepted = hits;
+    return out;
 }
 
 } // namespace insignia

@@ -283,6 +283,19 @@ int insg_engine_generate(insg_engine *e, int first_token, int count, int *out_to
         return int(INSG_OK);
     });
 }
+int insg_engine_prime_speculative(insg_engine *e, const int *prompt, int count)
+{
+    return guarded(e, [&] { return e->dec->prime_speculative(prompt, count); });
+}
+int insg_engine_generate_speculative(insg_engine *e, int first_token, int count, int *out_tokens, int *accepted, const int *forced_drafts)
+{
+    return guarded(e, [&] {
+        if (!out_tokens && count > 0) return insg::fail(INSG_E_ARG, "null output");
+        const std::vector<int> t = e->dec->generate_speculative(first_token, count, accepted, forced_drafts);
+        if (!t.empty()) std::memcpy(out_tokens, t.data(), t.size() * sizeof(int));
+        return int(INSG_OK);
+    });
+}
 int insg_engine_profile_gemv_chain(insg_engine *e, int replays, float *ms_per_token, uint64_t *bytes, int *launches)
 {
     return guarded(e, [&] {

@@ -135,6 +135,32 @@ def test_cfg3_512_prompt_256_generated_identical_to_reference(cuda, full_ckpt, c
         assert cos(h, ref_hidden) >= 0.9999 and np.max(np.abs(h - ref_hidden)) <= 2e-2 * np.abs(ref_hidden).max()
 
 
+@pytest.mark.parametrize("drafts", ["mtp", "forced"])
+def test_speculative_decode_identical_to_reference(cuda, full_ckpt, cfg3_reference, drafts):
+    """Draft-1 / verify greedy decode against the reference's plain greedy ids over 512 + 256 tokens.  "mtp": the drafts
+    come from the MTP head (on random weights nearly all are wrong: the roll-back path).  "forced": the caller supplies
+    drafts, right ones and wrong ones in runs of three, so that accepted and rejected passes alternate."""
+    from insignia_b200.engine import Engine
+
+    prompt, first, want, min_gap, ref_hidden = cfg3_reference
+    n = len(want)
+    forced = None
+    if drafts == "forced":
+        forced = [want[i] if (i // 3) % 2 == 0 else (want[i] + 1) % 248320 for i in range(n)]
+    with Engine(full_ckpt[1], max_context=len(prompt) + n + 8) as e:
+        assert e.prime_speculative(prompt) == first
+        got, accepted = e.generate_speculative(first, n - 5, forced_drafts=forced)
+        assert got == want[: n - 5], (min_gap, [i for i, (a, b) in enumerate(zip(got, want)) if a != b][:3])
+        assert e.position == len(prompt) + n - 5
+        if forced is not None:
+            assert 0.25 * n < accepted < 0.5 * n, accepted
+        # plain greedy decode carries on from the speculative state
+        assert e.generate(got[-1], 5) == want[n - 5:]
+        h = e.read("hidden")
+        assert cos(h, ref_hidden) >= 0.9999 and np.max(np.abs(h - ref_hidden)) <= 2e-2 * np.abs(ref_hidden).max()
+        print(f"speculative ({drafts}): {accepted} drafts accepted over {n - 5} tokens")
+
+
 def test_prompt_in_passes_of_four_then_greedy_tokens_identical_to_reference(cuda, full_ckpt):
     """The prompt through forward_tokens (four tokens per pass over the weights), then greedy decode: same ids as the
     reference fed token by token."""

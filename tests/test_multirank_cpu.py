@@ -1,5 +1,6 @@
-"""World-size-2 gloo run of the benchmark's replica logic on CPU (no GPU): per-rank prompts differ by rank,
-the step time is the maximum over ranks and the job throughput is the sum of the replicas' tokens over it."""
+"""World-size-2 gloo run of the benchmark's replica logic on CPU (no GPU), through bench.py's own functions: per-rank
+prompts differ by rank, the step time is the maximum over ranks and the job throughput is the sum of the replicas' tokens
+over it."""
 import os
 import subprocess
 import sys
@@ -11,19 +12,17 @@ WORKER = textwrap.dedent("""
     import os, sys, json
     sys.path.insert(0, %r)
     import numpy as np, torch, torch.distributed as dist
+    import bench                                           # the benchmark's own helpers, not a copy of them
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
-    rng = np.random.default_rng(0 + 1000 * rank)          # same derivation as bench.run_native
-    prompt = rng.integers(0, 248320, 16)
-    ms = torch.tensor([10.0 * (rank + 1)])                 # rank 1 is the slow replica
-    dist.barrier()
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    prompt = bench.prompt_for_rank(0, rank, 16)
+    ms = bench.max_over_ranks(10.0 * (rank + 1), dist, "cpu")   # rank 1 is the slow replica
     gathered = [None] * world
     dist.all_gather_object(gathered, prompt.tolist())
     if rank == 0:
         K = 8
-        print(json.dumps({"ms": float(ms.item()), "value": world * K / (float(ms.item()) * 1e-3),
-                          "distinct": gathered[0] != gathered[1]}))
+        print(json.dumps({"ms": ms, "value": bench.job_throughput(world, K, ms), "distinct": gathered[0] != gathered[1],
+                          "rank0_is_reference_prompt": gathered[0] == bench.prompt_for_rank(0, 0, 16).tolist()}))
     dist.barrier()
     dist.destroy_process_group()
 """) % ROOT
@@ -40,7 +39,7 @@ def test_replica_timing_is_max_over_ranks(tmp_path):
 
     line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
     r = json.loads(line)
-    assert r["ms"] == 20.0 and abs(r["value"] - 2 * 8 / 0.020) < 1e-6 and r["distinct"]
+    assert r["ms"] == 20.0 and abs(r["value"] - 2 * 8 / 0.020) < 1e-6 and r["distinct"] and r["rank0_is_reference_prompt"]
 
 
 def test_reference_arm_runs_on_rank0_only():
