@@ -28,6 +28,11 @@ divided by the slowest rank's time (weak scaling).
 (see oracle/Makefile), driven through its public decode_token loop on the same checkpoint and prompt, on rank 0 alone.
 If that library is absent it falls back to the CPU oracle port.
 
+``--config 1`` (configs[1]) times the MXFP4 matrix products alone (the model's three largest shapes at 1, 2, 4, 16 and 64
+tokens; 1-4 tokens on the mma.sync kernel, 16 and 64 on the tcgen05 kernel) and ``--config 2`` (configs[2]) the attention
+decode kernel over cached contexts of 1024, 8192 and 32768 tokens; both print one JSON line with a ``legs`` list and run on
+one GPU.
+
 ``--config 4`` (BASELINE.json configs[4]): ``--batch B`` sequences per GPU decoded in lock step on one weight copy
 (2048-token prompts by default, ``--steps`` generated tokens), aggregate tok/s; with ``--speculative`` the batch-1
 draft-1 / verify greedy loop with its acceptance rate.
@@ -64,7 +69,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--config", type=int, default=3, choices=[3, 4])
+    ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3, 4])
+    ap.add_argument("--shape", default=None, help="config 1: only this matrix, as ROWSxCOLS")
+    ap.add_argument("--tokens", type=int, default=None, help="config 1: only this token count; config 2: only this context length")
     ap.add_argument("--prompt", type=int, default=None, help="prompt tokens (default 512 for config 3, 2048 for config 4)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--kv-bf16", action="store_true", help="bf16 KV cache (the default is the reference's fp32 cache)")
@@ -393,6 +400,114 @@ def run_native(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def _event_us(fn, steps, warmup):
+    """Mean device time of one call: `steps` calls captured into one CUDA graph (so that the host's launch rate is not what
+    is measured), the graph replayed three times between CUDA events on the capturing stream; the fastest replay counts."""
+    import torch
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(warmup):
+            fn()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(steps):
+                fn()
+        graph.replay()
+        side.synchronize()
+        best = None
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side)
+            graph.replay()
+            b.record(side)
+            side.synchronize()
+            ms = a.elapsed_time(b)
+            best = ms if best is None else min(best, ms)
+    return best * 1e3 / steps
+
+
+def run_kernel_configs(args):
+    """configs[1] and configs[2]: the matrix product and the attention decode kernels alone, CUDA events on the launching
+    (current) stream, operands rotated over copies that together exceed the L2 so that every launch streams from HBM."""
+    import torch
+
+    from insignia_b200 import mxfp4, ops
+
+    torch.cuda.set_device(0)
+    peak, src = measured_hbm_peak()
+    K, W = (args.steps if args.steps != 256 else 20), max(3, min(args.warmup, 5))
+    rng = np.random.default_rng(args.seed)
+    legs = []
+    with ClockSampler(0) as clocks:
+        if args.config == 1:
+            shapes = [(24576, 4096), (4096, 12288), (248320, 4096)]
+            if args.shape:
+                shapes = [tuple(int(v) for v in args.shape.lower().split("x"))]
+            for rows, cols in shapes:
+                base = (rng.standard_normal((min(rows, 4096), cols)) * 0.02).astype(np.float32)
+                w, s = mxfp4.quantize_rows(base)
+                reps = -(-rows // base.shape[0])
+                dw = torch.from_numpy(np.tile(w, (reps, 1))[:rows].view(np.int32)).cuda()
+                ds = torch.from_numpy(np.tile(s, (reps, 1))[:rows]).cuda()
+                nbytes = rows * cols * 17 // 32
+                copies = max(2, -(-(160 << 20) // nbytes))
+                for M in ([args.tokens] if args.tokens else [1, 2, 4, 16, 64]):
+                    x = torch.randn(M, cols, device="cuda")
+                    it = [0]
+                    if M >= 16:
+                        packs = [ops.repack_umma(dw, ds) for _ in range(copies)]
+                        scratch = ops.umma_gemm_scratch(cols, M)
+                        kernel = "umma_gemm_kernel (tcgen05 kind::mxf4)"
+
+                        def fn():
+                            it[0] += 1
+                            ops.gemm_umma(packs[it[0] % copies], x, scratch=scratch)
+                    else:
+                        packs = [ops.repack(dw, ds) for _ in range(copies)]
+                        kernel = "gemv_fused_kernel (mma.sync)"
+
+                        def fn():
+                            it[0] += 1
+                            ops.gemv_packed(packs[it[0] % copies], x)
+                    us = _event_us(fn, K, W)
+                    legs.append({"rows": rows, "cols": cols, "tokens": M, "kernel": kernel, "us": us, "tok_per_s": M / us * 1e6,
+                                 "weight_gbs": nbytes / us * 1e-3, "frac_of_peak": nbytes / us * 1e-3 / peak})
+                    del packs
+            metric, unit = "MXFP4 matrix product, weight bytes streamed per second", "GB/s"
+            head = max(legs, key=lambda l: l["frac_of_peak"])["weight_gbs"]
+            work = "configs[1]: y[m] = W x[m], MXFP4 weights, fp32 activations, M tokens"
+        else:
+            for ctx in ([args.tokens] if args.tokens else [1024, 8192, 32768]):
+                for dt in (torch.float32, torch.bfloat16):
+                    n = max(2, -(-(160 << 20) // (2 * ctx * 1024 * (4 if dt == torch.float32 else 2))))
+                    n = min(n, 40)
+                    caches = [(torch.randn(ctx * 1024, device="cuda").to(dt), torch.randn(ctx * 1024, device="cuda").to(dt)) for _ in range(n)]
+                    q = torch.randn(4096, device="cuda")
+                    scratch = ops.gqa_scratch("cuda", ctx)
+                    it = [0]
+
+                    def fn():
+                        it[0] += 1
+                        k, v = caches[it[0] % n]
+                        ops.gqa_decode(q, k, v, ctx, scratch=scratch)
+                    us = _event_us(fn, K, W)
+                    nbytes = 2 * ctx * 1024 * (4 if dt == torch.float32 else 2)
+                    legs.append({"context": ctx, "kv_cache": "f32" if dt == torch.float32 else "bf16", "sequences": 1, "us": us,
+                                 "cache_gbs": nbytes / us * 1e-3, "frac_of_peak": nbytes / us * 1e-3 / peak,
+                                 "sequences_8_us": 8 * us, "note": "eight sequences are eight launches of the same kernel"})
+                    del caches
+            metric, unit = "GQA decode (16 query heads, 4 kv heads, head 256), cache bytes streamed per second", "GB/s"
+            head = max(legs, key=lambda l: l["frac_of_peak"])["cache_gbs"]
+            work = "configs[2]: one query token against a cached context"
+    print(json.dumps({"metric": metric, "value": head, "unit": unit, "n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "native",
+                      "gpu_launches": K * len(legs), "clocks": clocks.summary(),
+                      "config": {"workload": work, "peak_gbs": peak, "peak_source": src,
+                                 "l2": "operands rotate over copies that together exceed the 126 MB L2"}, "legs": legs}), flush=True)
+
+
 def run_config4(args, rank, world, local_rank, dist, st, idx):
     """configs[4]: ``--batch`` sequences per GPU in lock step on one weight copy (the prompt goes through the same batch
     steps), or the batch-1 draft-1 / verify loop with ``--speculative``."""
@@ -527,7 +642,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.config in (1, 2):
+        if rank == 0:
+            run_kernel_configs(args)
+    elif args.impl == "reference":
         run_reference(args, rank, world, local_rank)
     else:
         run_native(args, rank, world, local_rank)

@@ -85,7 +85,11 @@ class Engine:
     def generate_speculative(self, first_token: int, count: int, forced_drafts=None):
         """``count`` greedy tokens by draft-1 / verify; returns (tokens, number of accepted drafts)."""
         buf, acc = (C.c_int * count)(), C.c_int()
-        forced = None if forced_drafts is None else (C.c_int * count)(*[int(t) for t in forced_drafts])
+        forced = None
+        if forced_drafts is not None:  # entry i is the draft offered when i tokens have been produced
+            if len(forced_drafts) < count:
+                raise ValueError("forced_drafts needs one entry per generated token")
+            forced = (C.c_int * len(forced_drafts))(*[int(t) for t in forced_drafts])
         check(_lib.lib().insg_engine_generate_speculative(self._h, first_token, count, buf, C.byref(acc), forced))
         return list(buf), acc.value
 

@@ -2,7 +2,7 @@
 
 Run where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference /path/to/reference-checkout
 
 It writes a seeded 4-layer synthetic checkpoint (the model's layers 0-3: three
 DeltaNet blocks and one attention block, full-size matrices, 64 embedding rows),
@@ -39,7 +39,7 @@ GOLDEN_CFG = dict(layers=(0, 1, 2, 3), vocab_rows=64, mtp=False, lm_head=True, s
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
     tools = os.path.join(args.reference, "tools")
     with tempfile.TemporaryDirectory() as tmp:

@@ -1,4 +1,4 @@
-"""The several-token tcgen05 GEMM (eight tokens per kind::mxf4 instruction), through the C ABI, against the CPU oracle
+"""The several-token tcgen05 GEMM (eight or sixteen tokens per kind::mxf4 instruction, stream-K shares), through the C ABI, against the CPU oracle
 and against the one-token kernels."""
 import os
 import sys
@@ -32,6 +32,24 @@ def test_gemm_umma_vs_oracle(cuda, rows, cols, M):
     # a token's result does not depend on which tokens travel with it
     y1 = host(ops.gemm_umma(P, dev(x[M - 1:M])))
     assert np.max(np.abs(y1[0] - y[M - 1])) <= 1e-6 * np.abs(y[M - 1]).max()
+
+
+@pytest.mark.parametrize("rows,cols,M", [(128 * 37, 512, 16), (4096, 4096, 8), (640, 12288, 40)])
+def test_gemm_umma_is_deterministic_across_cut_units(cuda, rows, cols, M):
+    """Units cut by share boundaries are summed in share order by whichever CTA arrives last: repeated calls must agree
+    bit for bit (shapes chosen so that most units are cut, some into many parts)."""
+    from insignia_b200 import ops
+
+    rng = np.random.default_rng(rows + M)
+    w, s = rand_matrix(rng, rows, cols)
+    x = dev((rng.standard_normal((M, cols)) * 2).astype(np.float32))
+    P = ops.repack_umma(dev(w), dev(s))
+    scratch = ops.umma_gemm_scratch(cols, M)
+    first = host(ops.gemm_umma(P, x, scratch=scratch))
+    for _ in range(5):
+        assert np.array_equal(host(ops.gemm_umma(P, x, scratch=scratch)), first)
+    y64 = orc.gemv_mlx_f64(w, s, host(x)[M - 1])
+    assert np.max(np.abs(first[M - 1] - y64)) <= 4e-6 * np.abs(y64).max()
 
 
 def test_gemm_umma_extreme_tokens(cuda):
