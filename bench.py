@@ -379,8 +379,9 @@ def run_native(args, rank, world, local_rank):
                                "on, weights exceed L2)"},
         "clocks": clocks.summary(),
         "prefill": {"value": world * (args.prompt - PRE) / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": args.prompt - PRE,
-                    "how": "forward_tokens: passes of up to 32 tokens through the tcgen05 kernel (eight tokens per kind::mxf4 "
-                           "instruction), DeltaNet and attention steps token by token; outside the timed metric"},
+                    "how": "forward_tokens: passes of up to 32 tokens through the tcgen05 kernel (sixteen tokens per kind::mxf4 "
+                           "instruction), the DeltaNet recurrence of a pass in one launch per layer, the attention of a pass in "
+                           "two launches per layer; outside the timed metric"},
     }
     if rank == 0 and world == 1:
         if not args.no_reference_check:

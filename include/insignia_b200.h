@@ -358,6 +358,12 @@ typedef struct insg_attn_op {
     int pdl;
 } insg_attn_op;
 INSG_API int insg_attention_step(const insg_attn_op *op /* host */, insg_stream_t stream);
+/* `tokens` consecutive tokens of one sequence in two launches (prompt processing): op describes token 0 (rotary position
+ * and cache row *position + position_offset); token m takes qraw + m * 8192, k_raw + m * 1024, v + m * 1024, writes
+ * out + m * 4096 and cache row + m, and attends the rows up to its own.  scratch: tokens * insg_gqa_scratch_bytes(.)
+ * bytes whose first 64 bytes per token are zero before the first use (the kernel leaves them zero); q_scratch: device,
+ * tokens * 4096 floats.  op->pdl is ignored (plain stream order).  Same math per token as insg_attention_step. */
+INSG_API int insg_attention_chunk(const insg_attn_op *op /* host */, int tokens, float *q_scratch, insg_stream_t stream);
 
 /* ----------------------------------------------- stand-alone small kernels */
 /* One entry point per reference free function, same argument meaning. */

@@ -83,6 +83,7 @@ SIGNATURES = {
     "insg_gqa_scratch_bytes": (sz, [i32]),
     "insg_gqa_decode": (i32, [vp, vp, vp, vp, i32, i32, vp, sz, vp]),
     "insg_gqa_decode_noalloc": (i32, [vp, vp, vp, vp, i32, i32, vp]),
+    "insg_attention_chunk": (i32, [vp, i32, vp, vp]),
     "insg_attention_step": (i32, [C.POINTER(AttnOp), vp]),
     "insg_rmsnorm_bf16": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "insg_rmsnorm_zero_centered": (i32, [vp, vp, vp, i32, i32, C.c_float, vp]),

@@ -34,6 +34,12 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
 
     const int kvh = blockIdx.x / kSplits, split = blockIdx.x % kSplits;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // token of a chunk (plain form only; a single launch has blockIdx.y == 0 and zero strides)
+    const int bt = blockIdx.y;
+    const float *q_in = p.q + size_t(bt) * p.q_stride;
+    float *out_base = p.out + size_t(bt) * p.out_stride;
+    unsigned *counters = reinterpret_cast<unsigned *>(reinterpret_cast<uint8_t *>(p.counters) + size_t(bt) * p.scratch_stride);
+    float *partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(p.partials) + size_t(bt) * p.scratch_stride);
 
     pdl_launch_dependents();
 
@@ -44,6 +50,8 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     if constexpr (FUSED) {
         pos = __ldcg(p.position) + p.position_offset;
         tokens = pos + 1;
+    } else if (p.position) { // chunk: the rows were written by the launch before this one (plain stream order)
+        tokens = __ldcg(p.position) + p.position_offset + bt + 1;
     }
     tokens = max(1, min(tokens, p.max_context)); // host checks; never index past the cache
     int chunk = max(kMinChunk, (tokens + kSplits - 1) / kSplits);
@@ -87,7 +95,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         if constexpr (FUSED) {
             if (warp < 4) {
                 float v[8];
-                const float4 *src = reinterpret_cast<const float4 *>(p.q + size_t(kvh * 4 + warp) * 512 + lane * 8);
+                const float4 *src = reinterpret_cast<const float4 *>(q_in + size_t(kvh * 4 + warp) * 512 + lane * 8);
                 const float4 a = __ldcg(src), b = __ldcg(src + 1);
                 v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
                 norm_rope_256(v, norm_wv, lane, pos, rope_c, rope_s);
@@ -115,7 +123,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
                 }
             }
         } else {
-            for (int i = tid; i < 1024; i += kAtThreads) s_q[i >> 8][i & 255] = __ldcg(p.q + size_t(kvh) * 1024 + i);
+            for (int i = tid; i < 1024; i += kAtThreads) s_q[i >> 8][i & 255] = __ldcg(q_in + size_t(kvh) * 1024 + i);
         }
     }
     __syncthreads();
@@ -228,7 +236,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         }
     }
     __syncthreads();
-    float *part = p.partials + size_t(kvh * kSplits + split) * kPartFloats;
+    float *part = partials + size_t(kvh * kSplits + split) * kPartFloats;
     if (has_work) {
         const int d = tid;
 #pragma unroll
@@ -251,13 +259,13 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const unsigned ticket = atomicAdd(p.counters + kvh, 1u);
+        const unsigned ticket = atomicAdd(counters + kvh, 1u);
         s_last = (ticket == kSplits - 1);
     }
     __syncthreads();
     if (s_last) {
         __threadfence();
-        const float *pp = p.partials + size_t(kvh * kSplits) * kPartFloats;
+        const float *pp = partials + size_t(kvh * kSplits) * kPartFloats;
         // weights of the splits: warp h takes query head h, a lane takes splits lane and lane+32
         if (warp < 4) {
             const int h = warp, sa = lane, sb = lane + 32;
@@ -287,14 +295,52 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
             a.w = fmaf(v.w, e, a.w);
         }
         const float inv = 1.0f / s_lg[h];
-        reinterpret_cast<float4 *>(p.out + size_t(kvh * 4 + h) * 256)[c4] = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
-        if (tid == 0) p.counters[kvh] = 0u;
+        reinterpret_cast<float4 *>(out_base + size_t(kvh * 4 + h) * 256)[c4] = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+        if (tid == 0) counters[kvh] = 0u;
     }
 }
 
-template <bool BF16, bool FUSED> int launch_attn(const AttnParams &p, cudaStream_t st, bool pdl)
+template <bool BF16, bool FUSED> int launch_attn(const AttnParams &p, cudaStream_t st, bool pdl, int chunk_tokens = 1)
 {
-    return launch(attn_splitk_kernel<BF16, FUSED>, dim3(4 * kSplits), dim3(kAtThreads), 0, st, pdl, p);
+    return launch(attn_splitk_kernel<BF16, FUSED>, dim3(4 * kSplits, chunk_tokens), dim3(kAtThreads), 0, st, pdl, p);
+}
+
+// A chunk of consecutive tokens, step one: per token m (one CTA each) the per-head RMSNorm + partial RoPE of the 16 query
+// heads (into qn[m][16][256]) and of the 4 key heads, and the token's key and value rows written to the cache at row
+// position + offset + m.  Warp tasks 0..15 = query heads, 16..19 = key heads, 20..23 = value heads.
+// (reference: split_q_gate + qwen35_qk_norm_rope_gate + store_kv, src/qwen_kernels.cu:15,31 and src/ops.cu:9, once per token)
+template <bool BF16> __global__ void __launch_bounds__(kAtThreads) attn_chunk_prepare_kernel(const __grid_constant__ AttnParams p, float *qn)
+{
+    using Row = KvRow<BF16>;
+    const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = __ldcg(p.position) + p.position_offset + m;
+    if (pos < 0 || pos >= p.max_context) return; // host checks; never index past the cache
+    float rope_c[8], rope_s[8];
+    if (lane < 8) rope_table(pos, lane, p.fast_trig != 0, rope_c, rope_s);
+    for (int task = warp; task < 24; task += kAtWarps) {
+        if (task < 20) {
+            const bool is_q = task < 16;
+            const int h = is_q ? task : task - 16;
+            const float *src = is_q ? p.q + size_t(m) * 8192 + size_t(h) * 512 + lane * 8 : p.k_raw + size_t(m) * 1024 + h * 256 + lane * 8;
+            const float4 a = __ldcg(reinterpret_cast<const float4 *>(src)), b = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
+            float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            norm_rope_256(v, reinterpret_cast<const uint4 *>(is_q ? p.q_w : p.k_w)[lane], lane, pos, rope_c, rope_s);
+            if (is_q) {
+                float4 *dst = reinterpret_cast<float4 *>(qn + size_t(m) * 4096 + h * 256 + lane * 8);
+                dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+                dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+                const size_t row = (size_t(pos) * 4 + h) * 256 + lane * 8;
+#pragma unroll
+                for (int j = 0; j < 8; j++) Row::store(p.kc, row + j, v[j]);
+            }
+        } else {
+            const int h = task - 20;
+            const size_t row = (size_t(pos) * 4 + h) * 256 + lane * 8;
+#pragma unroll
+            for (int j = 0; j < 8; j++) Row::store(p.vc, row + j, __ldcg(p.v_new + size_t(m) * 1024 + h * 256 + lane * 8 + j));
+        }
+    }
 }
 
 size_t attn_scratch_bytes() { return 64 + size_t(4) * kSplits * kPartFloats * sizeof(float); }
@@ -365,6 +411,30 @@ int insg_gqa_decode(const float *q, const void *k_cache, const void *v_cache, fl
     if (kv_dtype != INSG_KV_F32 && kv_dtype != INSG_KV_BF16) return fail(INSG_E_ARG, "gqa_decode: bad kv dtype");
     if (scratch_bytes < attn_scratch_bytes()) return fail(INSG_E_SHAPE, "gqa_decode: scratch too small");
     return attn_plain_launch(q, k_cache, v_cache, out, tokens, kv_dtype, scratch, stream);
+}
+
+int insg_attention_chunk(const insg_attn_op *op, int tokens, float *q_scratch, insg_stream_t stream)
+{
+    if (!op || !op->qraw || !op->k_raw || !op->v || !op->q_norm_w || !op->k_norm_w || !op->k_cache || !op->v_cache ||
+        !op->out || !op->position || !op->scratch || !q_scratch)
+        return fail(INSG_E_ARG, "attention_chunk: null pointer");
+    if (tokens < 1 || tokens > 65535) return fail(INSG_E_SHAPE, "attention_chunk: 1 <= tokens <= 65535");
+    if (op->scratch_bytes < size_t(tokens) * attn_scratch_bytes()) return fail(INSG_E_SHAPE, "attention_chunk: scratch too small");
+    if (op->max_context <= 0) return fail(INSG_E_SHAPE, "attention_chunk: max_context");
+    AttnParams p = {};
+    p.q = op->qraw; p.k_raw = op->k_raw; p.v_new = op->v; p.q_w = op->q_norm_w; p.k_w = op->k_norm_w;
+    p.kc = op->k_cache; p.vc = op->v_cache; p.out = op->out;
+    p.position = op->position; p.position_offset = op->position_offset;
+    p.max_context = op->max_context; p.fast_trig = op->fast_trig;
+    const bool bf16 = op->kv_dtype == INSG_KV_BF16;
+    int rc = bf16 ? launch(attn_chunk_prepare_kernel<true>, dim3(tokens), dim3(kAtThreads), 0, stream, false, p, q_scratch)
+                  : launch(attn_chunk_prepare_kernel<false>, dim3(tokens), dim3(kAtThreads), 0, stream, false, p, q_scratch);
+    if (rc != INSG_OK) return rc;
+    // step two: every (kv head, split, token) CTA is the plain split-K decode of its token over the rows up to its own
+    p.q = q_scratch; p.q_stride = 4096; p.out_stride = 4096; p.scratch_stride = attn_scratch_bytes();
+    p.counters = static_cast<unsigned *>(op->scratch);
+    p.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(op->scratch) + 64);
+    return bf16 ? launch_attn<true, false>(p, stream, false, tokens) : launch_attn<false, false>(p, stream, false, tokens);
 }
 
 int insg_attention_step(const insg_attn_op *op, insg_stream_t stream)

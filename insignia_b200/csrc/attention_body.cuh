@@ -25,6 +25,10 @@ struct AttnParams {
     int fast_trig;
     unsigned *counters;    // [4] at the head of scratch
     float *partials;       // [4][kSplits][kPartFloats]
+    // a chunk of consecutive tokens in one launch (blockIdx.y = token; all zero for a single token): token m uses
+    // q + m * q_stride, out + m * out_stride, scratch + m * scratch_stride bytes, and sees position + offset + m + 1 rows
+    int q_stride, out_stride;
+    size_t scratch_stride;
 };
 
 // A lane's 8 dims of one cache row, as loaded (converted only when used, so that two token groups can be in flight).

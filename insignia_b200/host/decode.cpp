@@ -33,8 +33,8 @@ constexpr size_t kMultiHidden = 0, kMultiQkv = kMultiHidden + size_t(kBigChunk) 
                  kMultiA = kMultiZ + size_t(kBigChunk) * 4096, kMultiB = kMultiA + size_t(kBigChunk) * 32,
                  kMultiCore = kMultiB + size_t(kBigChunk) * 32, kMultiQg = kMultiCore + size_t(kBigChunk) * 4096,
                  kMultiKey = kMultiQg + size_t(kBigChunk) * 8192, kMultiValue = kMultiKey + size_t(kBigChunk) * 1024,
-                 kMultiAct = kMultiValue + size_t(kBigChunk) * 1024, kMultiTokens = kMultiAct + size_t(kBigChunk) * 12288,
-                 kMultiFloats = kMultiTokens + kBigChunk;
+                 kMultiAct = kMultiValue + size_t(kBigChunk) * 1024, kMultiQn = kMultiAct + size_t(kBigChunk) * 12288,
+                 kMultiTokens = kMultiQn + size_t(kBigChunk) * 4096, kMultiFloats = kMultiTokens + kBigChunk;
 constexpr size_t kPrepBytes = kPrepSums + 2 * 296 * sizeof(float); // one row of sums per image
 const char *const kLM = "language_model";
 
@@ -90,14 +90,15 @@ void DecodeWorkspace::allocate()
     dev_alloc(&d_token, 4 + size_t(max_context) + 1); // token, position, next, pad, then the token log
     d_position = d_token + 1;
     d_next = d_token + 2;
-    cuda_check(cudaMalloc(&attn_scratch, insg_gqa_scratch_bytes(max_context)), "cudaMalloc attention scratch");
+    // one region per token of a prompt chunk; the single-token step uses the first
+    cuda_check(cudaMalloc(&attn_scratch, size_t(kBigChunk) * insg_gqa_scratch_bytes(max_context)), "cudaMalloc attention scratch");
     cuda_check(cudaMalloc(&argmax_scratch, insg_gemv_argmax_scratch_bytes()), "cudaMalloc arg-max scratch");
     cuda_check(cudaMalloc(&prep, kPrepBytes), "cudaMalloc prepared inputs");
     cuda_check(cudaMalloc(&multi, kMultiFloats * sizeof(float)), "cudaMalloc multi-token buffers");
     umma_scratch_bytes = insg_umma_gemm_scratch_bytes(kInter, kBigChunk);
     cuda_check(cudaMalloc(&umma_scratch, umma_scratch_bytes), "cudaMalloc tcgen05 activation image");
     cuda_check(cudaMemsetAsync(prep, 0, kPrepBytes, stream), "memset");
-    cuda_check(cudaMemsetAsync(attn_scratch, 0, 64, stream), "memset");
+    cuda_check(cudaMemsetAsync(attn_scratch, 0, size_t(kBigChunk) * insg_gqa_scratch_bytes(max_context), stream), "memset");
     cuda_check(cudaMemsetAsync(argmax_scratch, 0, 64, stream), "memset");
     cuda_check(cudaMemsetAsync(d_token, 0, (4 + size_t(max_context) + 1) * sizeof(int), stream), "memset");
     // The reference leaves the KV caches uninitialised (src/decode.cu:10); rows are always written before they are read.
@@ -386,7 +387,7 @@ static void enqueue_attention_block(Ctx &c, const Qwen35Decode::Plan::Block &b, 
 // weights once for the T tokens; the DeltaNet and attention steps, which are recurrences, run token by token.
 namespace {
 struct Multi {
-    float *hidden, *qkv, *z, *a, *b, *core, *qg, *key, *value, *act;
+    float *hidden, *qkv, *z, *a, *b, *core, *qg, *key, *value, *act, *qn;
     int *tokens;
     int T;
     // speculative verify pass (T == 2): the DeltaNet state is read from dn_in, the state after the first token goes to
@@ -396,7 +397,7 @@ struct Multi {
     explicit Multi(DecodeWorkspace &x, int t)
         : hidden(x.multi + kMultiHidden), qkv(x.multi + kMultiQkv), z(x.multi + kMultiZ), a(x.multi + kMultiA), b(x.multi + kMultiB),
           core(x.multi + kMultiCore), qg(x.multi + kMultiQg), key(x.multi + kMultiKey), value(x.multi + kMultiValue),
-          act(x.multi + kMultiAct), tokens(reinterpret_cast<int *>(x.multi + kMultiTokens)), T(t)
+          act(x.multi + kMultiAct), qn(x.multi + kMultiQn), tokens(reinterpret_cast<int *>(x.multi + kMultiTokens)), T(t)
     {
     }
 };
@@ -484,27 +485,26 @@ void attention_block_multi(Ctx &c, const Qwen35Decode::Plan::Block &b, void *kc,
     in.seg[2] = seg(b.v, u.value, INSG_EPI_STORE);
     run_gemv(c, in);
 
-    for (int m = 0; m < u.T; m++) { // token m sits at the device position + m and sees the rows of the tokens before it
-        insg_attn_op at = {};
-        at.qraw = u.qg + size_t(m) * 8192;
-        at.k_raw = u.key + size_t(m) * 1024;
-        at.v = u.value + size_t(m) * 1024;
-        at.q_norm_w = b.q_norm;
-        at.k_norm_w = b.k_norm;
-        at.k_cache = kc;
-        at.v_cache = vc;
-        at.out = u.core + size_t(m) * 4096;
-        at.position = x.d_position;
-        at.position_offset = m;
-        at.max_context = x.max_context;
-        at.kv_dtype = x.options.kv_bf16 ? INSG_KV_BF16 : INSG_KV_F32;
-        at.fast_trig = x.options.accurate_trig ? 0 : 1;
-        at.scratch = x.attn_scratch;
-        at.scratch_bytes = insg_gqa_scratch_bytes(x.max_context);
-        at.pdl = 0; // it fetches cache rows before the dependency wait; the row of token m - 1 was written by the launch before
-        insg_check(insg_attention_step(&at, c.st));
-        c.launches++;
-    }
+    // token m sits at the device position + m and sees the rows up to its own: the keys and values of the whole chunk
+    // go to the cache first, then every token's attention runs in one launch
+    insg_attn_op at = {};
+    at.qraw = u.qg;
+    at.k_raw = u.key;
+    at.v = u.value;
+    at.q_norm_w = b.q_norm;
+    at.k_norm_w = b.k_norm;
+    at.k_cache = kc;
+    at.v_cache = vc;
+    at.out = u.core;
+    at.position = x.d_position;
+    at.position_offset = 0;
+    at.max_context = x.max_context;
+    at.kv_dtype = x.options.kv_bf16 ? INSG_KV_BF16 : INSG_KV_F32;
+    at.fast_trig = x.options.accurate_trig ? 0 : 1;
+    at.scratch = x.attn_scratch;
+    at.scratch_bytes = size_t(kBigChunk) * insg_gqa_scratch_bytes(x.max_context);
+    insg_check(insg_attention_chunk(&at, u.T, u.qn, c.st));
+    c.launches += 2;
 
     insg_gemv_op o = {};
     o.in = u.core;
@@ -739,7 +739,7 @@ bool Qwen35Decode::selftest_barrier_timeout()
     const bool gave_up = result[1] != 0;
     insg_check(insg_program_recover(p.prog, p.stream));
     cuda_check(cudaMemsetAsync(x_.d_token + 3, 0, sizeof(int), p.stream), "clear status");
-    cuda_check(cudaMemsetAsync(x_.attn_scratch, 0, 64, p.stream), "clear attention tickets");
+    cuda_check(cudaMemsetAsync(x_.attn_scratch, 0, size_t(kBigChunk) * insg_gqa_scratch_bytes(x_.max_context), p.stream), "clear attention tickets");
     cuda_check(cudaMemsetAsync(x_.argmax_scratch, 0, 64, p.stream), "clear arg-max ticket");
     fused_token_valid_ = false;
     return gave_up;
@@ -910,7 +910,7 @@ void Qwen35Decode::recover_after_timeout()
     Plan &p = plan();
     if (p.prog) insg_program_recover(p.prog, p.stream);
     cudaMemsetAsync(x_.d_token + 3, 0, sizeof(int), p.stream);
-    cudaMemsetAsync(x_.attn_scratch, 0, 64, p.stream);
+    cudaMemsetAsync(x_.attn_scratch, 0, size_t(kBigChunk) * insg_gqa_scratch_bytes(x_.max_context), p.stream);
     cudaMemsetAsync(x_.argmax_scratch, 0, 64, p.stream);
     cudaStreamSynchronize(p.stream);
     fused_token_valid_ = false;

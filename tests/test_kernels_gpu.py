@@ -388,6 +388,40 @@ def test_attention_step_sequence_vs_oracle(cuda, kv_bf16):
     assert np.max(np.abs(host(kc.float())[:70 * 1024] - kc_ref[:70 * 1024])) <= (2.0 ** -7 * np.abs(kc_ref).max() if kv_bf16 else 1e-5)
 
 
+@pytest.mark.parametrize("kv_bf16", [False, True])
+def test_attention_chunk_equals_token_steps_bitwise(cuda, kv_bf16):
+    """A chunk of consecutive tokens in two launches (keys and values of the chunk stored first, then every token's
+    attention over the rows up to its own) against the same tokens fed one insg_attention_step at a time."""
+    from insignia_b200 import ops
+
+    rng = np.random.default_rng(41)
+    ctx, start, T = 400, 37, 32
+    qw, kw = bf16(rng, 256), bf16(rng, 256)
+    dt = torch.bfloat16 if kv_bf16 else torch.float32
+    history_k, history_v = torch.randn(ctx * 1024, device="cuda").to(dt), torch.randn(ctx * 1024, device="cuda").to(dt)
+    qraw = dev(rng.standard_normal((T, 8192)).astype(np.float32))
+    kraw = dev(rng.standard_normal((T, 1024)).astype(np.float32))
+    v = dev(rng.standard_normal((T, 1024)).astype(np.float32))
+    pos_dev = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kc1, vc1 = history_k.clone(), history_v.clone()
+    scratch = ops.gqa_scratch("cuda")
+    want = []
+    for m in range(T):
+        pos_dev.fill_(start + m)
+        want.append(host(ops.attention_step(qraw[m], kraw[m], v[m], dev(qw), dev(kw), kc1, vc1, pos_dev, ctx, scratch)))
+    kc2, vc2 = history_k.clone(), history_v.clone()
+    pos_dev.fill_(start)
+    big = torch.zeros(T * scratch.numel(), dtype=torch.uint8, device="cuda")
+    got = host(ops.attention_chunk(qraw, kraw, v, dev(qw), dev(kw), kc2, vc2, pos_dev, ctx, big, T))
+    assert np.array_equal(got, np.stack(want))
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    # the scratch heads are left zero: a second chunk right behind the first gives the same again
+    kc3, vc3 = history_k.clone(), history_v.clone()
+    assert np.array_equal(host(ops.attention_chunk(qraw, kraw, v, dev(qw), dev(kw), kc3, vc3, pos_dev, ctx, big, T)), got)
+    with pytest.raises(Exception, match="scratch"):
+        ops.attention_chunk(qraw, kraw, v, dev(qw), dev(kw), kc3, vc3, pos_dev, ctx, scratch, T)
+
+
 # -------------------------------------------------------------------- small ops
 def test_small_ops_vs_oracle(cuda):
     from insignia_b200 import mxfp4, ops
