@@ -72,6 +72,7 @@ def parse_args():
     ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3, 4])
     ap.add_argument("--shape", default=None, help="config 1: only this matrix, as ROWSxCOLS")
     ap.add_argument("--tokens", type=int, default=None, help="config 1: only this token count; config 2: only this context length")
+    ap.add_argument("--eager", action="store_true", help="configs 1 and 2: plain launches instead of one CUDA graph of the steps (for profiler captures)")
     ap.add_argument("--prompt", type=int, default=None, help="prompt tokens (default 512 for config 3, 2048 for config 4)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--kv-bf16", action="store_true", help="bf16 KV cache (the default is the reference's fp32 cache)")
@@ -401,7 +402,7 @@ def run_native(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-def _event_us(fn, steps, warmup):
+def _event_us(fn, steps, warmup, eager=False):
     """Mean device time of one call: `steps` calls captured into one CUDA graph (so that the host's launch rate is not what
     is measured), the graph replayed three times between CUDA events on the capturing stream; the fastest replay counts."""
     import torch
@@ -411,6 +412,14 @@ def _event_us(fn, steps, warmup):
         for _ in range(warmup):
             fn()
         side.synchronize()
+        if eager:  # launch by launch: includes the host's launch rate
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side)
+            for _ in range(steps):
+                fn()
+            b.record(side)
+            side.synchronize()
+            return a.elapsed_time(b) * 1e3 / steps
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
             for _ in range(steps):
@@ -472,7 +481,7 @@ def run_kernel_configs(args):
                         def fn():
                             it[0] += 1
                             ops.gemv_packed(packs[it[0] % copies], x)
-                    us = _event_us(fn, K, W)
+                    us = _event_us(fn, K, W, args.eager)
                     legs.append({"rows": rows, "cols": cols, "tokens": M, "kernel": kernel, "us": us, "tok_per_s": M / us * 1e6,
                                  "weight_gbs": nbytes / us * 1e-3, "frac_of_peak": nbytes / us * 1e-3 / peak})
                     del packs
@@ -493,7 +502,7 @@ def run_kernel_configs(args):
                         it[0] += 1
                         k, v = caches[it[0] % n]
                         ops.gqa_decode(q, k, v, ctx, scratch=scratch)
-                    us = _event_us(fn, K, W)
+                    us = _event_us(fn, K, W, args.eager)
                     nbytes = 2 * ctx * 1024 * (4 if dt == torch.float32 else 2)
                     legs.append({"context": ctx, "kv_cache": "f32" if dt == torch.float32 else "bf16", "sequences": 1, "us": us,
                                  "cache_gbs": nbytes / us * 1e-3, "frac_of_peak": nbytes / us * 1e-3 / peak,
