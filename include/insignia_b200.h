@@ -38,8 +38,8 @@ enum {
 
 INSG_API const char *insg_last_error(void);  /* host string, thread-local */
 INSG_API int insg_version(void);
-/* Tuning knobs of the optional tcgen05 GEMV kernel, process-wide, for benchmarking only: "umma_stages",
- * "umma_nacc", "umma_prefetch".  The default path has no process-wide knobs. */
+/* Kept for binary compatibility: this build has no process-wide tuning keys (every launch shape is fixed per kernel;
+ * per-engine choices are DecodeOptions), so every key answers INSG_E_ARG. */
 INSG_API int insg_tune_set(const char *key /* host */, int value);
 
 /* ------------------------------------------------------------------ MXFP4 */
@@ -269,7 +269,11 @@ INSG_API uint64_t insg_program_weight_bytes(const insg_program *prog);
 /* One gated-delta-rule step for 32 value heads (16 q/k heads, head>>1), dk=dv=128.
  * state fp32 [32][128(k)][128(v)] updated in place; q16,k16 fp32 [16][128];
  * v32 fp32 [32][128]; g32, beta32 fp32 [32]; out32 fp32 [32][128].
- * Replaces deltanet_decode (include/insignia_deltanet.cuh:5, src/deltanet.cu:4-14). */
+ * Replaces deltanet_decode (include/insignia_deltanet.cuh:5, src/deltanet.cu:4-14).
+ * pdl (all DeltaNet entry points): 1 launches with programmatic stream serialization; the kernel then reads its STATE
+ * before the dependency wait and everything else after it.  Precondition: the launch right before it in the stream does
+ * not write the state (the engine puts a GEMV there); two pdl = 1 steps on the same state back to back would race, so
+ * pass pdl = 0 when nothing separates them. */
 INSG_API int insg_deltanet_decode(float *state, const float *q16, const float *k16, const float *v32,
                                   const float *g32, const float *beta32, float *out32, int pdl,
                                   insg_stream_t stream);

@@ -37,9 +37,6 @@ int sm_count()
     return cached[dev];
 }
 
-int umma_tune(const char *key, int value);
-int umma_gemm_tune(const char *key, int value);
-
 } // namespace insg
 
 extern "C" {
@@ -48,10 +45,9 @@ const char *insg_last_error(void) { return insg::g_error.c_str(); }
 int insg_version(void) { return 100; }
 int insg_tune_set(const char *key, int value)
 {
+    (void)value;
     if (!key) return insg::fail(INSG_E_ARG, "tune: null key");
-    if (insg::umma_tune(key, value) == INSG_OK) return INSG_OK;
-    if (insg::umma_gemm_tune(key, value) == INSG_OK) return INSG_OK;
-    return insg::fail(INSG_E_ARG, "unknown tuning key");
+    return insg::fail(INSG_E_ARG, "unknown tuning key"); // this build has none: launch shapes are fixed per kernel
 }
 
 } // extern "C"

@@ -385,24 +385,13 @@ __global__ void repack_umma_kernel(const uint32_t *__restrict__ w, const uint8_t
 }
 
 namespace {
-struct UTune {
-    int stages = 16;
-    int nacc = 8;
-    int prefetch = 8;
-} g_utune;
+// fixed launch shape (measured best; no process-wide knobs: engines and threads share this library)
+constexpr int kUStages = 16, kUNacc = 8, kUPrefetch = 8;
 
 std::mutex g_attr_mutex;
 bool g_attr_done[64] = {false}; // the shared-memory opt-in is a per-device function attribute
 } // namespace
 
-int umma_tune(const char *key, int value)
-{
-    const std::string k = key;
-    if (k == "umma_stages") { g_utune.stages = std::max(2, std::min(value, 24)); return INSG_OK; }
-    if (k == "umma_nacc") { g_utune.nacc = std::max(1, std::min(value, kAccMax)); return INSG_OK; }
-    if (k == "umma_prefetch") { g_utune.prefetch = std::max(1, std::min(value, 24)); return INSG_OK; }
-    return INSG_E_ARG;
-}
 
 int gemv_umma_launch(const insg_gemv_op *op, cudaStream_t st)
 {
@@ -446,11 +435,11 @@ int gemv_umma_launch(const insg_gemv_op *op, cudaStream_t st)
     }
     p.error_flag = static_cast<int *>(op->error_flag);
     const size_t fixed = size_t(p.nkb) * kBImgPerKb + 512 + 64 * 4 + 1024;
-    int stages = std::min(g_utune.stages, int((size_t(220) * 1024 - fixed) / kURec));
+    int stages = std::min(kUStages, int((size_t(220) * 1024 - fixed) / kURec));
     stages = std::max(2, std::min(stages, 24));
     p.stages = stages;
-    p.nacc = g_utune.nacc;
-    p.prefetch = std::min(g_utune.prefetch, stages);
+    p.nacc = kUNacc;
+    p.prefetch = std::min(kUPrefetch, stages);
     const size_t smem = size_t(stages) * kURec + fixed;
     {
         int dev = 0;

@@ -445,8 +445,8 @@ void delta_block_multi(Ctx &c, const Qwen35Decode::Plan::Block &b, int di, const
     in.seg[3] = seg(b.b, u.b, INSG_EPI_BETA);
     run_gemv(c, in);
 
-    // all T steps in one launch: the state stays on chip between them.  No dependent-launch overlap: the kernel fetches
-    // its state before the dependency wait, which is safe because the launch before it (the GEMV) does not write state.
+    // all T steps in one launch: the state stays on chip between them.  The kernel fetches its state before the
+    // dependent-launch wait, which is safe because the launch before it (the GEMV) does not write state.
     const size_t soff = size_t(di) * 32 * 128 * 128;
     if (u.dn_second)
         insg_check(insg_deltanet_decode_verify(u.dn_in + soff, u.dn_first + soff, u.dn_second + soff, u.qkv, u.qkv + 2048, u.qkv + 4096, u.a, u.b,
@@ -803,7 +803,7 @@ void Qwen35Decode::replay_token_step()
 void Qwen35Decode::forward_token(int token)
 {
     if (token < 0 || token >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
-    if (x_.options.n_layers > 3 && x_.position >= x_.max_context) throw std::runtime_error("KV cache full");
+    if (x_.position >= x_.max_context) throw std::runtime_error("KV cache full"); // also bounds the token log
     if (persistent()) {
         run_program(1, token);
     } else {
@@ -820,7 +820,7 @@ void Qwen35Decode::forward_tokens(const int *tokens, int count)
     if (!tokens) throw std::runtime_error("forward_tokens: null token list");
     for (int i = 0; i < count; i++)
         if (tokens[i] < 0 || tokens[i] >= Qwen35Shape::vocab) throw std::runtime_error("token out of range");
-    if (x_.options.n_layers > 3 && x_.position + count > x_.max_context) throw std::runtime_error("KV cache full");
+    if (x_.position + count > x_.max_context) throw std::runtime_error("KV cache full");
     if (x_.options.gemv_tcgen05) { // that layout takes one token per launch
         for (int i = 0; i < count; i++) forward_token(tokens[i]);
         return;
