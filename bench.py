@@ -546,14 +546,27 @@ def run_config4(args, rank, world, local_rank, dist, st, idx):
         if args.speculative:
             prompt = [int(t) for t in rng.integers(0, VOCAB, args.prompt)]
             stream = torch.cuda.ExternalStream(eng.stream, device=local_rank)
+            # the plain greedy continuation first: the right drafts for the upper-bound leg
             first = eng.prime_speculative(prompt)
-            for _ in range(max(1, W // 4)):
-                toks, _ = eng.generate_speculative(first, 4)
-                first = toks[-1]
-            ms, (toks, accepted) = timed(stream, lambda: eng.generate_speculative(first, K))
+            truth = eng.generate(first, W + K)
+
+            def leg(forced):
+                eng.reset()
+                tok = eng.prime_speculative(prompt)
+                if W > 0:
+                    toks, _ = eng.generate_speculative(tok, W, forced_drafts=truth[:W] if forced else None)
+                    tok = toks[-1]
+                ms, (toks, acc) = timed(stream, lambda: eng.generate_speculative(tok, K, forced_drafts=truth[W:W + K] if forced else None))
+                return ms, toks, acc
+
+            ms_right, toks_right, acc_right = leg(True)
+            ms, toks, accepted = leg(False)
             seqs, launches = 1, 0
-            extra = {"draft_acceptance": accepted / max(1, K), "note": "random-weight MTP head: drafts are almost never accepted, so a "
-                     "step costs a draft plus a two-token verify pass for one token"}
+            extra = {"draft_acceptance": accepted / max(1, K), "identical_to_plain_greedy": toks == truth[W:W + K] and toks_right == truth[W:W + K],
+                     "all_drafts_right": {"value": job_throughput(world, K, ms_right), "unit": "tok/s", "accepted": acc_right,
+                                          "how": "the same loop with the right drafts supplied by the caller: the bound a trained MTP head approaches"},
+                     "note": "random-weight MTP head: its drafts are almost never accepted, so a step costs a draft plus a two-token verify "
+                             "pass for one token"}
         else:
             bt = Batch(eng, B, ctx)
             stream = torch.cuda.ExternalStream(bt.stream, device=local_rank)

@@ -145,6 +145,10 @@ struct Qwen35Decode::Plan {
     int *host_result{}; // pinned: {next token, wait-expired flag}, so the per-token read-back is a true asynchronous copy
     float *spec_state{}, *spec_conv{}, *spec_logits{}; // speculative decode: second DeltaNet state, convolution snapshot, [2][vocab] logits
     int *spec_pair{};                                  // device: the two arg-max results of a verify pass
+    int *spec_host{};                                  // pinned: {token, draft} on the way in
+    cudaGraphExec_t exec_verify[2]{};                  // the verify pass, by which DeltaNet state buffer is the live one
+    cudaGraphExec_t exec_mtp[2]{};                     // the MTP block without / with its head
+    int verify_runs[2]{}, mtp_runs[2]{};               // first run of each form is eager (kernel variants set their attributes)
     insg_program *prog{};     // the token step as one persistent launch
     std::vector<std::pair<std::string, long long>> program_options; // applied to every program this engine builds
 };
@@ -162,6 +166,9 @@ Qwen35Decode::~Qwen35Decode()
     if (p.graph) cudaGraphDestroy(p.graph);
     if (p.prog) insg_program_destroy(p.prog);
     for (void *q : {(void *)p.spec_state, (void *)p.spec_conv, (void *)p.spec_logits, (void *)p.spec_pair}) cudaFree(q);
+    if (p.spec_host) cudaFreeHost(p.spec_host);
+    for (cudaGraphExec_t e : {p.exec_verify[0], p.exec_verify[1], p.exec_mtp[0], p.exec_mtp[1]})
+        if (e) cudaGraphExecDestroy(e);
     for (const std::string &n : p.pinned) w_.storage().release(n);
     for (const std::string &n : p.pinned_mats) w_.release(n);
     if (p.host_result) cudaFreeHost(p.host_result);
@@ -1072,6 +1079,39 @@ void Qwen35Decode::profile_gemv_chain(int replays, float *ms_per_token, uint64_t
     sync_scalars(-1); // the head operations advanced the device-side position; put the host's view back
 }
 
+namespace {
+// Runs `enqueue` on the stream: eagerly the first time (kernel variants set their function attributes on first use),
+// from then on as a replay of a graph captured on the second call.  The launches must read their variable inputs (tokens,
+// position) from device memory.
+template <class F> void run_graphed(bool use_graph, cudaStream_t st, cudaGraphExec_t &exec, int &runs, uint64_t &launches, F &&enqueue)
+{
+    if (!use_graph || runs == 0) {
+        enqueue();
+        runs++;
+        return;
+    }
+    if (!exec) {
+        const uint64_t before = launches;
+        cudaGraph_t g = nullptr;
+        cuda_check(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal), "begin graph capture");
+        try {
+            enqueue();
+        } catch (...) {
+            cudaStreamEndCapture(st, &g);
+            if (g) cudaGraphDestroy(g);
+            throw;
+        }
+        cuda_check(cudaStreamEndCapture(st, &g), "end graph capture");
+        const cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
+        cudaGraphDestroy(g);
+        cuda_check(e, "instantiate graph");
+        launches = before;
+    }
+    cuda_check(cudaGraphLaunch(exec, st), "launch graph");
+    launches++;
+}
+} // namespace
+
 int Qwen35Decode::mtp_draft(int token) { return mtp_step(token, true); }
 
 // The MTP block at the current position (reference: src/decode.cu:24-68).  draft = false stops before the head: the call
@@ -1094,32 +1134,34 @@ int Qwen35Decode::mtp_step(int token, bool draft)
     if (!p.head_ready || !p.embed_ready) throw std::runtime_error("mtp_draft needs a forwarded token");
     const bool pdl = x_.options.use_pdl;
     sync_scalars(token);
-    // embedding of the input token and the last hidden state, each normalised, side by side in qkv[8192]
-    insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
-                                x_.down, x_.d_token, p.embed.rows, kHidden, 0, p.stream));
-    insg_check(insg_rmsnorm_bf16(x_.down, p.mtp_norm_e, nullptr, x_.qkv, 1, kHidden, 0, p.stream));
-    insg_check(insg_rmsnorm_bf16(x_.hidden, p.mtp_norm_h, nullptr, x_.qkv + kHidden, 1, kHidden, 0, p.stream));
-    insg_check(insg_bf16_gemv(p.mtp_fc, x_.qkv, x_.hidden, kHidden, 2 * kHidden, 0, p.stream)); // overwrites the residual, as the reference
-    launches_ += 4;
-    Ctx c{x_, p.stream, pdl, launches_, false, nullptr, nullptr};
-    enqueue_attention_block(c, p.mtp, x_.mtp_keys, x_.mtp_values, -1); // rotary position / cache row position-1, position rows attended
+    run_graphed(x_.options.use_graph, p.stream, p.exec_mtp[draft ? 1 : 0], p.mtp_runs[draft ? 1 : 0], launches_, [&] {
+        // embedding of the input token and the last hidden state, each normalised, side by side in qkv[8192]
+        insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
+                                    x_.down, x_.d_token, p.embed.rows, kHidden, 0, p.stream));
+        insg_check(insg_rmsnorm_bf16(x_.down, p.mtp_norm_e, nullptr, x_.qkv, 1, kHidden, 0, p.stream));
+        insg_check(insg_rmsnorm_bf16(x_.hidden, p.mtp_norm_h, nullptr, x_.qkv + kHidden, 1, kHidden, 0, p.stream));
+        insg_check(insg_bf16_gemv(p.mtp_fc, x_.qkv, x_.hidden, kHidden, 2 * kHidden, 0, p.stream)); // overwrites the residual, as the reference
+        launches_ += 4;
+        Ctx c{x_, p.stream, pdl, launches_, false, nullptr, nullptr};
+        enqueue_attention_block(c, p.mtp, x_.mtp_keys, x_.mtp_values, -1); // rotary position / cache row position-1, position rows attended
+        if (!draft) return;
+        insg_gemv_op op = {};
+        op.in = x_.hidden;
+        op.norm_w = p.mtp_norm;
+        op.x_out = x_.norm;
+        op.cols = kHidden;
+        op.prologue = INSG_PRO_RMSNORM;
+        op.n_segments = 1;
+        op.seg[0] = seg(p.lm_head, x_.logits, INSG_EPI_LOGITS);
+        op.seg[0].rows = x_.options.vocab;
+        op.argmax_scratch = x_.argmax_scratch;
+        op.token_out = x_.d_next;
+        run_gemv(c, op);
+    });
     if (!draft) {
         fused_token_valid_ = false;
         return -1;
     }
-
-    insg_gemv_op op = {};
-    op.in = x_.hidden;
-    op.norm_w = p.mtp_norm;
-    op.x_out = x_.norm;
-    op.cols = kHidden;
-    op.prologue = INSG_PRO_RMSNORM;
-    op.n_segments = 1;
-    op.seg[0] = seg(p.lm_head, x_.logits, INSG_EPI_LOGITS);
-    op.seg[0].rows = x_.options.vocab;
-    op.argmax_scratch = x_.argmax_scratch;
-    op.token_out = x_.d_next;
-    run_gemv(c, op);
     fused_token_valid_ = true;
     return logits_argmax();
 }
@@ -1159,6 +1201,7 @@ std::vector<int> Qwen35Decode::generate_speculative(int first_token, int count, 
         dev_alloc(&p.spec_conv, conv_floats);
         dev_alloc(&p.spec_logits, size_t(2) * Qwen35Shape::vocab);
         dev_alloc(&p.spec_pair, 2);
+        cuda_check(cudaMallocHost(&p.spec_host, 4 * sizeof(int)), "cudaMallocHost");
     }
     Ctx c{x_, p.stream, x_.options.use_pdl, launches_, false, nullptr, nullptr};
     c.layout = 0;
@@ -1186,35 +1229,39 @@ std::vector<int> Qwen35Decode::generate_speculative(int first_token, int count, 
         u.dn_in = cur;
         u.dn_first = cur;
         u.dn_second = alt;
-        const int pair_in[2] = {tok, draft};
+        p.spec_host[0] = tok;
+        p.spec_host[1] = draft;
         sync_scalars(-1);
-        cuda_check(cudaMemcpyAsync(u.tokens, pair_in, sizeof(pair_in), cudaMemcpyHostToDevice, p.stream), "copy tokens");
-        cuda_check(cudaMemcpyAsync(p.spec_conv, x_.conv_state, conv_floats * sizeof(float), cudaMemcpyDeviceToDevice, p.stream), "snapshot history");
-        for (int m = 0; m < 2; m++) {
-            insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
-                                        u.hidden + size_t(m) * kHidden, u.tokens + m, p.embed.rows, kHidden, 0, p.stream));
-            launches_++;
-        }
-        for (int l = 0; l < n; l++) {
-            if (Qwen35Shape::full_attention(l)) {
-                const size_t off = size_t(l / 4) * x_.max_context * 1024 * (x_.options.kv_bf16 ? 2 : 4);
-                attention_block_multi(c, p.layers[l], reinterpret_cast<uint8_t *>(x_.kv_keys) + off, reinterpret_cast<uint8_t *>(x_.kv_values) + off, u);
-            } else {
-                delta_block_multi(c, p.layers[l], l - l / 4, u);
+        cuda_check(cudaMemcpyAsync(u.tokens, p.spec_host, 2 * sizeof(int), cudaMemcpyHostToDevice, p.stream), "copy tokens");
+        const int which = cur == x_.delta_state ? 0 : 1;
+        run_graphed(x_.options.use_graph, p.stream, p.exec_verify[which], p.verify_runs[which], launches_, [&] {
+            cuda_check(cudaMemcpyAsync(p.spec_conv, x_.conv_state, conv_floats * sizeof(float), cudaMemcpyDeviceToDevice, p.stream), "snapshot history");
+            for (int m = 0; m < 2; m++) {
+                insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
+                                            u.hidden + size_t(m) * kHidden, u.tokens + m, p.embed.rows, kHidden, 0, p.stream));
+                launches_++;
             }
-        }
-        insg_gemv_op head = {};
-        head.in = u.hidden;
-        head.norm_w = p.final_norm;
-        head.cols = kHidden;
-        head.prologue = INSG_PRO_RMSNORM;
-        head.tokens = 2;
-        head.n_segments = 1;
-        head.seg[0] = seg(p.lm_head, p.spec_logits, INSG_EPI_STORE);
-        head.seg[0].rows = x_.options.vocab;
-        run_gemv(c, head);
-        insg_check(insg_argmax_rows(p.spec_logits, x_.options.vocab, x_.options.vocab, 2, p.spec_pair, p.stream));
-        launches_++;
+            for (int l = 0; l < n; l++) {
+                if (Qwen35Shape::full_attention(l)) {
+                    const size_t off = size_t(l / 4) * x_.max_context * 1024 * (x_.options.kv_bf16 ? 2 : 4);
+                    attention_block_multi(c, p.layers[l], reinterpret_cast<uint8_t *>(x_.kv_keys) + off, reinterpret_cast<uint8_t *>(x_.kv_values) + off, u);
+                } else {
+                    delta_block_multi(c, p.layers[l], l - l / 4, u);
+                }
+            }
+            insg_gemv_op head = {};
+            head.in = u.hidden;
+            head.norm_w = p.final_norm;
+            head.cols = kHidden;
+            head.prologue = INSG_PRO_RMSNORM;
+            head.tokens = 2;
+            head.n_segments = 1;
+            head.seg[0] = seg(p.lm_head, p.spec_logits, INSG_EPI_STORE);
+            head.seg[0].rows = x_.options.vocab;
+            run_gemv(c, head);
+            insg_check(insg_argmax_rows(p.spec_logits, x_.options.vocab, x_.options.vocab, 2, p.spec_pair, p.stream));
+            launches_++;
+        });
         int *res = p.host_result;
         cuda_check(cudaMemcpyAsync(res, p.spec_pair, 2 * sizeof(int), cudaMemcpyDeviceToHost, p.stream), "read tokens");
         cuda_check(cudaStreamSynchronize(p.stream), "synchronize");
