@@ -369,6 +369,34 @@ INSG_API int insg_attention_step(const insg_attn_op *op /* host */, insg_stream_
  * tokens * 4096 floats.  op->pdl is ignored (plain stream order).  Same math per token as insg_attention_step. */
 INSG_API int insg_attention_chunk(const insg_attn_op *op /* host */, int tokens, float *q_scratch, insg_stream_t stream);
 
+/* ------------------------------------------------ tensor-parallel exchange */
+/* One-shot all-reduce (sum) of a short fp32 vector over NVLink peer memory, for the exchange step of a tensor-parallel
+ * decode block.  No reference counterpart: the reference is single-GPU and has no collective call site.
+ *
+ * One process per GPU: every rank calls insg_comm_create (allocates its exchange buffer on the current device),
+ * insg_comm_handle (64 bytes to all-gather among the ranks by any host channel), insg_comm_connect (maps the peers'
+ * buffers).  insg_allreduce_oneshot then is ONE kernel per rank: peer stores of the rank's vector into every rank's
+ * buffer, a release flag, a bounded wait for the other ranks' flags, the sum in rank order (bit-identical on every rank),
+ * in place.  count: a multiple of 4, <= max_floats; data 16-byte aligned; every rank must call with the same count, in
+ * the same order.  If a wait runs out (default 1 s, insg_comm_set_timeout) the rank's error flag is set
+ * (insg_comm_error reads it, synchronising the stream) and the result is undefined; insg_comm_reset on every rank,
+ * with no call in flight anywhere, makes the communicator usable again.  Capturable in a CUDA graph. */
+typedef struct insg_comm insg_comm;
+INSG_API insg_comm *insg_comm_create(int rank, int world /* 1..8 */, int max_floats);
+INSG_API void insg_comm_destroy(insg_comm *c);
+INSG_API int insg_comm_handle(insg_comm *c, void *handle64 /* host, 64 bytes out */);
+INSG_API int insg_comm_connect(insg_comm *c, const void *handles /* host, world x 64 bytes, in rank order */);
+INSG_API int insg_comm_set_timeout(insg_comm *c, unsigned long long timeout_ns);
+INSG_API int insg_comm_error(insg_comm *c, int *host_out, insg_stream_t stream);
+INSG_API int insg_comm_reset(insg_comm *c, insg_stream_t stream);
+INSG_API int insg_allreduce_oneshot(insg_comm *c, float *data, int count, insg_stream_t stream);
+/* All ranks in one process on ONE GPU (tests, development): comms[i] = rank i of `world`, created on the same device.
+ * The ranks run as one cooperative launch (their CTAs wait on one another, so they may not be separate launches).
+ * skip_rank >= 0 leaves that rank silent: the others' waits run out and set their error flags (failure-detection test). */
+INSG_API int insg_comm_connect_local(insg_comm **comms /* host array */, int world);
+INSG_API int insg_allreduce_oneshot_local(insg_comm **comms, float **data /* host array of device pointers */, int world, int count,
+                                          int skip_rank, insg_stream_t stream);
+
 /* ----------------------------------------------- stand-alone small kernels */
 /* One entry point per reference free function, same argument meaning. */
 

@@ -83,6 +83,16 @@ SIGNATURES = {
     "insg_gqa_scratch_bytes": (sz, [i32]),
     "insg_gqa_decode": (i32, [vp, vp, vp, vp, i32, i32, vp, sz, vp]),
     "insg_gqa_decode_noalloc": (i32, [vp, vp, vp, vp, i32, i32, vp]),
+    "insg_comm_create": (vp, [i32, i32, i32]),
+    "insg_comm_destroy": (None, [vp]),
+    "insg_comm_handle": (i32, [vp, vp]),
+    "insg_comm_connect": (i32, [vp, vp]),
+    "insg_comm_set_timeout": (i32, [vp, C.c_ulonglong]),
+    "insg_comm_error": (i32, [vp, vp, vp]),
+    "insg_comm_reset": (i32, [vp, vp]),
+    "insg_allreduce_oneshot": (i32, [vp, vp, i32, vp]),
+    "insg_comm_connect_local": (i32, [vp, i32]),
+    "insg_allreduce_oneshot_local": (i32, [vp, vp, i32, i32, i32, vp]),
     "insg_attention_chunk": (i32, [vp, i32, vp, vp]),
     "insg_attention_step": (i32, [C.POINTER(AttnOp), vp]),
     "insg_rmsnorm_bf16": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),

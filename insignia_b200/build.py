@@ -17,7 +17,7 @@ LIB = os.path.join(LIB_DIR, "libinsignia_b200.so")
 OBJ_DIR = os.path.join(LIB_DIR, "obj")
 
 SOURCES = [
-    "csrc/mxfp4_gemv.cu", "csrc/gemv_fused.cu", "csrc/umma_gemv.cu", "csrc/umma_gemm.cu", "csrc/persistent.cu", "csrc/deltanet.cu", "csrc/attention.cu", "csrc/elementwise.cu", "csrc/compat_kernels.cu", "csrc/capi_util.cu",
+    "csrc/mxfp4_gemv.cu", "csrc/gemv_fused.cu", "csrc/umma_gemv.cu", "csrc/umma_gemm.cu", "csrc/persistent.cu", "csrc/deltanet.cu", "csrc/attention.cu", "csrc/elementwise.cu", "csrc/allreduce.cu", "csrc/compat_kernels.cu", "csrc/capi_util.cu",
     "host/model_file.cpp", "host/storage.cpp", "host/qwen35.cpp", "host/decode.cpp", "host/batch_decode.cpp", "host/engine_capi.cpp",
 ]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler",

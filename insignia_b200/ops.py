@@ -209,6 +209,64 @@ class Program:
         return _lib.lib().insg_program_weight_bytes(self._h)
 
 
+class Comm:
+    """One rank's end of the one-shot all-reduce (``insg_comm_*``).  ``Comm.local(world, n)`` builds all ranks on the
+    current GPU (they then run as one cooperative launch); across processes: create, all-gather ``handle()``, ``connect``."""
+
+    def __init__(self, rank: int, world: int, max_floats: int):
+        self._h = _lib.lib().insg_comm_create(rank, world, max_floats)
+        if not self._h:
+            raise RuntimeError(_lib.lib().insg_last_error().decode())
+        self.rank, self.world, self.max_floats = rank, world, max_floats
+
+    def close(self):
+        if getattr(self, "_h", None):
+            _lib.lib().insg_comm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        check(_lib.lib().insg_comm_handle(self._h, buf))
+        return buf.raw
+
+    def connect(self, handles):
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.world
+        check(_lib.lib().insg_comm_connect(self._h, blob))
+
+    def set_timeout(self, ns: int):
+        check(_lib.lib().insg_comm_set_timeout(self._h, ns))
+
+    def error(self) -> int:
+        out = C.c_int()
+        check(_lib.lib().insg_comm_error(self._h, C.byref(out), _stream()))
+        return out.value
+
+    def reset(self):
+        check(_lib.lib().insg_comm_reset(self._h, _stream()))
+
+    def allreduce(self, data, count=None):
+        check(_lib.lib().insg_allreduce_oneshot(self._h, _p(data), count or data.numel(), _stream()))
+        return data
+
+    @staticmethod
+    def local(world: int, max_floats: int):
+        comms = [Comm(r, world, max_floats) for r in range(world)]
+        arr = (C.c_void_p * world)(*[c._h for c in comms])
+        check(_lib.lib().insg_comm_connect_local(arr, world))
+        return comms
+
+    @staticmethod
+    def allreduce_local(comms, tensors, count=None, skip_rank=-1):
+        world = len(comms)
+        hs = (C.c_void_p * world)(*[c._h for c in comms])
+        ds = (C.c_void_p * world)(*[_p(t) for t in tensors])
+        check(_lib.lib().insg_allreduce_oneshot_local(hs, ds, world, count or tensors[0].numel(), skip_rank, _stream()))
+
+
 def argmax_scratch(device):
     return torch.zeros(_lib.lib().insg_gemv_argmax_scratch_bytes(), dtype=torch.uint8, device=device)
 
