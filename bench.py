@@ -33,6 +33,11 @@ tokens; 1-4 tokens on the mma.sync kernel, 16 and 64 on the tcgen05 kernel) and 
 decode kernel over cached contexts of 1024, 8192 and 32768 tokens; both print one JSON line with a ``legs`` list and run on
 one GPU.
 
+``--config 5`` (under torchrun with N ranks, one per GPU): the exchange step of a tensor-parallel block -- the one-shot
+all-reduce of fp32[4096] over NVLink peer memory beside torch.distributed's (NCCL) all-reduce of the same vector -- and one
+MLP block sharded N ways (gate|up rows and down columns per rank, fused GEMV launches, one all-reduce) beside the same block
+on one GPU.  Device times, max over ranks.
+
 ``--config 4`` (BASELINE.json configs[4]): ``--batch B`` sequences per GPU decoded in lock step on one weight copy
 (2048-token prompts by default, ``--steps`` generated tokens), aggregate tok/s; with ``--speculative`` the batch-1
 draft-1 / verify greedy loop with its acceptance rate.
@@ -69,7 +74,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3, 4])
+    ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--shape", default=None, help="config 1: only this matrix, as ROWSxCOLS")
     ap.add_argument("--tokens", type=int, default=None, help="config 1: only this token count; config 2: only this context length")
     ap.add_argument("--eager", action="store_true", help="configs 1 and 2: plain launches instead of one CUDA graph of the steps (for profiler captures)")
@@ -518,6 +523,161 @@ def run_kernel_configs(args):
                                  "l2": "operands rotate over copies that together exceed the 126 MB L2"}, "legs": legs}), flush=True)
 
 
+def tp_shards(rank: int, world: int, seed: int):
+    """One MLP's matrices (4096 -> 12288 -> 4096, seeded, the same on every rank) and this rank's shards in the MLX layout:
+    rows [r, r + 12288 / world) of gate and up, the matching columns of down."""
+    from insignia_b200 import mxfp4
+
+    rng = np.random.default_rng(seed)
+    full = {n: mxfp4.quantize_rows((rng.standard_normal(shape) * 0.02).astype(np.float32))
+            for n, shape in (("gate", (12288, 4096)), ("up", (12288, 4096)), ("down", (4096, 12288)))}
+    per = 12288 // world
+    r0, r1 = rank * per, (rank + 1) * per
+    shard = {"gate": (full["gate"][0][r0:r1], full["gate"][1][r0:r1]), "up": (full["up"][0][r0:r1], full["up"][1][r0:r1]),
+             "down": (np.ascontiguousarray(full["down"][0][:, r0 // 8:r1 // 8]), np.ascontiguousarray(full["down"][1][:, r0 // 32:r1 // 32]))}
+    return full, shard, per
+
+
+def run_tp_blocks(args, rank, world, local_rank):
+    """config 5: the tensor-parallel exchange step and one sharded MLP block (see the module docstring)."""
+    import torch
+
+    from insignia_b200 import ops
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    K = args.steps if args.steps != 256 else 200
+    dev = lambda a: torch.from_numpy(a.view(np.int32) if a.dtype == np.uint32 else a).cuda()  # noqa: E731
+
+    comm = ops.Comm(rank, world, 4096)
+    if dist:
+        mine = torch.frombuffer(bytearray(comm.handle()), dtype=torch.uint8).cuda()
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        comm.connect([h.cpu().numpy().tobytes() for h in every])
+    else:
+        comm.connect([comm.handle()])
+
+    def graph_us(fn, steps):
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+            side.synchronize()
+            if dist:
+                dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(steps):
+                    fn()
+            g.replay()
+            side.synchronize()
+            best = None
+            for _ in range(3):
+                if dist:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(side)
+                g.replay()
+                b.record(side)
+                side.synchronize()
+                ms = max_over_ranks(a.elapsed_time(b), dist, "cuda")
+                best = ms if best is None else min(best, ms)
+        return best * 1e3 / steps
+
+    x = torch.randn(4096, device="cuda")
+    with ClockSampler(local_rank) as clocks:
+        oneshot_us = graph_us(lambda: comm.allreduce(x), K)
+        nccl_us = None
+        if dist:
+            try:
+                nccl_us = graph_us(lambda: dist.all_reduce(x), K)
+            except Exception as e:  # a collective library that cannot be captured is timed launch by launch
+                sys.stderr.write(f"[bench] NCCL all-reduce not captured in a graph ({e}); timing eager launches\n")
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                for _ in range(10):
+                    dist.all_reduce(x)
+                a.record()
+                for _ in range(K):
+                    dist.all_reduce(x)
+                b.record()
+                torch.cuda.synchronize()
+                nccl_us = max_over_ranks(a.elapsed_time(b), dist, "cuda") * 1e3 / K
+
+        full, shard, per = tp_shards(rank, world, args.seed)
+        P = {n: ops.repack(dev(w), dev(s)) for n, (w, s) in shard.items()}
+        hidden = torch.randn(4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(args.seed))
+        nw = torch.ones(4096, dtype=torch.int16, device="cuda") * 0x3F80  # bf16 1.0
+        act, y = torch.zeros(per, device="cuda"), torch.zeros(4096, device="cuda")
+
+        def block():
+            ops.gemv_fused(hidden, [dict(packed=P["gate"], packed2=P["up"], out=act, rows=per, epilogue="swiglu")], prologue="rmsnorm", norm_w=nw)
+            ops.gemv_fused(act, [dict(packed=P["down"], out=y, rows=4096, epilogue="store")], cols=per)
+            comm.allreduce(y)
+
+        tp_us = graph_us(block, K)
+        block()
+        torch.cuda.synchronize()
+        got = y.cpu().numpy()
+        single_us, err = None, None
+        if rank == 0:
+            F = {n: ops.repack(dev(w), dev(s)) for n, (w, s) in full.items()}
+            act1, y1 = torch.zeros(12288, device="cuda"), torch.zeros(4096, device="cuda")
+
+            def block1():
+                ops.gemv_fused(hidden, [dict(packed=F["gate"], packed2=F["up"], out=act1, rows=12288, epilogue="swiglu")], prologue="rmsnorm", norm_w=nw)
+                ops.gemv_fused(act1, [dict(packed=F["down"], out=y1, rows=4096, epilogue="store")], cols=12288)
+
+            if world == 1:
+                single_us = tp_us
+            block1()
+            torch.cuda.synchronize()
+            want = y1.cpu().numpy()
+            err = float(np.max(np.abs(got - want)) / np.abs(want).max())
+        if dist:
+            dist.barrier()
+        if rank == 0 and world > 1:  # the same block on one GPU, timed alone (the other ranks idle)
+            side_fn = block1
+            single_us = None
+            s2 = torch.cuda.Stream()
+            with torch.cuda.stream(s2):
+                for _ in range(3):
+                    side_fn()
+                s2.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=s2):
+                    for _ in range(K):
+                        side_fn()
+                g.replay()
+                s2.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(s2)
+                g.replay()
+                b.record(s2)
+                s2.synchronize()
+                single_us = a.elapsed_time(b) * 1e3 / K
+        if dist:
+            dist.barrier()
+    if rank == 0:
+        print(json.dumps({"metric": "tensor-parallel exchange step: all-reduce of fp32[4096], device time", "value": oneshot_us, "unit": "us",
+                          "n_gpus": world, "steps": K, "warmup": 3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+                          "dtype": "f32", "data": "synthetic", "impl": "native", "gpu_launches": K * 4, "clocks": clocks.summary(),
+                          "config": {"workload": "one-shot all-reduce over NVLink peer memory (one kernel per rank) and one MLP block "
+                                                 "(4096 -> 12288 -> 4096, MXFP4) sharded over the ranks", "parallelism": f"tp{world}"},
+                          "allreduce_us": {"oneshot": oneshot_us, "nccl": nccl_us},
+                          "mlp_block_us": {"sharded": tp_us, "one_gpu": single_us, "max_rel_difference": err}}), flush=True)
+    comm.close()
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_config4(args, rank, world, local_rank, dist, st, idx):
     """configs[4]: ``--batch`` sequences per GPU in lock step on one weight copy (the prompt goes through the same batch
     steps), or the batch-1 draft-1 / verify loop with ``--speculative``."""
@@ -668,6 +828,8 @@ def main():
     if args.config in (1, 2):
         if rank == 0:
             run_kernel_configs(args)
+    elif args.config == 5:
+        run_tp_blocks(args, rank, world, local_rank)
     elif args.impl == "reference":
         run_reference(args, rank, world, local_rank)
     else:

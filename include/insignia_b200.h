@@ -376,8 +376,9 @@ INSG_API int insg_attention_chunk(const insg_attn_op *op /* host */, int tokens,
  * One process per GPU: every rank calls insg_comm_create (allocates its exchange buffer on the current device),
  * insg_comm_handle (64 bytes to all-gather among the ranks by any host channel), insg_comm_connect (maps the peers'
  * buffers).  insg_allreduce_oneshot then is ONE kernel per rank: peer stores of the rank's vector into every rank's
- * buffer, a release flag, a bounded wait for the other ranks' flags, the sum in rank order (bit-identical on every rank),
- * in place.  count: a multiple of 4, <= max_floats; data 16-byte aligned; every rank must call with the same count, in
+ * buffer as 8-byte {value, call number} words (the call number is the arrival flag of the value it travels with: no
+ * fence, no separate flag), a bounded wait for the other ranks' words, the sum in rank order (bit-identical on every
+ * rank), in place.  count: a multiple of 4, <= max_floats; data 16-byte aligned; every rank must call with the same count, in
  * the same order.  If a wait runs out (default 1 s, insg_comm_set_timeout) the rank's error flag is set
  * (insg_comm_error reads it, synchronising the stream) and the result is undefined; insg_comm_reset on every rank,
  * with no call in flight anywhere, makes the communicator usable again.  Capturable in a CUDA graph. */

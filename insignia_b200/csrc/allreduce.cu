@@ -3,13 +3,14 @@
 // protocol latency, not bandwidth, is the cost.
 //
 // The reference has no collective call site (it is single-GPU); this is the building block its roadmap names for a
-// tensor-parallel run.  Protocol, per rank, ONE kernel:
-//   1. every CTA stores its chunk of the rank's vector into slot [rank] of EVERY rank's exchange buffer (plain peer
-//      stores: each GPU's own memory is only ever read by its own SMs), fences at system scope and raises the flag
-//      (source rank, CTA) on every rank to the call's epoch with a release store;
-//   2. it polls its own flags until all sources have reached the epoch -- bounded by the clock; on expiry the error
-//      flag is set and the kernel goes on with whatever arrived, so the context stays usable;
-//   3. it adds the slots IN RANK ORDER (every rank gets bit-identical sums) and writes the result in place.
+// tensor-parallel run.  Protocol, per rank, ONE kernel, no fence and no separate flag:
+//   1. every thread stores its elements of the rank's vector into slot [rank] of EVERY rank's exchange buffer as
+//      8-byte words {value, epoch of this call} (plain peer stores, each one atomic: the epoch is the arrival flag
+//      of exactly the value it travels with; each GPU's own memory is only ever read by its own SMs);
+//   2. it then polls the same elements of every source slot in its own buffer until their epoch is this call's --
+//      bounded by the clock; on expiry the error flag is set and the kernel goes on with whatever is there, so the
+//      context stays usable;
+//   3. it adds the values IN RANK ORDER (every rank gets bit-identical sums) and writes the result in place.
 // Two slot sets alternate by epoch parity: a rank can be at most one call ahead of the slowest reader.  The epoch is
 // kept in device memory per CTA, so the launch can be captured in a CUDA graph.  No TMA, no multicast, no library
 // kernel touches peer memory.
@@ -31,8 +32,7 @@ constexpr int kArThreads = 256;
 
 struct ArRank {
     float *data;                    // this rank's vector, reduced in place
-    float *slots[kArMaxWorld];      // slots[p]: base of rank p's slot area ([2 sets][world][max_floats]), as seen from this rank
-    uint32_t *flags[kArMaxWorld];   // flags[p]: rank p's flag area ([world][kArMaxBlocks])
+    uint2 *slots[kArMaxWorld];      // slots[p]: base of rank p's slot area ([2 sets][world][max_floats] of {value, epoch}), as seen from this rank
     uint32_t *epoch;                // this rank's per-CTA call counters [kArMaxBlocks]
     int *error_flag;                // this rank's; set to 1 when a wait ran out
     int rank;
@@ -50,6 +50,16 @@ __device__ __forceinline__ unsigned long long ar_now()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+__device__ __forceinline__ void ar_store(uint2 *p, float v, uint32_t e)
+{
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(e) : "memory");
+}
+__device__ __forceinline__ uint2 ar_load(const uint2 *p)
+{
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
 
 __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const __grid_constant__ ArParams p)
 {
@@ -59,49 +69,42 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const __g
     const uint32_t e = __ldcg(me.epoch + b) + 1u; // this call's epoch (per CTA: no coordination between the CTAs)
     const size_t set_off = size_t(e & 1u) * W * p.max_floats;
     // the vector is cut by position, the same way for every call of a communicator (a CTA's range may be empty for a short
-    // vector; it still takes part in the handshake, so the per-CTA epochs of all ranks move in lock step)
+    // vector; its epoch still advances, so the per-CTA epochs of all ranks move in lock step)
     const int nvec = p.count >> 2, per = ((p.max_floats >> 2) + nb - 1) / nb, v0 = min(nvec, b * per), v1 = min(nvec, v0 + per);
-    __shared__ int s_expired;
-    if (tid == 0) s_expired = 0;
+    bool expired = false;
 
-    // 1. my chunk into my slot on every rank
+    // 1. my elements, each with the epoch, into my slot on every rank
     for (int i = v0 + tid; i < v1; i += kArThreads) {
         const float4 v = __ldcg(reinterpret_cast<const float4 *>(me.data) + i);
-        for (int q = 0; q < W; q++)
-            reinterpret_cast<float4 *>(me.slots[q] + set_off + size_t(me.rank) * p.max_floats)[i] = v;
+        for (int q = 0; q < W; q++) {
+            uint2 *dst = me.slots[q] + set_off + size_t(me.rank) * p.max_floats + size_t(i) * 4;
+            ar_store(dst, v.x, e);
+            ar_store(dst + 1, v.y, e);
+            ar_store(dst + 2, v.z, e);
+            ar_store(dst + 3, v.w, e);
+        }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < W) {
-        uint32_t *f = me.flags[tid] + me.rank * kArMaxBlocks + b;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(e) : "memory");
-    }
-    // 2. wait for every source's chunk (bounded)
-    if (tid < W) {
-        const uint32_t *f = me.flags[me.rank] + tid * kArMaxBlocks + b;
-        const unsigned long long t0 = ar_now();
-        for (;;) {
-            uint32_t v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-            if (int(v - e) >= 0) break;
-            if (ar_now() - t0 > p.timeout_ns) {
-                s_expired = 1;
-                break;
+    // 2 + 3. every source's elements as they arrive (bounded), summed in rank order
+    const uint2 *mine = me.slots[me.rank] + set_off;
+    const unsigned long long t0 = ar_now();
+    for (int i = v0 + tid; i < v1; i += kArThreads) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int q = 0; q < W; q++) {
+            const uint2 *src = mine + size_t(q) * p.max_floats + size_t(i) * 4;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint2 v = ar_load(src + j);
+                while (v.y != e && !expired) {
+                    if (ar_now() - t0 > p.timeout_ns) expired = true;
+                    else v = ar_load(src + j);
+                }
+                a[j] += __uint_as_float(v.x);
             }
         }
+        reinterpret_cast<float4 *>(me.data)[i] = make_float4(a[0], a[1], a[2], a[3]);
     }
+    if (expired && me.error_flag) *me.error_flag = 1;
     __syncthreads();
-    if (s_expired && tid == 0 && me.error_flag) *me.error_flag = 1;
-    // 3. the sum, in rank order
-    const float *mine = me.slots[me.rank] + set_off;
-    for (int i = v0 + tid; i < v1; i += kArThreads) {
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int q = 0; q < W; q++) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(mine + size_t(q) * p.max_floats) + i);
-            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
-        }
-        reinterpret_cast<float4 *>(me.data)[i] = a;
-    }
     if (tid == 0) me.epoch[b] = e;
 }
 
@@ -116,16 +119,15 @@ struct insg_comm {
     bool opened[kArMaxWorld] = {};
     int *error_flag = nullptr;
     unsigned long long timeout_ns = 1000000000ull;
-    size_t slot_bytes() const { return size_t(2) * world * max_floats * sizeof(float); }
-    size_t flag_bytes() const { return size_t(world) * kArMaxBlocks * sizeof(uint32_t); }
+    size_t slot_bytes() const { return size_t(2) * world * max_floats * sizeof(uint2); }
+    size_t flag_bytes() const { return 0; }
     size_t total_bytes() const { return slot_bytes() + flag_bytes() + kArMaxBlocks * sizeof(uint32_t) + 64; }
     ArRank view(float *data) const
     {
         ArRank r = {};
         r.data = data;
         for (int q = 0; q < world; q++) {
-            r.slots[q] = reinterpret_cast<float *>(peer[q]);
-            r.flags[q] = reinterpret_cast<uint32_t *>(peer[q] + slot_bytes());
+            r.slots[q] = reinterpret_cast<uint2 *>(peer[q]);
         }
         r.epoch = reinterpret_cast<uint32_t *>(base + slot_bytes() + flag_bytes());
         r.error_flag = error_flag;
