@@ -554,6 +554,7 @@ def run_tp_blocks(args, rank, world, local_rank):
     dev = lambda a: torch.from_numpy(a.view(np.int32) if a.dtype == np.uint32 else a).cuda()  # noqa: E731
 
     comm = ops.Comm(rank, world, 4096)
+    comm.set_timeout(20_000_000)  # 20 ms: a rank out of step ends its waits quickly instead of stretching the run
     if dist:
         mine = torch.frombuffer(bytearray(comm.handle()), dtype=torch.uint8).cuda()
         every = [torch.empty_like(mine) for _ in range(world)]
@@ -568,6 +569,8 @@ def run_tp_blocks(args, rank, world, local_rank):
             for _ in range(3):
                 fn()
             side.synchronize()
+            if comm.error():
+                raise RuntimeError("a wait of the one-shot all-reduce ran out during warm-up (ranks out of step)")
             if dist:
                 dist.barrier()
             g = torch.cuda.CUDAGraph()
