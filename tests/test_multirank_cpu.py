@@ -48,3 +48,30 @@ def test_reference_arm_runs_on_rank0_only():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"], capture_output=True,
                          text=True, env=env, timeout=120)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_tensor_parallel_shards_add_up_to_the_block():
+    """bench.tp_shards: rows of gate|up and the matching columns of down per rank; the ranks' partial outputs, summed in
+    rank order (what the one-shot all-reduce does), are the unsharded MLP block.  CPU oracle arithmetic, two ranks."""
+    import numpy as np
+
+    sys.path.insert(0, ROOT)
+    import bench
+    from oracle import oracle as orc
+
+    x = np.random.default_rng(5).standard_normal(4096).astype(np.float32)
+
+    def mlp(gate, up, down, cols):
+        g, u = orc.gemv_mlx(gate[0], gate[1], x), orc.gemv_mlx(up[0], up[1], x)
+        act = (g / (1 + np.exp(-g)) * u).astype(np.float32)
+        assert act.shape[0] == cols
+        return orc.gemv_mlx(down[0], down[1], act)
+
+    parts, full = [], None
+    for rank in range(2):
+        full, shard, per = bench.tp_shards(rank, 2, seed=3)
+        assert per == 6144 and shard["gate"][0].shape == (6144, 512) and shard["down"][0].shape == (4096, 768) and shard["down"][1].shape == (4096, 192)
+        parts.append(mlp(shard["gate"], shard["up"], shard["down"], per))
+    want = mlp(full["gate"], full["up"], full["down"], 12288)
+    got = (parts[0] + parts[1]).astype(np.float32)
+    assert np.max(np.abs(got - want)) <= 1e-5 * np.abs(want).max()
