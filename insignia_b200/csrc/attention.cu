@@ -40,6 +40,8 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     float *out_base = p.out + size_t(bt) * p.out_stride;
     unsigned *counters = reinterpret_cast<unsigned *>(reinterpret_cast<uint8_t *>(p.counters) + size_t(bt) * p.scratch_stride);
     float *partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(p.partials) + size_t(bt) * p.scratch_stride);
+    void *kc = static_cast<uint8_t *>(p.kc) + size_t(bt) * p.cache_stride, *vc = static_cast<uint8_t *>(p.vc) + size_t(bt) * p.cache_stride;
+    const float *k_raw = p.k_raw + size_t(bt) * p.kvin_stride, *v_new = p.v_new + size_t(bt) * p.kvin_stride;
 
     pdl_launch_dependents();
 
@@ -60,8 +62,8 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     int fresh = tokens - 1; // the row the producer (or this kernel) is still writing
 
     GroupRaw<BF16, kGroup> ga, gb; // this warp's next two token groups, in flight while it works on earlier ones
-    load_group<BF16, kGroup>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
-    load_group<BF16, kGroup>(p.kc, p.vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
+    load_group<BF16, kGroup>(kc, vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
+    load_group<BF16, kGroup>(kc, vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
     uint4 norm_wv = make_uint4(0u, 0u, 0u, 0u);
     float rope_c[8], rope_s[8];
     if constexpr (FUSED) {
@@ -83,8 +85,8 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
             t0 = split * chunk;
             t1 = min(tokens, t0 + chunk);
             fresh = tokens - 1;
-            load_group<BF16, kGroup>(p.kc, p.vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
-            load_group<BF16, kGroup>(p.kc, p.vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
+            load_group<BF16, kGroup>(kc, vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
+            load_group<BF16, kGroup>(kc, vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
             if (warp < 5 && lane < 8) rope_table(pos, lane, p.fast_trig != 0, rope_c, rope_s);
         }
     }
@@ -103,22 +105,22 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
                 for (int j = 0; j < 8; j++) s_q[warp][lane * 8 + j] = v[j];
             } else if (warp == 4 && pos >= t0 && pos < t1) {
                 float v[8];
-                const float4 *src = reinterpret_cast<const float4 *>(p.k_raw + kvh * 256 + lane * 8);
+                const float4 *src = reinterpret_cast<const float4 *>(k_raw + kvh * 256 + lane * 8);
                 const float4 a = __ldcg(src), b = __ldcg(src + 1);
                 v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
                 norm_rope_256(v, norm_wv, lane, pos, rope_c, rope_s);
                 const size_t row = (size_t(pos) * 4 + kvh) * 256 + lane * 8;
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
-                    Row::store(p.kc, row + j, v[j]);
+                    Row::store(kc, row + j, v[j]);
                     s_knew[lane * 8 + j] = Row::round(v[j]);
                 }
             } else if (warp == 5 && pos >= t0 && pos < t1) {
                 const size_t row = (size_t(pos) * 4 + kvh) * 256 + lane * 8;
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
-                    const float v = __ldcg(p.v_new + kvh * 256 + lane * 8 + j);
-                    Row::store(p.vc, row + j, v);
+                    const float v = __ldcg(v_new + kvh * 256 + lane * 8 + j);
+                    Row::store(vc, row + j, v);
                     s_vnew[lane * 8 + j] = Row::round(v);
                 }
             }
@@ -159,8 +161,8 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
                         for (int j = 0; j < 8; j++) kk[g][j] = s_knew[lane * 8 + j];
                     } else {
                         const size_t row = (size_t(fresh) * 4 + kvh) * 256;
-                        Row::unpack(Row::load_raw(p.kc, row, lane), kk[g]);
-                        vfresh = Row::load_raw(p.vc, row, lane);
+                        Row::unpack(Row::load_raw(kc, row, lane), kk[g]);
+                        vfresh = Row::load_raw(vc, row, lane);
                     }
                 }
             }
@@ -220,11 +222,11 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         const int tend = min(t1, fresh);
         for (int tb = t0 + warp * kGroup; tb < t1; tb += 2 * kAtWarps * kGroup) {
             process(ga, tb);
-            load_group<BF16, kGroup>(p.kc, p.vc, kvh, tb + 2 * kAtWarps * kGroup, tend, lane, ga);
+            load_group<BF16, kGroup>(kc, vc, kvh, tb + 2 * kAtWarps * kGroup, tend, lane, ga);
             const int tb2 = tb + kAtWarps * kGroup;
             if (tb2 < t1) {
                 process(gb, tb2);
-                load_group<BF16, kGroup>(p.kc, p.vc, kvh, tb2 + 2 * kAtWarps * kGroup, tend, lane, gb);
+                load_group<BF16, kGroup>(kc, vc, kvh, tb2 + 2 * kAtWarps * kGroup, tend, lane, gb);
             }
         }
         // ---- fold the 8 warps --------------------------------------------------------
@@ -435,6 +437,27 @@ int insg_attention_chunk(const insg_attn_op *op, int tokens, float *q_scratch, i
     p.counters = static_cast<unsigned *>(op->scratch);
     p.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(op->scratch) + 64);
     return bf16 ? launch_attn<true, false>(p, stream, false, tokens) : launch_attn<false, false>(p, stream, false, tokens);
+}
+
+int insg_attention_batch(const insg_attn_op *op, int sequences, size_t cache_stride_bytes, insg_stream_t stream)
+{
+    if (!op || !op->qraw || !op->k_raw || !op->v || !op->q_norm_w || !op->k_norm_w || !op->k_cache || !op->v_cache ||
+        !op->out || !op->position || !op->scratch)
+        return fail(INSG_E_ARG, "attention_batch: null pointer");
+    if (sequences < 1 || sequences > 65535) return fail(INSG_E_SHAPE, "attention_batch: 1 <= sequences <= 65535");
+    if (op->scratch_bytes < size_t(sequences) * attn_scratch_bytes()) return fail(INSG_E_SHAPE, "attention_batch: scratch too small");
+    if (op->max_context <= 0) return fail(INSG_E_SHAPE, "attention_batch: max_context");
+    if (sequences > 1 && (cache_stride_bytes == 0 || (cache_stride_bytes & 15))) return fail(INSG_E_ARG, "attention_batch: cache stride must be a positive multiple of 16 bytes");
+    AttnParams p = {};
+    p.q = op->qraw; p.k_raw = op->k_raw; p.v_new = op->v; p.q_w = op->q_norm_w; p.k_w = op->k_norm_w;
+    p.kc = op->k_cache; p.vc = op->v_cache; p.out = op->out;
+    p.position = op->position; p.position_offset = op->position_offset;
+    p.max_context = op->max_context; p.fast_trig = op->fast_trig;
+    p.counters = static_cast<unsigned *>(op->scratch);
+    p.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(op->scratch) + 64);
+    p.q_stride = 8192; p.out_stride = 4096; p.kvin_stride = 1024; p.scratch_stride = attn_scratch_bytes(); p.cache_stride = cache_stride_bytes;
+    const bool pdl = op->pdl != 0;
+    return op->kv_dtype == INSG_KV_BF16 ? launch_attn<true, true>(p, stream, pdl, sequences) : launch_attn<false, true>(p, stream, pdl, sequences);
 }
 
 int insg_attention_step(const insg_attn_op *op, insg_stream_t stream)

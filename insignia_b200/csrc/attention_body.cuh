@@ -29,6 +29,10 @@ struct AttnParams {
     // q + m * q_stride, out + m * out_stride, scratch + m * scratch_stride bytes, and sees position + offset + m + 1 rows
     int q_stride, out_stride;
     size_t scratch_stride;
+    // independent sequences in one launch of the fused form (blockIdx.y = sequence, all at the same position): sequence s
+    // also takes k_raw + s * kvin_stride, v_new + s * kvin_stride and the caches at + s * cache_stride bytes
+    int kvin_stride;
+    size_t cache_stride;
 };
 
 // A lane's 8 dims of one cache row, as loaded (converted only when used, so that two token groups can be in flight).

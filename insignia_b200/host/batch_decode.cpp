@@ -237,26 +237,26 @@ void Qwen35BatchDecode::enqueue_step()
             in.seg[2] = seg(blk.v, m.value, INSG_EPI_STORE);
             gemv(in);
             const size_t layer_off = size_t(l / 4) * max_context_ * 1024 * (options_.kv_bf16 ? 2 : 4);
-            for (int s = 0; s < B; s++) { // every sequence attends over its own cache
+            {   // every sequence attends over its own cache, all of them in one launch
                 insg_attn_op at = {};
-                at.qraw = m.qg + size_t(s) * 8192;
-                at.k_raw = m.key + size_t(s) * 1024;
-                at.v = m.value + size_t(s) * 1024;
+                at.qraw = m.qg;
+                at.k_raw = m.key;
+                at.v = m.value;
                 at.q_norm_w = blk.q_norm;
                 at.k_norm_w = blk.k_norm;
-                at.k_cache = static_cast<uint8_t *>(m.kv_keys) + size_t(s) * m.kv_seq_bytes + layer_off;
-                at.v_cache = static_cast<uint8_t *>(m.kv_values) + size_t(s) * m.kv_seq_bytes + layer_off;
-                at.out = m.core + size_t(s) * 4096;
+                at.k_cache = static_cast<uint8_t *>(m.kv_keys) + layer_off;
+                at.v_cache = static_cast<uint8_t *>(m.kv_values) + layer_off;
+                at.out = m.core;
                 at.position = m.d_position;
                 at.max_context = max_context_;
                 at.kv_dtype = options_.kv_bf16 ? INSG_KV_BF16 : INSG_KV_F32;
                 at.fast_trig = options_.accurate_trig ? 0 : 1;
-                at.scratch = static_cast<uint8_t *>(m.attn_scratch) + size_t(s) * m.attn_scratch_each;
-                at.scratch_bytes = m.attn_scratch_each;
-                // safe with dependent-launch overlap: the cache rows a launch fetches before its dependency wait were written
-                // a whole step ago (the launches right before it belong to other sequences, with caches of their own)
+                at.scratch = m.attn_scratch;
+                at.scratch_bytes = size_t(B) * m.attn_scratch_each;
+                // safe with dependent-launch overlap: the cache rows the launch fetches before its dependency wait were
+                // written a whole step ago
                 at.pdl = 1;
-                insg_check(insg_attention_step(&at, st));
+                insg_check(insg_attention_batch(&at, B, m.kv_seq_bytes, st));
                 launches_++;
             }
             insg_gemv_op o = {};

@@ -330,6 +330,21 @@ def attention_step(qraw, k_raw, v, q_w, k_w, k_cache, v_cache, position, max_con
     return out
 
 
+def attention_batch(qraw, k_raw, v, q_w, k_w, k_cache, v_cache, position, max_context, scratch, sequences, fast_trig=True, pdl=False):
+    """One step for ``sequences`` independent sequences at the same position in one launch; qraw [sequences][8192], k_raw
+    and v [sequences][1024], k_cache / v_cache [sequences][max_context * 1024]; scratch: ``sequences`` zero-headed regions."""
+    op = AttnOp()
+    op.qraw, op.k_raw, op.v, op.q_norm_w, op.k_norm_w = _p(qraw), _p(k_raw), _p(v), _p(q_w), _p(k_w)
+    op.k_cache, op.v_cache = _p(k_cache), _p(v_cache)
+    out = torch.empty(sequences * 16 * 256, dtype=torch.float32, device=qraw.device)
+    op.out, op.position, op.position_offset, op.max_context = _p(out), _p(position), 0, max_context
+    op.kv_dtype = KV_BF16 if k_cache.dtype == torch.bfloat16 else KV_F32
+    op.fast_trig, op.scratch, op.scratch_bytes, op.pdl = int(fast_trig), _p(scratch), scratch.numel(), int(pdl)
+    stride = k_cache.numel() // sequences * k_cache.element_size()
+    check(_lib.lib().insg_attention_batch(C.byref(op), sequences, stride, _stream()))
+    return out.reshape(sequences, 4096)
+
+
 def attention_chunk(qraw, k_raw, v, q_w, k_w, k_cache, v_cache, position, max_context, scratch, tokens, fast_trig=True):
     """``tokens`` consecutive tokens of one sequence (rows position .. position + tokens - 1) in two launches; qraw
     [tokens][8192], k_raw and v [tokens][1024]; scratch holds ``tokens`` zero-headed regions of :func:`gqa_scratch` size."""

@@ -422,6 +422,30 @@ def test_attention_chunk_equals_token_steps_bitwise(cuda, kv_bf16):
         ops.attention_chunk(qraw, kraw, v, dev(qw), dev(kw), kc3, vc3, pos_dev, ctx, scratch, T)
 
 
+@pytest.mark.parametrize("kv_bf16", [False, True])
+def test_attention_batch_equals_sequence_steps_bitwise(cuda, kv_bf16):
+    """Five independent sequences at the same position in one launch against one insg_attention_step per sequence."""
+    from insignia_b200 import ops
+
+    rng = np.random.default_rng(43)
+    ctx, pos, B = 300, 211, 5
+    qw, kw = bf16(rng, 256), bf16(rng, 256)
+    dt = torch.bfloat16 if kv_bf16 else torch.float32
+    kc, vc = torch.randn(B, ctx * 1024, device="cuda").to(dt), torch.randn(B, ctx * 1024, device="cuda").to(dt)
+    qraw = dev(rng.standard_normal((B, 8192)).astype(np.float32))
+    kraw = dev(rng.standard_normal((B, 1024)).astype(np.float32))
+    v = dev(rng.standard_normal((B, 1024)).astype(np.float32))
+    pos_dev = torch.full((1,), pos, dtype=torch.int32, device="cuda")
+    kc1, vc1 = kc.clone(), vc.clone()
+    scratch = ops.gqa_scratch("cuda")
+    want = [host(ops.attention_step(qraw[s], kraw[s], v[s], dev(qw), dev(kw), kc1[s], vc1[s], pos_dev, ctx, scratch)) for s in range(B)]
+    kc2, vc2 = kc.clone(), vc.clone()
+    big = torch.zeros(B * scratch.numel(), dtype=torch.uint8, device="cuda")
+    got = host(ops.attention_batch(qraw, kraw, v, dev(qw), dev(kw), kc2, vc2, pos_dev, ctx, big, B))
+    assert np.array_equal(got, np.stack(want))
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+
+
 # -------------------------------------------------------------------- small ops
 def test_small_ops_vs_oracle(cuda):
     from insignia_b200 import mxfp4, ops
