@@ -114,7 +114,8 @@ INSG_API int insg_mxfp4_gemv_packed(const void *packed, const float *x, float *y
                                     insg_stream_t stream);
 
 /* Y[m][rows] = W x[m] for M tokens on the tcgen05 tensor cores (kind::mxf4, weights in the insg_mxfp4_repack_umma
- * layout, eight tokens per instruction, fp32-exact activations as base-4 digit columns); x fp32 [M][cols], y fp32
+ * layout, sixteen tokens per instruction, fp32-exact activations as eight balanced base-9 digit columns each); x fp32
+ * [M][cols], y fp32
  * [M][rows].  The M >= 8 counterpart of insg_mxfp4_gemv_packed (src/decode.cu:13 applied to M tokens; the reference
  * has no batched form).  scratch: insg_umma_gemm_scratch_bytes(cols, M) of device memory. */
 INSG_API size_t insg_umma_gemm_scratch_bytes(int cols, int tokens);
@@ -210,7 +211,7 @@ typedef struct insg_gemv_op {
     int tokens;                 /* 0 or 1: one token.  More: consecutive tokens of one sequence in one call (the weights are
                                    streamed once per pass): in, aux and x_out are [tokens][cols], every out is
                                    [tokens][rows]; the convolution history is advanced token by token.  layout 0: 2 or 4
-                                   tokens (one launch of the mma.sync kernel); layout 1: any count up to 4096, eight tokens
+                                   tokens (one launch of the mma.sync kernel); layout 1: any count up to 4096, sixteen tokens
                                    per tcgen05 instruction (needs umma_scratch).  Not with INSG_PRO_PREPARED, prepared
                                    outputs or INSG_EPI_LOGITS. */
     void *umma_scratch;         /* layout 1 with tokens > 1: device scratch of insg_umma_gemm_scratch_bytes(cols, tokens) for

@@ -38,7 +38,7 @@ struct DecodeOptions {
                                    // input ready as fp16 pieces (and its sum of squares), so that one starts streaming
                                    // without normalising or converting anything; false: every GEMV prepares its own input
     bool prefill_tcgen05 = true;   // forward_tokens with 16 or more tokens: passes of up to 32 tokens through the tcgen05
-                                   // kernel (kind::mxf4, eight tokens per instruction; needs a second, tile-layout copy of
+                                   // kernel (kind::mxf4, sixteen tokens per instruction; needs a second, tile-layout copy of
                                    // the weights); false: always passes of four tokens through the mma.sync kernel
     int n_layers = Qwen35Shape::layers;
     int vocab = Qwen35Shape::vocab;
