@@ -361,6 +361,8 @@ typedef struct insg_attn_op {
     void *scratch;
     size_t scratch_bytes;
     int pdl;
+    int *error_flag;          /* device int set to 1 if a bounded wait inside the kernel ran out (bf16 cache, long contexts:
+                                 rows are staged by bulk copies with mbarrier completion), or NULL */
 } insg_attn_op;
 INSG_API int insg_attention_step(const insg_attn_op *op /* host */, insg_stream_t stream);
 /* `tokens` consecutive tokens of one sequence in two launches (prompt processing): op describes token 0 (rotary position

@@ -31,7 +31,7 @@ class GemvOp(C.Structure):
 class AttnOp(C.Structure):
     _fields_ = [("qraw", vp), ("k_raw", vp), ("v", vp), ("q_norm_w", vp), ("k_norm_w", vp), ("k_cache", vp),
                 ("v_cache", vp), ("out", vp), ("position", vp), ("position_offset", i32), ("max_context", i32),
-                ("kv_dtype", i32), ("fast_trig", i32), ("scratch", vp), ("scratch_bytes", sz), ("pdl", i32)]
+                ("kv_dtype", i32), ("fast_trig", i32), ("scratch", vp), ("scratch_bytes", sz), ("pdl", i32), ("error_flag", vp)]
 
 
 class EngineOptions(C.Structure):

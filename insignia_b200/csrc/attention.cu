@@ -12,8 +12,18 @@
 // do not depend on scheduling.  The fused entry also does the per-head RMSNorm,
 // partial RoPE and the cache write of the current token (src/ops.cu:9,
 // src/qwen_kernels.cu:15,31) so one launch replaces five.
+//
+// bf16 cache, long contexts: the scalar loop is bound by instruction issue (half the bytes, the same instructions),
+// so from kMmaMinTokens cached rows on the warps score and accumulate on the tensor cores instead (mma.sync
+// m16n8k16 bf16, fp32 accumulation): 16 cached rows per step per warp, fetched into the warp's own shared-memory tile
+// by one cp.async.bulk per lane (16 key rows + 16 value rows, mbarrier completion, bounded wait); the fp32 query goes in
+// as two bf16 pieces (hi + lo) in the eight N columns (4 heads x 2 pieces), the softmax weights likewise for P.V, so
+// products keep ~16 bits of the fp32 operands and the cache values are exact.
 #include "attention_body.cuh"
 #include "host_util.h"
+#include "umma_common.cuh"
+
+#include <mutex>
 
 namespace insg {
 
@@ -21,6 +31,114 @@ constexpr int kAtThreads = 256;
 constexpr int kAtWarps = 8;
 constexpr int kGroup = 4;                    // tokens a warp scores at once
 constexpr int kMinChunk = kAtWarps * kGroup; // tokens per split at least: one group per warp
+constexpr int kMmaMinTokens = 2048;          // bf16 cache: cached rows from which the tensor-core loop is used
+constexpr int kTileRow = 528;                // a staged row: 512 bytes of bf16 + 16 of padding (conflict-free ldmatrix)
+constexpr int kTileBytes = 16 * kTileRow;    // 16 rows
+constexpr size_t kMmaSmem = size_t(kAtWarps) * 2 * kTileBytes; // per warp: a key tile and a value tile
+
+__device__ __forceinline__ uint32_t bf16_piece_pair(float a, float b, int piece)
+{
+    // piece 0: the bf16 roundings of a and b; piece 1: the bf16 roundings of what those left over
+    __nv_bfloat16 ha = __float2bfloat16_rn(a), hb = __float2bfloat16_rn(b);
+    if (piece) {
+        ha = __float2bfloat16_rn(a - __bfloat162float(ha));
+        hb = __float2bfloat16_rn(b - __bfloat162float(hb));
+    }
+    return uint32_t(__bfloat16_as_ushort(ha)) | (uint32_t(__bfloat16_as_ushort(hb)) << 16);
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One warp's share of a split on the tensor cores: rows t0 + 16 (warp + 8 n) .. of [t0, t1), bf16 cache.  Leaves the
+// warp's (max, denominator, weighted values) in s_m_w / s_l_w / s_acc_w like the scalar loop does.
+__device__ __forceinline__ void attn_mma_warp(const void *kc, const void *vc, int kvh, int t0, int t1, int warp, int lane,
+                                              const float (*s_q)[256], uint8_t *tiles, uint64_t *bar, volatile int *abort_flag,
+                                              float *s_m_w, float *s_l_w, float (*s_acc_w)[256])
+{
+    const int g = lane >> 2, t = lane & 3;
+    uint8_t *tile_k = tiles + size_t(warp) * 2 * kTileBytes, *tile_v = tile_k + kTileBytes;
+    if (lane == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    // the query as the B operand: column g = (head g >> 1, piece g & 1), k rows 2t, 2t+1 and 2t+8, 2t+9 of every 16 dims
+    uint32_t qb[16][2];
+    {
+        const float *qh = s_q[g >> 1];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int d = 16 * i + 2 * t;
+            qb[i][0] = bf16_piece_pair(qh[d] * 0.0625f, qh[d + 1] * 0.0625f, g & 1);
+            qb[i][1] = bf16_piece_pair(qh[d + 8] * 0.0625f, qh[d + 9] * 0.0625f, g & 1);
+        }
+    }
+    float m_run = -3.0e38f, l_run = 0.f; // of head t (the same in the eight lanes that share t, l_run as a partial sum)
+    float acc[16][4];                    // [16 dims each][dim g: (hi, lo) of head t | dim g + 8: (hi, lo)]
+#pragma unroll
+    for (int j = 0; j < 16; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    uint32_t phase = 0;
+    const uint32_t lm_row = uint32_t(lane & 7), lm_id = uint32_t(lane >> 3);
+    const uint32_t k_addr = smem_u32(tile_k) + ((lm_id & 1) * 8 + lm_row) * kTileRow + (lm_id >> 1) * 16; // + 32 i: rows of K as m, dims as k
+    const uint32_t v_addr = smem_u32(tile_v) + ((lm_id >> 1) * 8 + lm_row) * kTileRow + (lm_id & 1) * 16; // + 32 j: transposed: dims as m, rows as k
+    for (int tb = t0 + 16 * warp; tb < t1; tb += 16 * kAtWarps) {
+        __syncwarp();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the tile was read by ordinary loads; the copies below overwrite it
+        if (lane == 0) mbar_expect_tx(bar, 32 * 512);
+        __syncwarp();
+        {
+            const int r = lane & 15, tok = min(tb + r, t1 - 1); // rows past the split repeat its last row: masked below
+            const uint8_t *src = static_cast<const uint8_t *>(lane < 16 ? kc : vc) + (size_t(tok) * 4 + kvh) * 512;
+            bulk_load((lane < 16 ? tile_k : tile_v) + r * kTileRow, src, 512, bar);
+        }
+        if (!mbar_wait(bar, phase, abort_flag)) break;
+        phase ^= 1u;
+        // ---- scores: S[16 rows][8 columns] = K tile . q pieces ----
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            uint32_t a0, a1, a2, a3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(k_addr + 32 * i));
+            mma_bf16(c, a0, a1, a2, a3, qb[i][0], qb[i][1]);
+        }
+        const bool v0 = tb + g < t1, v1 = tb + g + 8 < t1;
+        const float s0 = v0 ? c[0] + c[1] : -3.0e38f, s1 = v1 ? c[2] + c[3] : -3.0e38f; // rows tb + g and tb + g + 8, head t
+        float mx = fmaxf(s0, s1);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m_run, mx), corr = __expf(m_run - m_new);
+        const float p0 = v0 ? __expf(s0 - m_new) : 0.f, p1 = v1 ? __expf(s1 - m_new) : 0.f;
+        l_run = fmaf(l_run, corr, p0 + p1);
+        m_run = m_new;
+#pragma unroll
+        for (int j = 0; j < 16; j++) { acc[j][0] *= corr; acc[j][1] *= corr; acc[j][2] *= corr; acc[j][3] *= corr; }
+        // ---- the weights as the B operand of P.V: column g = (head g >> 1, piece g & 1), k rows = cached rows ----
+        const int src_a = 8 * t + (g >> 1), src_b = src_a + 4; // lanes that hold rows 2t and 2t + 1 (and + 8) of that head
+        const float x0 = __shfl_sync(0xffffffffu, p0, src_a), x1 = __shfl_sync(0xffffffffu, p0, src_b);
+        const float y0 = __shfl_sync(0xffffffffu, p1, src_a), y1 = __shfl_sync(0xffffffffu, p1, src_b);
+        const uint32_t pb0 = bf16_piece_pair(x0, x1, g & 1), pb1 = bf16_piece_pair(y0, y1, g & 1);
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            uint32_t a0, a1, a2, a3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(v_addr + 32 * j));
+            mma_bf16(acc[j], a0, a1, a2, a3, pb0, pb1);
+        }
+    }
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 4);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 8);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
+    if (g == 0) { s_m_w[t] = m_run; s_l_w[t] = l_run; }
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        s_acc_w[t][16 * j + g] = acc[j][0] + acc[j][1];
+        s_acc_w[t][16 * j + g + 8] = acc[j][2] + acc[j][3];
+    }
+}
 
 template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) attn_splitk_kernel(const __grid_constant__ AttnParams p)
 {
@@ -31,6 +149,9 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     __shared__ __align__(16) float s_acc[kAtWarps][4][256];
     __shared__ int s_last;
     __shared__ float s_e[64][4], s_lg[4];
+    __shared__ __align__(8) uint64_t s_bar[kAtWarps];
+    __shared__ int s_abort;
+    extern __shared__ __align__(128) uint8_t s_tiles[]; // bf16 cache only: per warp a key tile and a value tile
 
     const int kvh = blockIdx.x / kSplits, split = blockIdx.x % kSplits;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -61,9 +182,13 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     int t0 = split * chunk, t1 = min(tokens, t0 + chunk);
     int fresh = tokens - 1; // the row the producer (or this kernel) is still writing
 
+    bool use_mma = BF16 && tokens >= kMmaMinTokens; // long bf16 contexts: the tensor-core loop (reads every row from the cache)
+    if (tid == 0) s_abort = 0;
     GroupRaw<BF16, kGroup> ga, gb; // this warp's next two token groups, in flight while it works on earlier ones
-    load_group<BF16, kGroup>(kc, vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
-    load_group<BF16, kGroup>(kc, vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
+    if (!use_mma) {
+        load_group<BF16, kGroup>(kc, vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
+        load_group<BF16, kGroup>(kc, vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
+    }
     uint4 norm_wv = make_uint4(0u, 0u, 0u, 0u);
     float rope_c[8], rope_s[8];
     if constexpr (FUSED) {
@@ -85,8 +210,11 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
             t0 = split * chunk;
             t1 = min(tokens, t0 + chunk);
             fresh = tokens - 1;
-            load_group<BF16, kGroup>(kc, vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
-            load_group<BF16, kGroup>(kc, vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
+            use_mma = BF16 && tokens >= kMmaMinTokens;
+            if (!use_mma) {
+                load_group<BF16, kGroup>(kc, vc, kvh, t0 + warp * kGroup, min(t1, fresh), lane, ga);
+                load_group<BF16, kGroup>(kc, vc, kvh, t0 + (warp + kAtWarps) * kGroup, min(t1, fresh), lane, gb);
+            }
             if (warp < 5 && lane < 8) rope_table(pos, lane, p.fast_trig != 0, rope_c, rope_s);
         }
     }
@@ -115,6 +243,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
                     Row::store(kc, row + j, v[j]);
                     s_knew[lane * 8 + j] = Row::round(v[j]);
                 }
+                if (use_mma) asm volatile("fence.proxy.async;" ::: "memory"); // the tensor-core loop fetches this row by bulk copy
             } else if (warp == 5 && pos >= t0 && pos < t1) {
                 const size_t row = (size_t(pos) * 4 + kvh) * 256 + lane * 8;
 #pragma unroll
@@ -123,6 +252,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
                     Row::store(vc, row + j, v);
                     s_vnew[lane * 8 + j] = Row::round(v);
                 }
+                if (use_mma) asm volatile("fence.proxy.async;" ::: "memory");
             }
         } else {
             for (int i = tid; i < 1024; i += kAtThreads) s_q[i >> 8][i & 255] = __ldcg(q_in + size_t(kvh) * 1024 + i);
@@ -130,7 +260,14 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     }
     __syncthreads();
 
-    if (has_work) {
+    bool mma_done = false;
+    if constexpr (BF16) {
+        if (has_work && use_mma) {
+            attn_mma_warp(kc, vc, kvh, t0, t1, warp, lane, s_q, s_tiles, &s_bar[warp], &s_abort, s_m[warp], s_l[warp], s_acc[warp]);
+            mma_done = true;
+        }
+    }
+    if (has_work && !mma_done) {
         float q[4][8];
 #pragma unroll
         for (int h = 0; h < 4; h++)
@@ -300,11 +437,28 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         reinterpret_cast<float4 *>(out_base + size_t(kvh * 4 + h) * 256)[c4] = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
         if (tid == 0) counters[kvh] = 0u;
     }
+    if (tid == 0 && s_abort && p.error_flag) *p.error_flag = 1;
 }
 
 template <bool BF16, bool FUSED> int launch_attn(const AttnParams &p, cudaStream_t st, bool pdl, int chunk_tokens = 1)
 {
-    return launch(attn_splitk_kernel<BF16, FUSED>, dim3(4 * kSplits, chunk_tokens), dim3(kAtThreads), 0, st, pdl, p);
+    size_t smem = 0;
+    if (BF16) { // the tensor-core loop's tiles: more than 48 KB of dynamic shared memory is a per-device opt-in
+        static std::mutex mu;
+        static bool done[64] = {false};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+        if (dev < 0 || dev >= 64) return fail(INSG_E_LIMIT, "attention: device ordinal beyond 63");
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[dev]) {
+            e = cudaFuncSetAttribute(attn_splitk_kernel<BF16, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kMmaSmem));
+            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attention)");
+            done[dev] = true;
+        }
+        smem = kMmaSmem;
+    }
+    return launch(attn_splitk_kernel<BF16, FUSED>, dim3(4 * kSplits, chunk_tokens), dim3(kAtThreads), smem, st, pdl, p);
 }
 
 // A chunk of consecutive tokens, step one: per token m (one CTA each) the per-head RMSNorm + partial RoPE of the 16 query
@@ -427,7 +581,7 @@ int insg_attention_chunk(const insg_attn_op *op, int tokens, float *q_scratch, i
     p.q = op->qraw; p.k_raw = op->k_raw; p.v_new = op->v; p.q_w = op->q_norm_w; p.k_w = op->k_norm_w;
     p.kc = op->k_cache; p.vc = op->v_cache; p.out = op->out;
     p.position = op->position; p.position_offset = op->position_offset;
-    p.max_context = op->max_context; p.fast_trig = op->fast_trig;
+    p.max_context = op->max_context; p.fast_trig = op->fast_trig; p.error_flag = op->error_flag;
     const bool bf16 = op->kv_dtype == INSG_KV_BF16;
     int rc = bf16 ? launch(attn_chunk_prepare_kernel<true>, dim3(tokens), dim3(kAtThreads), 0, stream, false, p, q_scratch)
                   : launch(attn_chunk_prepare_kernel<false>, dim3(tokens), dim3(kAtThreads), 0, stream, false, p, q_scratch);
@@ -452,7 +606,7 @@ int insg_attention_batch(const insg_attn_op *op, int sequences, size_t cache_str
     p.q = op->qraw; p.k_raw = op->k_raw; p.v_new = op->v; p.q_w = op->q_norm_w; p.k_w = op->k_norm_w;
     p.kc = op->k_cache; p.vc = op->v_cache; p.out = op->out;
     p.position = op->position; p.position_offset = op->position_offset;
-    p.max_context = op->max_context; p.fast_trig = op->fast_trig;
+    p.max_context = op->max_context; p.fast_trig = op->fast_trig; p.error_flag = op->error_flag;
     p.counters = static_cast<unsigned *>(op->scratch);
     p.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(op->scratch) + 64);
     p.q_stride = 8192; p.out_stride = 4096; p.kvin_stride = 1024; p.scratch_stride = attn_scratch_bytes(); p.cache_stride = cache_stride_bytes;
@@ -471,7 +625,7 @@ int insg_attention_step(const insg_attn_op *op, insg_stream_t stream)
     p.q = op->qraw; p.k_raw = op->k_raw; p.v_new = op->v; p.q_w = op->q_norm_w; p.k_w = op->k_norm_w;
     p.kc = op->k_cache; p.vc = op->v_cache; p.out = op->out;
     p.position = op->position; p.position_offset = op->position_offset;
-    p.max_context = op->max_context; p.fast_trig = op->fast_trig;
+    p.max_context = op->max_context; p.fast_trig = op->fast_trig; p.error_flag = op->error_flag;
     p.counters = static_cast<unsigned *>(op->scratch);
     p.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(op->scratch) + 64);
     const bool pdl = op->pdl != 0;

@@ -33,6 +33,7 @@ struct AttnParams {
     // also takes k_raw + s * kvin_stride, v_new + s * kvin_stride and the caches at + s * cache_stride bytes
     int kvin_stride;
     size_t cache_stride;
+    int *error_flag;       // set to 1 when a bounded wait inside the kernel ran out (bf16 tensor-core path), or null
 };
 
 // A lane's 8 dims of one cache row, as loaded (converted only when used, so that two token groups can be in flight).

@@ -251,6 +251,7 @@ void Qwen35BatchDecode::enqueue_step()
                 at.max_context = max_context_;
                 at.kv_dtype = options_.kv_bf16 ? INSG_KV_BF16 : INSG_KV_F32;
                 at.fast_trig = options_.accurate_trig ? 0 : 1;
+                at.error_flag = m.d_error;
                 at.scratch = m.attn_scratch;
                 at.scratch_bytes = size_t(B) * m.attn_scratch_each;
                 // safe with dependent-launch overlap: the cache rows the launch fetches before its dependency wait were

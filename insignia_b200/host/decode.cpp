@@ -368,6 +368,7 @@ static void enqueue_attention_block(Ctx &c, const Qwen35Decode::Plan::Block &b, 
     at.max_context = x.max_context;
     at.kv_dtype = x.options.kv_bf16 ? INSG_KV_BF16 : INSG_KV_F32;
     at.fast_trig = x.options.accurate_trig ? 0 : 1;
+    at.error_flag = x.d_token + 3;
     at.scratch = x.attn_scratch;
     at.scratch_bytes = insg_gqa_scratch_bytes(x.max_context);
     at.pdl = c.pdl ? 1 : 0;
@@ -508,6 +509,7 @@ void attention_block_multi(Ctx &c, const Qwen35Decode::Plan::Block &b, void *kc,
     at.max_context = x.max_context;
     at.kv_dtype = x.options.kv_bf16 ? INSG_KV_BF16 : INSG_KV_F32;
     at.fast_trig = x.options.accurate_trig ? 0 : 1;
+    at.error_flag = x.d_token + 3;
     at.scratch = x.attn_scratch;
     at.scratch_bytes = size_t(kBigChunk) * insg_gqa_scratch_bytes(x.max_context);
     insg_check(insg_attention_chunk(&at, u.T, u.qn, c.st));
