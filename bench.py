@@ -77,6 +77,7 @@ def parse_args():
     ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--shape", default=None, help="config 1: only this matrix, as ROWSxCOLS")
     ap.add_argument("--tokens", type=int, default=None, help="config 1: only this token count; config 2: only this context length")
+    ap.add_argument("--sequences", type=int, default=8, help="config 2: sequences of the batched leg (1 = skip it)")
     ap.add_argument("--eager", action="store_true", help="configs 1 and 2: plain launches instead of one CUDA graph of the steps (for profiler captures)")
     ap.add_argument("--prompt", type=int, default=None, help="prompt tokens (default 512 for config 3, 2048 for config 4)")
     ap.add_argument("--seed", type=int, default=0)
@@ -495,7 +496,7 @@ def run_kernel_configs(args):
             work = "configs[1]: y[m] = W x[m], MXFP4 weights, fp32 activations, M tokens"
         else:
             for ctx in ([args.tokens] if args.tokens else [1024, 8192, 32768]):
-                for dt in (torch.float32, torch.bfloat16):
+                for dt in ((torch.bfloat16,) if args.kv_bf16 else (torch.float32, torch.bfloat16)):
                     n = max(2, -(-(160 << 20) // (2 * ctx * 1024 * (4 if dt == torch.float32 else 2))))
                     n = min(n, 40)
                     caches = [(torch.randn(ctx * 1024, device="cuda").to(dt), torch.randn(ctx * 1024, device="cuda").to(dt)) for _ in range(n)]
@@ -509,8 +510,13 @@ def run_kernel_configs(args):
                         ops.gqa_decode(q, k, v, ctx, scratch=scratch)
                     us = _event_us(fn, K, W, args.eager)
                     nbytes = 2 * ctx * 1024 * (4 if dt == torch.float32 else 2)
-                    # eight sequences, each with its own cache, in one launch of the fused step (norm, RoPE, cache write, attention)
-                    B = 8
+                    if args.sequences <= 1:
+                        legs.append({"context": ctx, "kv_cache": "f32" if dt == torch.float32 else "bf16", "sequences": 1, "us": us,
+                                     "cache_gbs": nbytes / us * 1e-3, "frac_of_peak": nbytes / us * 1e-3 / peak})
+                        del caches
+                        continue
+                    # several sequences, each with its own cache, in one launch of the fused step (norm, RoPE, cache write, attention)
+                    B = args.sequences
                     n8 = max(2, min(6, -(-(160 << 20) // (B * nbytes))))
                     kc8 = [torch.randn(B, ctx * 1024, device="cuda").to(dt) for _ in range(n8)]
                     vc8 = [torch.randn(B, ctx * 1024, device="cuda").to(dt) for _ in range(n8)]
