@@ -369,14 +369,16 @@ INSG_API int insg_attention_step(const insg_attn_op *op /* host */, insg_stream_
  * and cache row *position + position_offset); token m takes qraw + m * 8192, k_raw + m * 1024, v + m * 1024, writes
  * out + m * 4096 and cache row + m, and attends the rows up to its own.  scratch: tokens * insg_gqa_scratch_bytes(.)
  * bytes whose first 64 bytes per token are zero before the first use (the kernel leaves them zero); q_scratch: device,
- * tokens * 4096 floats.  op->pdl is ignored (plain stream order).  Same math per token as insg_attention_step. */
+ * tokens * 4096 floats.  rows_hint: 0, or an upper bound of the rows the LAST token of the chunk attends (*position +
+ * position_offset + tokens) when the host knows it: short contexts then start fewer CTAs; a hint that turns out too
+ * small raises *op->error_flag.  op->pdl is ignored (plain stream order).  Same math per token as insg_attention_step. */
+INSG_API int insg_attention_chunk(const insg_attn_op *op /* host */, int tokens, float *q_scratch, int rows_hint, insg_stream_t stream);
 /* One step for `sequences` independent sequences at the same position in ONE launch (a decode batch): op describes
  * sequence 0; sequence s takes qraw + s * 8192, k_raw + s * 1024, v + s * 1024, writes out + s * 4096, and has its
  * caches at k_cache / v_cache + s * cache_stride_bytes.  scratch: sequences * insg_gqa_scratch_bytes(.) bytes, the first
  * 64 bytes per sequence zero before the first use.  Same math per sequence as insg_attention_step.  No reference
  * counterpart (it is strictly batch 1). */
 INSG_API int insg_attention_batch(const insg_attn_op *op /* host */, int sequences, size_t cache_stride_bytes, insg_stream_t stream);
-INSG_API int insg_attention_chunk(const insg_attn_op *op /* host */, int tokens, float *q_scratch, insg_stream_t stream);
 
 /* ------------------------------------------------ tensor-parallel exchange */
 /* One-shot all-reduce (sum) of a short fp32 vector over NVLink peer memory, for the exchange step of a tensor-parallel

@@ -94,7 +94,7 @@ SIGNATURES = {
     "insg_comm_connect_local": (i32, [vp, i32]),
     "insg_allreduce_oneshot_local": (i32, [vp, vp, i32, i32, i32, vp]),
     "insg_attention_batch": (i32, [vp, i32, sz, vp]),
-    "insg_attention_chunk": (i32, [vp, i32, vp, vp]),
+    "insg_attention_chunk": (i32, [vp, i32, vp, i32, vp]),
     "insg_attention_step": (i32, [C.POINTER(AttnOp), vp]),
     "insg_rmsnorm_bf16": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "insg_rmsnorm_zero_centered": (i32, [vp, vp, vp, i32, i32, C.c_float, vp]),

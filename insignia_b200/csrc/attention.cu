@@ -23,6 +23,7 @@
 #include "host_util.h"
 #include "umma_common.cuh"
 
+#include <algorithm>
 #include <mutex>
 
 namespace insg {
@@ -153,7 +154,8 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     __shared__ int s_abort;
     extern __shared__ __align__(128) uint8_t s_tiles[]; // bf16 cache only: per warp a key tile and a value tile
 
-    const int kvh = blockIdx.x / kSplits, split = blockIdx.x % kSplits;
+    const int ns = int(gridDim.x) >> 2; // splits launched per kv head (37, or fewer when the host knows the context is short)
+    const int kvh = blockIdx.x / ns, split = blockIdx.x % ns;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // token of a chunk (plain form only; a single launch has blockIdx.y == 0 and zero strides)
     const int bt = blockIdx.y;
@@ -219,6 +221,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
         }
     }
     const bool has_work = t0 < tokens;
+    if (nsplit > ns && tid == 0 && p.error_flag) *p.error_flag = 1; // the host's hint was too small: rows would be left out
 
     if (has_work) {
         // ---- query (and current key) preparation --------------------------------
@@ -399,7 +402,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     __syncthreads();
     if (tid == 0) {
         const unsigned ticket = atomicAdd(counters + kvh, 1u);
-        s_last = (ticket == kSplits - 1);
+        s_last = (ticket == unsigned(ns) - 1u);
     }
     __syncthreads();
     if (s_last) {
@@ -440,7 +443,7 @@ template <bool BF16, bool FUSED> __global__ void __launch_bounds__(kAtThreads) a
     if (tid == 0 && s_abort && p.error_flag) *p.error_flag = 1;
 }
 
-template <bool BF16, bool FUSED> int launch_attn(const AttnParams &p, cudaStream_t st, bool pdl, int chunk_tokens = 1)
+template <bool BF16, bool FUSED> int launch_attn(const AttnParams &p, cudaStream_t st, bool pdl, int chunk_tokens = 1, int splits = kSplits)
 {
     size_t smem = 0;
     if (BF16) { // the tensor-core loop's tiles: more than 48 KB of dynamic shared memory is a per-device opt-in
@@ -458,7 +461,7 @@ template <bool BF16, bool FUSED> int launch_attn(const AttnParams &p, cudaStream
         }
         smem = kMmaSmem;
     }
-    return launch(attn_splitk_kernel<BF16, FUSED>, dim3(4 * kSplits, chunk_tokens), dim3(kAtThreads), smem, st, pdl, p);
+    return launch(attn_splitk_kernel<BF16, FUSED>, dim3(4 * splits, chunk_tokens), dim3(kAtThreads), smem, st, pdl, p);
 }
 
 // A chunk of consecutive tokens, step one: per token m (one CTA each) the per-head RMSNorm + partial RoPE of the 16 query
@@ -569,7 +572,7 @@ int insg_gqa_decode(const float *q, const void *k_cache, const void *v_cache, fl
     return attn_plain_launch(q, k_cache, v_cache, out, tokens, kv_dtype, scratch, stream);
 }
 
-int insg_attention_chunk(const insg_attn_op *op, int tokens, float *q_scratch, insg_stream_t stream)
+int insg_attention_chunk(const insg_attn_op *op, int tokens, float *q_scratch, int rows_hint, insg_stream_t stream)
 {
     if (!op || !op->qraw || !op->k_raw || !op->v || !op->q_norm_w || !op->k_norm_w || !op->k_cache || !op->v_cache ||
         !op->out || !op->position || !op->scratch || !q_scratch)
@@ -590,7 +593,13 @@ int insg_attention_chunk(const insg_attn_op *op, int tokens, float *q_scratch, i
     p.q = q_scratch; p.q_stride = 4096; p.out_stride = 4096; p.scratch_stride = attn_scratch_bytes();
     p.counters = static_cast<unsigned *>(op->scratch);
     p.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(op->scratch) + 64);
-    return bf16 ? launch_attn<true, false>(p, stream, false, tokens) : launch_attn<false, false>(p, stream, false, tokens);
+    // the splits a context of rows_hint rows needs (the kernel's own geometry); fewer CTAs to start and to count in
+    int splits = kSplits;
+    if (rows_hint > 0) {
+        const int chunk = std::max(kMinChunk, (rows_hint + kSplits - 1) / kSplits);
+        splits = std::max(1, std::min(kSplits, (rows_hint + chunk - 1) / chunk));
+    }
+    return bf16 ? launch_attn<true, false>(p, stream, false, tokens, splits) : launch_attn<false, false>(p, stream, false, tokens, splits);
 }
 
 int insg_attention_batch(const insg_attn_op *op, int sequences, size_t cache_stride_bytes, insg_stream_t stream)

@@ -181,7 +181,8 @@ __global__ void __launch_bounds__(kGThreads, 2) umma_digitize_kernel(const __gri
 
 // Causal convolution (kernel 4) + SiLU over `tokens` consecutive tokens of one sequence, in place: io[m][c] holds the raw
 // projection on entry and the activation on return; the three-value history per channel is read and left updated.
-// (reference: src/qwen_kernels.cu:31, once per token)
+// The filter is not recursive (out[m] needs raw[m-3..m] only), so a thread takes one channel and up to 32 tokens at a
+// time: all their loads are in flight together, then the outputs are stored.  (reference: src/qwen_kernels.cu:31, once per token)
 __global__ void conv_tokens_kernel(float *io, float *conv_state, const uint16_t *conv_w, int channels, int tokens)
 {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -191,12 +192,18 @@ __global__ void conv_tokens_kernel(float *io, float *conv_state, const uint16_t 
     const uint2 wv = reinterpret_cast<const uint2 *>(conv_w)[c];
     const float w0 = bf16_bits_to_float(wv.x & 0xffff), w1 = bf16_bits_to_float(wv.x >> 16);
     const float w2 = bf16_bits_to_float(wv.y & 0xffff), w3 = bf16_bits_to_float(wv.y >> 16);
-    for (int m = 0; m < tokens; m++) {
-        float *q = io + size_t(m) * channels + c;
-        const float yv = *q;
-        const float z = fmaf(h0, w0, fmaf(h1, w1, fmaf(h2, w2, yv * w3)));
-        h0 = h1; h1 = h2; h2 = yv;
-        *q = fast_silu(z);
+    for (int m0 = 0; m0 < tokens; m0 += 32) {
+        float x[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) x[j] = m0 + j < tokens ? __ldcg(io + size_t(m0 + j) * channels + c) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            if (m0 + j < tokens) {
+                const float z = fmaf(h0, w0, fmaf(h1, w1, fmaf(h2, w2, x[j] * w3)));
+                h0 = h1; h1 = h2; h2 = x[j];
+                io[size_t(m0 + j) * channels + c] = fast_silu(z);
+            }
+        }
     }
     st[0] = h0; st[1] = h1; st[2] = h2;
 }
@@ -783,7 +790,7 @@ int gemm_umma_launch(const insg_gemv_op *op, cudaStream_t st)
     for (int i = 0; i < op->n_segments; i++) {
         const insg_gemv_segment &s = op->seg[i];
         if (s.epilogue == INSG_EPI_CONV_SILU && s.conv_token_stride == 0) { // one sequence: the history runs through the tokens
-            rc = launch(conv_tokens_kernel, dim3((s.rows + 255) / 256), dim3(256), 0, st, false, s.out, s.conv_state, s.conv_w, s.rows, tokens);
+            rc = launch(conv_tokens_kernel, dim3((s.rows + 63) / 64), dim3(64), 0, st, false, s.out, s.conv_state, s.conv_w, s.rows, tokens);
             if (rc != INSG_OK) return rc;
         }
     }

@@ -402,6 +402,7 @@ struct Multi {
     // dn_first and the state after the second to dn_second (bases of [24][32][128][128]); null = the workspace's state in place
     const float *dn_in = nullptr;
     float *dn_first = nullptr, *dn_second = nullptr;
+    int rows_hint = 0; // eager passes: the rows the pass's last token attends (the host's position + T); 0 inside a replayed graph
     explicit Multi(DecodeWorkspace &x, int t)
         : hidden(x.multi + kMultiHidden), qkv(x.multi + kMultiQkv), z(x.multi + kMultiZ), a(x.multi + kMultiA), b(x.multi + kMultiB),
           core(x.multi + kMultiCore), qg(x.multi + kMultiQg), key(x.multi + kMultiKey), value(x.multi + kMultiValue),
@@ -512,7 +513,7 @@ void attention_block_multi(Ctx &c, const Qwen35Decode::Plan::Block &b, void *kc,
     at.error_flag = x.d_token + 3;
     at.scratch = x.attn_scratch;
     at.scratch_bytes = size_t(kBigChunk) * insg_gqa_scratch_bytes(x.max_context);
-    insg_check(insg_attention_chunk(&at, u.T, u.qn, c.st));
+    insg_check(insg_attention_chunk(&at, u.T, u.qn, u.rows_hint, c.st));
     c.launches += 2;
 
     insg_gemv_op o = {};
@@ -852,6 +853,7 @@ void Qwen35Decode::forward_tokens(const int *tokens, int count)
         c.layout = use_umma ? 1 : -1;
         const std::vector<Plan::Block> &blocks = use_umma ? p.layers_umma : p.layers;
         Multi u(x_, T);
+        if (use_umma) u.rows_hint = x_.position + T; // eager passes only: a replayed graph must not bake the context length in
         sync_scalars(-1); // the chunk's first position; token m of the chunk sits at position + m
         cuda_check(cudaMemcpyAsync(u.tokens, tokens + done, size_t(T) * sizeof(int), cudaMemcpyHostToDevice, p.stream), "copy tokens");
         auto enqueue_chunk = [&] {

@@ -345,7 +345,7 @@ def attention_batch(qraw, k_raw, v, q_w, k_w, k_cache, v_cache, position, max_co
     return out.reshape(sequences, 4096)
 
 
-def attention_chunk(qraw, k_raw, v, q_w, k_w, k_cache, v_cache, position, max_context, scratch, tokens, fast_trig=True):
+def attention_chunk(qraw, k_raw, v, q_w, k_w, k_cache, v_cache, position, max_context, scratch, tokens, fast_trig=True, rows_hint=0):
     """``tokens`` consecutive tokens of one sequence (rows position .. position + tokens - 1) in two launches; qraw
     [tokens][8192], k_raw and v [tokens][1024]; scratch holds ``tokens`` zero-headed regions of :func:`gqa_scratch` size."""
     op = AttnOp()
@@ -356,7 +356,7 @@ def attention_chunk(qraw, k_raw, v, q_w, k_w, k_cache, v_cache, position, max_co
     op.kv_dtype = KV_BF16 if k_cache.dtype == torch.bfloat16 else KV_F32
     op.fast_trig, op.scratch, op.scratch_bytes, op.pdl = int(fast_trig), _p(scratch), scratch.numel(), 0
     qn = torch.empty(tokens * 4096, dtype=torch.float32, device=qraw.device)
-    check(_lib.lib().insg_attention_chunk(C.byref(op), tokens, _p(qn), _stream()))
+    check(_lib.lib().insg_attention_chunk(C.byref(op), tokens, _p(qn), rows_hint, _stream()))
     return out.reshape(tokens, 4096)
 
 

@@ -415,9 +415,10 @@ def test_attention_chunk_equals_token_steps_bitwise(cuda, kv_bf16):
     got = host(ops.attention_chunk(qraw, kraw, v, dev(qw), dev(kw), kc2, vc2, pos_dev, ctx, big, T))
     assert np.array_equal(got, np.stack(want))
     assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
-    # the scratch heads are left zero: a second chunk right behind the first gives the same again
+    # the scratch heads are left zero: a second chunk right behind the first gives the same again; with the host's hint of
+    # the context length fewer CTAs start, and the result is the same
     kc3, vc3 = history_k.clone(), history_v.clone()
-    assert np.array_equal(host(ops.attention_chunk(qraw, kraw, v, dev(qw), dev(kw), kc3, vc3, pos_dev, ctx, big, T)), got)
+    assert np.array_equal(host(ops.attention_chunk(qraw, kraw, v, dev(qw), dev(kw), kc3, vc3, pos_dev, ctx, big, T, rows_hint=start + T)), got)
     with pytest.raises(Exception, match="scratch"):
         ops.attention_chunk(qraw, kraw, v, dev(qw), dev(kw), kc3, vc3, pos_dev, ctx, scratch, T)
 
