@@ -54,14 +54,25 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
 
     pdl_wait();
 
+    // Every dependent input of a step is requested at once; with several steps the next step's inputs are requested
+    // before this step's arithmetic (they do not depend on it), so only the first step waits for a load.
+    // Each warp reads the whole q and k of the key head (four values per lane) and normalises them itself: L2 norms
+    // over 128 with eps added to the sum, as the reference.
+    float4 nq4 = __ldcg(reinterpret_cast<const float4 *>(q16 + kh * 128) + lane);
+    float4 nk4 = __ldcg(reinterpret_cast<const float4 *>(k16 + kh * 128) + lane);
+    float4 nv4 = __ldcg(reinterpret_cast<const float4 *>(v32 + head * 128 + slice * 32) + vq); // this thread's columns
+    float ng = __ldcg(g32 + head), nbeta = __ldcg(beta32 + head);
     for (int step = 0; step < tokens; step++, q16 += qkv_stride, k16 += qkv_stride, v32 += qkv_stride, g32 += 32, beta32 += 32, out32 += 4096) {
         __syncwarp(); // the previous step's reads of this warp's q/k copy are done
-        // Every dependent input is requested at once.  Each warp reads the whole q and k of the key head (four values per
-        // lane) and normalises them itself: L2 norms over 128 with eps added to the sum, as the reference.
-        const float4 q4 = __ldcg(reinterpret_cast<const float4 *>(q16 + kh * 128) + lane);
-        const float4 k4 = __ldcg(reinterpret_cast<const float4 *>(k16 + kh * 128) + lane);
-        const float4 v4 = __ldcg(reinterpret_cast<const float4 *>(v32 + head * 128 + slice * 32) + vq); // this thread's columns
-        const float g_in = __ldcg(g32 + head), beta = __ldcg(beta32 + head);
+        const float4 q4 = nq4, k4 = nk4, v4 = nv4;
+        const float g_in = ng, beta = nbeta;
+        if (step + 1 < tokens) {
+            nq4 = __ldcg(reinterpret_cast<const float4 *>(q16 + qkv_stride + kh * 128) + lane);
+            nk4 = __ldcg(reinterpret_cast<const float4 *>(k16 + qkv_stride + kh * 128) + lane);
+            nv4 = __ldcg(reinterpret_cast<const float4 *>(v32 + qkv_stride + head * 128 + slice * 32) + vq);
+            ng = __ldcg(g32 + 32 + head);
+            nbeta = __ldcg(beta32 + 32 + head);
+        }
         const float qn = warp_sum(fmaf(q4.x, q4.x, fmaf(q4.y, q4.y, fmaf(q4.z, q4.z, q4.w * q4.w))));
         const float kn = warp_sum(fmaf(k4.x, k4.x, fmaf(k4.y, k4.y, fmaf(k4.z, k4.z, k4.w * k4.w))));
         const float qs = rsqrtf(qn + 1e-6f) * 0.08838834764831845f, ks = rsqrtf(kn + 1e-6f);
