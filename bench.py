@@ -590,6 +590,9 @@ def run_tp_blocks(args, rank, world, local_rank):
     def graph_us(fn, steps):
         side = torch.cuda.Stream()
         with torch.cuda.stream(side):
+            if dist:
+                dist.barrier()  # the ranks reach the first exchange together (its waits are short)
+            torch.cuda.synchronize()
             for _ in range(3):
                 fn()
             side.synchronize()
