@@ -121,27 +121,34 @@ def test_config2_attention_decode_bf16_cache(cuda, ctx):
             # (from 2048 cached rows on the bf16 cache runs on the tensor cores with the query and the weights as two bf16
             # pieces each: a different rounding than the fp32 loop, far inside the bar above)
             got32 = ops.gqa_decode(dev(q), dev(kc), dev(vc), ctx).cpu().numpy()
-            assert np.max(np.abs(got32 - got)) <= (1e-6 if ctx < 2048 else 1e-5) * max(1.0, np.abs(got).max())
+            assert np.max(np.abs(got32 - got)) <= (1e-6 if ctx < 2048 else 2e-5) * max(1.0, np.abs(got).max())
 
 
+@pytest.mark.parametrize("kv_bf16", [True, False])
 @pytest.mark.parametrize("ctx", [2048, 2049, 2063, 4100, 6001])
-def test_attention_bf16_tensor_core_loop_ragged_lengths(cuda, ctx):
-    """The tensor-core loop of the bf16 cache (from 2048 rows on) at lengths that leave ragged last tiles and idle warps,
-    with large scores (sharp softmax) in one head, against the CPU oracle; the row past the end must not leak in."""
+def test_attention_tensor_core_loop_ragged_lengths(cuda, ctx, kv_bf16):
+    """The tensor-core loop of the bf16 cache (from 2048 rows on, 16 rows per warp step) at lengths that leave ragged last
+    tiles and idle warps, with large scores (sharp softmax) in one head, against the CPU oracle; the row past the end must
+    not leak in.  The fp32 cache (scalar loop at every length) runs the same cases."""
     from insignia_b200 import ops
 
     rng = np.random.default_rng(ctx)
-    kc, vc = bf16_round(rng.standard_normal(ctx * 1024)), bf16_round(rng.standard_normal(ctx * 1024) * 3)
+    kc, vc = rng.standard_normal(ctx * 1024).astype(np.float32), (rng.standard_normal(ctx * 1024) * 3).astype(np.float32)
+    if kv_bf16:
+        kc, vc = bf16_round(kc), bf16_round(vc)
+    dt = torch.bfloat16 if kv_bf16 else torch.float32
     q = rng.standard_normal(4096).astype(np.float32)
     q[:256] *= 6.0  # head 0: scores spread over +-6, the softmax picks a few rows
-    kbig = torch.full(((ctx + 8) * 1024,), 1.0e4, device="cuda").to(torch.bfloat16)  # what lies past the end is poison
-    vbig = torch.full(((ctx + 8) * 1024,), 1.0e4, device="cuda").to(torch.bfloat16)
-    kbig[: ctx * 1024] = dev(kc).to(torch.bfloat16)
-    vbig[: ctx * 1024] = dev(vc).to(torch.bfloat16)
+    kbig = torch.full(((ctx + 8) * 1024,), 1.0e4, device="cuda").to(dt)  # what lies past the end is poison
+    vbig = torch.full(((ctx + 8) * 1024,), 1.0e4, device="cuda").to(dt)
+    kbig[: ctx * 1024] = dev(kc).to(dt)
+    vbig[: ctx * 1024] = dev(vc).to(dt)
     got = ops.gqa_decode(dev(q), kbig, vbig, ctx).cpu().numpy()
     want = orc.gqa_decode(q, kc, vc, ctx)
     assert np.all(np.isfinite(got))
-    assert np.max(np.abs(got - want)) <= 3e-5 * max(1.0, np.abs(want).max())
+    err = float(np.max(np.abs(got - want)) / max(1.0, np.abs(want).max()))
+    print(f"ctx {ctx} {'bf16' if kv_bf16 else 'fp32'} cache: max error {err:.2e}")
+    assert err <= 3e-5
 
 
 def test_attention_step_bf16_long_context_fused_equals_unfused(cuda):
