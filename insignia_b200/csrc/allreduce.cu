@@ -145,6 +145,8 @@ int ar_check(const insg_comm *c, const float *data, int count)
     if (reinterpret_cast<uintptr_t>(data) & 15) return fail(INSG_E_ARG, "allreduce: data must be 16-byte aligned");
     for (int q = 0; q < c->world; q++)
         if (!c->peer[q]) return fail(INSG_E_ARG, "allreduce: communicator not connected");
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != c->device) return fail(INSG_E_ARG, "allreduce: the communicator belongs to another device than the current one");
     return INSG_OK;
 }
 } // namespace
