@@ -80,6 +80,7 @@ def test_config1_matmul_shapes_and_token_counts(cuda, rows, cols):
 
     w, s = _quantised(rows, cols, seed=rows + cols)
     packed = ops.repack(w, s)
+    tiles = ops.repack_umma(w, s)  # the same matrix in the tcgen05 kernel's layout (16 and 64 tokens go through it too)
     rng = np.random.default_rng(1)
     sample = np.sort(rng.choice(rows, 512, replace=False))
     pick = torch.from_numpy(sample).cuda()
@@ -102,6 +103,13 @@ def test_config1_matmul_shapes_and_token_counts(cuda, rows, cols):
         # a token's result does not depend on how many tokens travel with it
         y1 = ops.gemv_packed(packed, dev(x[M - 1])).cpu().numpy()
         assert np.array_equal(y1, y[M - 1])
+        if M >= 16:
+            # the tcgen05 kind::mxf4 kernel (sixteen tokens per instruction, stream-K shares): same bar on the sampled rows,
+            # and the whole matrix against the mma.sync kernel's result
+            yt = ops.gemm_umma(tiles, dev(x)).cpu().numpy().reshape(M, rows)
+            err_t = np.max(np.abs(yt[:, sample] - want)) / np.abs(want).max()
+            assert err_t <= 4e-6, (M, err_t)
+            assert np.max(np.abs(yt - y)) <= 4e-6 * np.abs(y).max()
 
 
 # ---------------------------------------------------------------------------------------------- configs[2]
