@@ -188,6 +188,38 @@ def test_prompt_in_passes_of_four_then_greedy_tokens_identical_to_reference(cuda
         ref.close()
 
 
+@pytest.mark.parametrize("sequences", [2, 8])
+def test_batch_on_the_full_model_identical_to_reference(cuda, full_ckpt, sequences):
+    """configs[4] on the full model: sequences decoded in lock step on one weight copy (2: mma.sync kernel, 8: tcgen05 kernel),
+    each from its own prompt; every sequence's greedy ids equal the reference engine's for that prompt."""
+    from insignia_b200.engine import Batch, Engine
+
+    n_prompt, n_gen = 24, 40
+    rng = np.random.default_rng(5)
+    prompts = rng.integers(0, 248320, (sequences, n_prompt))
+    want = []
+    for s in range(min(sequences, 3)):  # the reference decodes at 54 tok/s: three sequences are checked against it
+        ref = ref_engine.RefEngine(full_ckpt[1], max_context=n_prompt + n_gen + 4)  # a fresh engine: fresh recurrent state
+        try:
+            for t in prompts[s]:
+                ref.forward_token(int(t))
+            t = ref.logits_argmax()
+            toks = [t]
+            for _ in range(n_gen):
+                t = ref.decode_token(t)
+                toks.append(t)
+            want.append(toks)
+        finally:
+            ref.close()
+    with Engine(full_ckpt[1], max_context=8) as e, Batch(e, sequences, n_prompt + n_gen + 4) as b:
+        for i in range(n_prompt - 1):
+            b.forward_tokens(prompts[:, i])
+        first = b.decode_tokens(prompts[:, -1])
+        got = b.generate(first, n_gen)
+        for s in range(len(want)):
+            assert [first[s]] + list(got[:, s]) == want[s], s
+
+
 def test_mtp_draft_matches_reference(cuda, full_ckpt):
     """src/test_mtp.cu:3: forward a token, take the arg-max, draft twice."""
     from insignia_b200.engine import Engine
