@@ -568,6 +568,12 @@ __global__ void __launch_bounds__(kThreads, 1) persistent_token_kernel(const __g
     }
     __syncthreads();
     unsigned target = s_base;
+    // The scalars CTA 0 has just stored are read by every CTA of a first phase that is not CTA 0's alone (an attention
+    // phase reads the position): one barrier orders the store before those reads.  Once per launch, not per token.
+    if ((a.set_token >= 0 && a.d_token) || (a.set_position >= 0 && a.d_position)) {
+        target += unsigned(a.arrivals);
+        if (!grid_barrier(a, target, &s_ok)) return;
+    }
 
     // the prefetch cursors live in shared memory between phases: they must not cost registers in the record loop
     __shared__ PfCursor s_pf;

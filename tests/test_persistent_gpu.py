@@ -168,7 +168,7 @@ def test_program_inproj_deltanet_outproj(cuda):
 @pytest.mark.parametrize("kv_bf16", [False, True])
 def test_program_attention_phase_sequence_vs_oracle(cuda, kv_bf16):
     """The attention phase (norm + RoPE + cache write + split-K attention) over consecutive positions, run as a one-phase
-    program fed by a tiny copy phase, against the unfused oracle chain."""
+    program whose launch sets the position every CTA then reads, against the unfused oracle chain."""
     from insignia_b200 import ops
 
     rng = np.random.default_rng(103)
