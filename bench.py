@@ -386,7 +386,7 @@ def run_native(args, rank, world, local_rank):
                                "on, weights exceed L2)"},
         "clocks": clocks.summary(),
         "prefill": {"value": world * (args.prompt - PRE) / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": args.prompt - PRE,
-                    "how": "forward_tokens: passes of up to 32 tokens through the tcgen05 kernel (sixteen tokens per kind::mxf4 "
+                    "how": "forward_tokens: passes of up to 256 tokens through the tcgen05 kernel (sixteen tokens per kind::mxf4 "
                            "instruction), the DeltaNet recurrence of a pass in one launch per layer, the attention of a pass in "
                            "two launches per layer; outside the timed metric"},
     }

@@ -499,7 +499,7 @@ typedef struct insg_engine_options {
     int persistent;               /* 0: one launch per fused operation (162 per token), replayed from a CUDA graph when
                                      use_graph is set; 1: a token step is ONE persistent cooperative launch (insg_program_*) */
     int prefill_mma_sync;         /* 0: insg_engine_forward_tokens sends 16 or more tokens through the tcgen05 kernel in passes
-                                     of up to 32 (second copy of the weights in its tile layout); 1: always passes of four
+                                     of up to 256 (second copy of the weights in its tile layout); 1: always passes of four
                                      through the mma.sync kernel */
     int gemv_unprepared;          /* 0: a GEMV that writes the residual stream or the SwiGLU output leaves the next
                                      GEMV's input prepared (insg_gemv_segment.prep); 1: every GEMV converts its own */

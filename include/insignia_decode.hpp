@@ -37,7 +37,7 @@ struct DecodeOptions {
     bool prepared_inputs = true;   // a GEMV that writes the residual stream or the SwiGLU output also leaves the next GEMV's
                                    // input ready as fp16 pieces (and its sum of squares), so that one starts streaming
                                    // without normalising or converting anything; false: every GEMV prepares its own input
-    bool prefill_tcgen05 = true;   // forward_tokens with 16 or more tokens: passes of up to 32 tokens through the tcgen05
+    bool prefill_tcgen05 = true;   // forward_tokens with 16 or more tokens: passes of up to 256 tokens through the tcgen05
                                    // kernel (kind::mxf4, sixteen tokens per instruction; needs a second, tile-layout copy of
                                    // the weights); false: always passes of four tokens through the mma.sync kernel
     int n_layers = Qwen35Shape::layers;
@@ -68,7 +68,7 @@ public:
     int *d_next{};       // device: arg-max of the last logits
     void *attn_scratch{};
     void *argmax_scratch{};
-    float *multi{};      // device: activations of up to 32 consecutive tokens (forward_tokens)
+    float *multi{};      // device: activations of up to 256 consecutive tokens (forward_tokens)
     void *umma_scratch{}; // device: digit image of the activations for the tcgen05 kernel (forward_tokens)
     size_t umma_scratch_bytes{};
     void *prep{};        // device: prepared GEMV inputs, fp16 [2][4096] + fp16 [2][12288] + fp32 [2][296] sums of squares

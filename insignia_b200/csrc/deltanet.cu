@@ -166,7 +166,7 @@ extern "C" int insg_deltanet_decode_tokens(float *state, const float *q16, const
                                            insg_stream_t stream)
 {
     if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
-    if (tokens < 1 || tokens > 64 || qkv_stride < 0) return fail(INSG_E_SHAPE, "deltanet: 1..64 tokens per launch");
+    if (tokens < 1 || tokens > 1024 || qkv_stride < 0) return fail(INSG_E_SHAPE, "deltanet: 1..1024 tokens per launch");
     return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
                   beta32, out32, tokens, qkv_stride, 0ll, nullptr, nullptr);
 }

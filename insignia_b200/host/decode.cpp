@@ -28,7 +28,7 @@ constexpr size_t kPrepHidden = 0, kPrepAct = size_t(2) * kHidden * 2, kPrepSums 
 constexpr int kMultiSteps = 8; // token steps per graph in Qwen35Decode::generate
 // DecodeWorkspace::multi: activations of up to kChunk consecutive tokens for Qwen35Decode::forward_tokens, [token][width] each
 constexpr int kChunk = 4;     // tokens per pass of the mma.sync kernel
-constexpr int kBigChunk = 32; // tokens per pass of the tcgen05 kernel (two groups of sixteen)
+constexpr int kBigChunk = 256; // tokens per pass of the tcgen05 kernel (sixteen groups of sixteen)
 constexpr size_t kMultiHidden = 0, kMultiQkv = kMultiHidden + size_t(kBigChunk) * 4096, kMultiZ = kMultiQkv + size_t(kBigChunk) * 8192,
                  kMultiA = kMultiZ + size_t(kBigChunk) * 4096, kMultiB = kMultiA + size_t(kBigChunk) * 32,
                  kMultiCore = kMultiB + size_t(kBigChunk) * 32, kMultiQg = kMultiCore + size_t(kBigChunk) * 4096,

@@ -166,7 +166,7 @@ def test_prompt_in_passes_of_four_then_greedy_tokens_identical_to_reference(cuda
     reference fed token by token."""
     from insignia_b200.engine import Engine
 
-    n_prompt, n_gen = 61, 48  # 32 tokens through the tcgen05 kernel, 28 + 1 in passes of four and one
+    n_prompt, n_gen = 61, 48  # all 61 in one pass through the tcgen05 kernel
     rng = np.random.default_rng(77)
     prompt = [int(t) for t in rng.integers(0, 248320, n_prompt)]
     ref = ref_engine.RefEngine(full_ckpt[1], max_context=n_prompt + n_gen + 4)

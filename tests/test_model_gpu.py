@@ -174,13 +174,16 @@ def test_forward_tokens_equals_token_loop(cuda, golden_ckpt, count):
             e.forward_tokens([1, 248320])
 
 
-@pytest.mark.parametrize("count", [16, 37, 50])
+@pytest.mark.parametrize("count", [16, 37, 50, 300])
 def test_forward_tokens_through_tcgen05_passes(cuda, golden_ckpt, count):
-    """Prompts of 16 tokens or more go through the tcgen05 kernel in passes of up to 32 tokens (the rest in passes of
-    four): the same state as the token loop to rounding, the same arg-max, and decoding continues with the same tokens."""
+    """Prompts of 16 tokens or more go through the tcgen05 kernel in passes of up to 256 tokens (the rest in passes of
+    four; 300 tokens = a full pass, a second one of 44): the same state as the token loop to rounding, the same arg-max,
+    and decoding continues with the same tokens."""
     rng = np.random.default_rng(count)
     prompt = [int(t) for t in rng.integers(0, 64, count)]
-    with small_engine(golden_ckpt[1]) as a, small_engine(golden_ckpt[1], prefill_tcgen05=False) as b, small_engine(golden_ckpt[1]) as c:
+    ctx = max(64, count + 8)
+    with small_engine(golden_ckpt[1], max_context=ctx) as a, small_engine(golden_ckpt[1], max_context=ctx, prefill_tcgen05=False) as b, \
+            small_engine(golden_ckpt[1], max_context=ctx) as c:
         a.forward_tokens(prompt)
         b.forward_tokens(prompt)
         for t in prompt:
