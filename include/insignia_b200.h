@@ -63,6 +63,11 @@ INSG_API int insg_mxfp4_get_row_mlx(const uint32_t *weight, const uint8_t *scale
 INSG_API int insg_mxfp4_embed(const uint32_t *weight, const uint8_t *scales, float *out, const int *device_row,
                               int rows, int cols, int pdl, insg_stream_t stream);
 
+/* The same lookup for `count` tokens of a prompt pass in one launch: row indices device_rows[0..count), outputs
+ * out[m * cols ...].  Each row equals insg_mxfp4_embed's. */
+INSG_API int insg_mxfp4_embed_tokens(const uint32_t *weight, const uint8_t *scales, float *out, const int *device_rows,
+                                     int count, int rows, int cols, int pdl, insg_stream_t stream);
+
 /* Writes the two device scalars the engine's kernels read (token id, position); either pointer may be NULL. */
 INSG_API int insg_set_scalars(int *device_token, int token, int *device_position, int position, insg_stream_t stream);
 

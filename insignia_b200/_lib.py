@@ -51,6 +51,7 @@ SIGNATURES = {
     "insg_quantize_q8_groups": (i32, [vp, vp, vp, i32, vp]),
     "insg_mxfp4_gemv_dp4a": (i32, [vp, vp, vp, vp, vp, i32, i32, vp]),
     "insg_mxfp4_embed": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "insg_mxfp4_embed_tokens": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "insg_set_scalars": (i32, [vp, i32, vp, i32, vp]),
     "insg_mxfp4_dequant_mlx": (i32, [vp, vp, vp, i32, i32, vp]),
     "insg_mxfp4_packed_bytes": (sz, [i32, i32]),

@@ -149,6 +149,151 @@ __global__ void __launch_bounds__(kDnThreads) deltanet_step_kernel(float *__rest
     }
 }
 
+
+// The recurrence over many consecutive steps (a prompt pass): the same arithmetic in the same order as
+// deltanet_step_kernel, so the state and the outputs are bit-identical to single steps, with everything that does not
+// depend on the state taken off the serial chain.  Per block of 32 steps the eight warps normalise q and k (four steps
+// each, all loads in flight), fetch v, beta and exp(g) into shared memory; a step then is: products with the slice,
+// fold over k (shuffles + one CTA barrier), update, products with q.  The partial sums are double-buffered by step
+// parity, so one barrier per step is enough, and the output of step t is folded by warp 0 while step t+1 runs.
+constexpr int kDnBlock = 32;
+
+__global__ void __launch_bounds__(kDnThreads) deltanet_steps_kernel(float *__restrict__ state, const float *__restrict__ q16,
+                                                                    const float *__restrict__ k16, const float *__restrict__ v32,
+                                                                    const float *__restrict__ g32, const float *__restrict__ beta32,
+                                                                    float *__restrict__ out32, int tokens, int qkv_stride)
+{
+    __shared__ __align__(16) float s_q[kDnBlock][128];
+    __shared__ __align__(16) float s_k[kDnBlock][128];
+    __shared__ __align__(16) float s_v[kDnBlock][32];
+    __shared__ float s_decay[kDnBlock], s_beta[kDnBlock];
+    __shared__ __align__(16) float s_mem[2][8][32];
+    __shared__ __align__(16) float s_out[2][8][32];
+
+    const int head = blockIdx.x / kSlices, slice = blockIdx.x % kSlices, kh = head >> 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int vq = tid & 7, kr = tid >> 3;
+    const int v0 = slice * 32 + vq * 4;
+
+    pdl_launch_dependents();
+    float *S = state + size_t(head) * 128 * 128;
+    float4 cell[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) cell[j] = __ldcg(reinterpret_cast<const float4 *>(S + size_t(kr + 32 * j) * 128 + v0));
+    pdl_wait();
+
+    for (int base = 0; base < tokens; base += kDnBlock) {
+        const int nb = min(kDnBlock, tokens - base);
+        // ---- inputs of the block's steps: warp w takes steps w, w+8, w+16, w+24 (every read of the previous block's rows
+        // lies before the barrier of its last step, which every warp has passed) ----
+        {
+            float4 q4[4], k4[4], x4[4];
+            float gs[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int s = warp + 8 * i;
+                q4[i] = k4[i] = x4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                gs[i] = 0.f;
+                if (s < nb) {
+                    const size_t off = size_t(base + s) * qkv_stride;
+                    q4[i] = __ldcg(reinterpret_cast<const float4 *>(q16 + off + kh * 128) + lane);
+                    k4[i] = __ldcg(reinterpret_cast<const float4 *>(k16 + off + kh * 128) + lane);
+                    if (lane < 8) x4[i] = __ldcg(reinterpret_cast<const float4 *>(v32 + off + head * 128 + slice * 32) + lane);
+                    else if (lane == 8) gs[i] = __ldcg(g32 + size_t(base + s) * 32 + head);
+                    else if (lane == 9) gs[i] = __ldcg(beta32 + size_t(base + s) * 32 + head);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int s = warp + 8 * i;
+                if (s < nb) { // warp-uniform
+                    const float qn = warp_sum(fmaf(q4[i].x, q4[i].x, fmaf(q4[i].y, q4[i].y, fmaf(q4[i].z, q4[i].z, q4[i].w * q4[i].w))));
+                    const float kn = warp_sum(fmaf(k4[i].x, k4[i].x, fmaf(k4[i].y, k4[i].y, fmaf(k4[i].z, k4[i].z, k4[i].w * k4[i].w))));
+                    const float qs = rsqrtf(qn + 1e-6f) * 0.08838834764831845f, ks = rsqrtf(kn + 1e-6f);
+                    reinterpret_cast<float4 *>(s_q[s])[lane] = make_float4(q4[i].x * qs, q4[i].y * qs, q4[i].z * qs, q4[i].w * qs);
+                    reinterpret_cast<float4 *>(s_k[s])[lane] = make_float4(k4[i].x * ks, k4[i].y * ks, k4[i].z * ks, k4[i].w * ks);
+                    if (lane < 8) reinterpret_cast<float4 *>(s_v[s])[lane] = x4[i];
+                    else if (lane == 8) s_decay[s] = expf(gs[i]);
+                    else if (lane == 9) s_beta[s] = gs[i];
+                }
+            }
+        }
+        __syncthreads();
+
+        for (int s = 0; s < nb; s++) {
+            const int t = base + s, par = t & 1;
+            float qq[4], kk[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                qq[j] = s_q[s][kr + 32 * j];
+                kk[j] = s_k[s][kr + 32 * j];
+            }
+            const float decay = s_decay[s], beta = s_beta[s];
+            const float4 v4 = *reinterpret_cast<const float4 *>(&s_v[s][vq * 4]);
+
+            float4 pm = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                pm.x = fmaf(cell[j].x * decay, kk[j], pm.x);
+                pm.y = fmaf(cell[j].y * decay, kk[j], pm.y);
+                pm.z = fmaf(cell[j].z * decay, kk[j], pm.z);
+                pm.w = fmaf(cell[j].w * decay, kk[j], pm.w);
+            }
+#pragma unroll
+            for (int m = 8; m <= 16; m <<= 1) {
+                pm.x += __shfl_xor_sync(0xffffffffu, pm.x, m);
+                pm.y += __shfl_xor_sync(0xffffffffu, pm.y, m);
+                pm.z += __shfl_xor_sync(0xffffffffu, pm.z, m);
+                pm.w += __shfl_xor_sync(0xffffffffu, pm.w, m);
+            }
+            if (lane < 8) *reinterpret_cast<float4 *>(&s_mem[par][warp][lane * 4]) = pm;
+            __syncthreads();
+            if (t > 0 && tid < 32) { // the previous step's output, off the chain
+                float o = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; w++) o += s_out[par ^ 1][w][tid];
+                out32[size_t(t - 1) * 4096 + head * 128 + slice * 32 + tid] = o;
+            }
+            float4 mem = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < 8; w++) {
+                const float4 u = *reinterpret_cast<const float4 *>(&s_mem[par][w][vq * 4]);
+                mem.x += u.x; mem.y += u.y; mem.z += u.z; mem.w += u.w;
+            }
+            const float4 dl = make_float4((v4.x - mem.x) * beta, (v4.y - mem.y) * beta, (v4.z - mem.z) * beta, (v4.w - mem.w) * beta);
+            float4 po = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                cell[j].x = fmaf(cell[j].x, decay, kk[j] * dl.x);
+                cell[j].y = fmaf(cell[j].y, decay, kk[j] * dl.y);
+                cell[j].z = fmaf(cell[j].z, decay, kk[j] * dl.z);
+                cell[j].w = fmaf(cell[j].w, decay, kk[j] * dl.w);
+                po.x = fmaf(cell[j].x, qq[j], po.x);
+                po.y = fmaf(cell[j].y, qq[j], po.y);
+                po.z = fmaf(cell[j].z, qq[j], po.z);
+                po.w = fmaf(cell[j].w, qq[j], po.w);
+            }
+#pragma unroll
+            for (int m = 8; m <= 16; m <<= 1) {
+                po.x += __shfl_xor_sync(0xffffffffu, po.x, m);
+                po.y += __shfl_xor_sync(0xffffffffu, po.y, m);
+                po.z += __shfl_xor_sync(0xffffffffu, po.z, m);
+                po.w += __shfl_xor_sync(0xffffffffu, po.w, m);
+            }
+            if (lane < 8) *reinterpret_cast<float4 *>(&s_out[par][warp][lane * 4]) = po;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) *reinterpret_cast<float4 *>(S + size_t(kr + 32 * j) * 128 + v0) = cell[j];
+    __syncthreads();
+    if (tid < 32) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) o += s_out[(tokens - 1) & 1][w][tid];
+        out32[size_t(tokens - 1) * 4096 + head * 128 + slice * 32 + tid] = o;
+    }
+}
+
 } // namespace insg
 
 using namespace insg;
@@ -167,8 +312,11 @@ extern "C" int insg_deltanet_decode_tokens(float *state, const float *q16, const
 {
     if (!state || !q16 || !k16 || !v32 || !g32 || !beta32 || !out32) return fail(INSG_E_ARG, "deltanet: null pointer");
     if (tokens < 1 || tokens > 1024 || qkv_stride < 0) return fail(INSG_E_SHAPE, "deltanet: 1..1024 tokens per launch");
-    return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32,
-                  beta32, out32, tokens, qkv_stride, 0ll, nullptr, nullptr);
+    if (tokens == 1)
+        return launch(deltanet_step_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32, beta32,
+                      out32, 1, qkv_stride, 0ll, nullptr, nullptr);
+    return launch(deltanet_steps_kernel, dim3(32 * kSlices), dim3(kDnThreads), 0, stream, pdl != 0, state, q16, k16, v32, g32, beta32,
+                  out32, tokens, qkv_stride);
 }
 
 extern "C" int insg_deltanet_decode_verify(const float *state, float *state_first, float *state_second, const float *q16, const float *k16,

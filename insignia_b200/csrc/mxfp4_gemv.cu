@@ -79,7 +79,9 @@ __global__ void embed_kernel(const uint32_t *__restrict__ w, const uint8_t *__re
     pdl_wait();
     const int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= cols) return;
-    const int row = __ldcg(row_ptr);
+    // blockIdx.y: token of a prompt pass (its own row index, its own output row)
+    const int row = __ldcg(row_ptr + blockIdx.y);
+    out += size_t(blockIdx.y) * cols;
     if (row < 0 || row >= rows) {
         out[k] = 0.f;
         return;
@@ -159,6 +161,15 @@ int insg_mxfp4_embed(const uint32_t *weight, const uint8_t *scales, float *out, 
     if (!weight || !scales || !out || !device_row) return fail(INSG_E_ARG, "embed: null pointer");
     if (rows <= 0 || cols <= 0 || (cols & 31)) return fail(INSG_E_SHAPE, "embed: bad rows/cols");
     return launch(embed_kernel, dim3((cols + 255) / 256), dim3(256), 0, stream, pdl != 0, weight, scales, out, device_row, rows, cols);
+}
+
+int insg_mxfp4_embed_tokens(const uint32_t *weight, const uint8_t *scales, float *out, const int *device_rows, int count, int rows,
+                            int cols, int pdl, insg_stream_t stream)
+{
+    if (!weight || !scales || !out || !device_rows) return fail(INSG_E_ARG, "embed: null pointer");
+    if (rows <= 0 || cols <= 0 || (cols & 31) || count < 1 || count > 65535) return fail(INSG_E_SHAPE, "embed: bad rows/cols/count");
+    return launch(embed_kernel, dim3((cols + 255) / 256, count), dim3(256), 0, stream, pdl != 0, weight, scales, out, device_rows, rows,
+                  cols);
 }
 
 int insg_set_scalars(int *device_token, int token, int *device_position, int position, insg_stream_t stream)

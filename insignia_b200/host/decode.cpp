@@ -857,11 +857,9 @@ void Qwen35Decode::forward_tokens(const int *tokens, int count)
         sync_scalars(-1); // the chunk's first position; token m of the chunk sits at position + m
         cuda_check(cudaMemcpyAsync(u.tokens, tokens + done, size_t(T) * sizeof(int), cudaMemcpyHostToDevice, p.stream), "copy tokens");
         auto enqueue_chunk = [&] {
-            for (int m = 0; m < T; m++) {
-                insg_check(insg_mxfp4_embed(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
-                                            u.hidden + size_t(m) * kHidden, u.tokens + m, p.embed.rows, kHidden, c.pdl ? 1 : 0, p.stream));
-                launches_++;
-            }
+            insg_check(insg_mxfp4_embed_tokens(static_cast<const uint32_t *>(p.embed.weight.data), static_cast<const uint8_t *>(p.embed.scales.data),
+                                               u.hidden, u.tokens, T, p.embed.rows, kHidden, c.pdl ? 1 : 0, p.stream));
+            launches_++;
             for (int l = 0; l < n; l++) {
                 if (Qwen35Shape::full_attention(l)) {
                     const size_t esz = x_.options.kv_bf16 ? 2 : 4;

@@ -712,12 +712,13 @@ def test_gemv_fused_consecutive_tokens_equal_single_token_launches(cuda, tokens)
         assert np.array_equal(host(act_1), host(act_t[m])) and np.array_equal(host(res_1), host(res_t[m])), m
 
 
-def test_deltanet_several_steps_in_one_launch(cuda):
-    """Four consecutive steps in one launch (state kept on chip) equal four launches, bit for bit."""
+@pytest.mark.parametrize("T", [2, 4, 32, 33, 70])
+def test_deltanet_several_steps_in_one_launch(cuda, T):
+    """Consecutive steps in one launch (state kept on chip, inputs prepared per block of 32 steps, outputs folded one
+    step late) equal single-step launches, bit for bit."""
     from insignia_b200 import ops
 
-    rng = np.random.default_rng(51)
-    T = 4
+    rng = np.random.default_rng(51 + T)
     state0 = (rng.standard_normal(32 * 128 * 128) * 0.05).astype(np.float32)
     qkv = rng.standard_normal((T, 8192)).astype(np.float32)
     g = -rng.uniform(0.01, 1, (T, 32)).astype(np.float32)
