@@ -257,7 +257,7 @@ INSG_API int insg_program_finalize(insg_program *prog);
 INSG_API int insg_program_set_option(insg_program *prog, const char *key /* host */, long long value);
 /* Runs the program n_tokens times in one launch (the arg-max feedback of a LOGITS epilogue links consecutive tokens).
  * token / position >= 0 are first stored to *device_token / *device_position by the kernel itself (pass -1 to leave
- * them).  If a barrier wait runs out, *error_flag (device int, may be NULL) is set to 1, every CTA leaves the kernel and
+ * them), followed by one device-wide barrier, so every CTA of the first operation reads the new values.  If a barrier wait runs out, *error_flag (device int, may be NULL) is set to 1, every CTA leaves the kernel and
  * the results are undefined; call insg_program_recover before the next run. */
 INSG_API int insg_program_run(insg_program *prog, int n_tokens, int token, int position, int *device_token,
                               int *device_position, int *error_flag, insg_stream_t stream);
