@@ -283,8 +283,9 @@ INSG_API uint64_t insg_program_weight_bytes(const insg_program *prog);
 INSG_API int insg_deltanet_decode(float *state, const float *q16, const float *k16, const float *v32,
                                   const float *g32, const float *beta32, float *out32, int pdl,
                                   insg_stream_t stream);
-/* The same step for `tokens` (1..64) consecutive positions of the sequence in one launch: the state is read once,
- * kept on chip from step to step and written once.  q16/k16/v32 of step m are at + m * qkv_stride floats, g32/beta32 at
+/* The same step for `tokens` (1..1024) consecutive positions of the sequence in one launch: the state is read once,
+ * kept on chip from step to step and written once (two or more tokens run a kernel that prepares the inputs of 32
+ * steps at a time; bit-identical results).  q16/k16/v32 of step m are at + m * qkv_stride floats, g32/beta32 at
  * + m * 32, out32 at + m * 4096.  Same arithmetic as `tokens` calls of insg_deltanet_decode.  No reference counterpart. */
 INSG_API int insg_deltanet_decode_tokens(float *state, const float *q16, const float *k16, const float *v32,
                                          const float *g32, const float *beta32, float *out32, int tokens, int qkv_stride,
